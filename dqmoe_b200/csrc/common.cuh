@@ -1,0 +1,121 @@
+// Shared host/device helpers of the dqmoe_b200 library: error reporting for the
+// C ABI, the host-mapped device status word, and small device utilities.
+#pragma once
+
+#include <cuda.h>
+#include <cuda_bf16.h>
+#include <cuda_fp8.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+#include <cstdarg>
+#include <cstdio>
+#include <string>
+
+#include "../../include/dqmoe.h"
+
+namespace dq {
+
+// ---------------------------------------------------------------- host errors
+
+// Message of the last failure on this thread (returned by dqmoe_last_error()).
+std::string& last_error();
+
+int fail(int code, const char* file, int line, const char* cond, const char* fmt = nullptr, ...);
+
+// Argument check in the reference's CPU_CHECK form (csrc/util.h:173-195): the
+// C ABI returns DQMOE_ERR_INVALID and the Python layer raises RuntimeError with
+// the "[ASSERT FAILED] ..." text.
+#define DQ_CHECK(cond)                                                              \
+    do {                                                                            \
+        if (!(cond)) return ::dq::fail(DQMOE_ERR_INVALID, __FILE__, __LINE__, #cond); \
+    } while (0)
+#define DQ_CHECK_FMT(cond, ...)                                                                  \
+    do {                                                                                         \
+        if (!(cond)) return ::dq::fail(DQMOE_ERR_INVALID, __FILE__, __LINE__, #cond, __VA_ARGS__); \
+    } while (0)
+// CUDA failures become error returns; the reference's CUDA_CHECK calls exit()
+// (csrc/util.h:61-80).
+#define DQ_CUDA(expr)                                                                   \
+    do {                                                                                \
+        cudaError_t e_ = (expr);                                                        \
+        if (e_ != cudaSuccess)                                                          \
+            return ::dq::fail(DQMOE_ERR_CUDA, __FILE__, __LINE__, #expr, "%s",          \
+                              cudaGetErrorString(e_));                                  \
+    } while (0)
+#define DQ_LAUNCH_CHECK() DQ_CUDA(cudaGetLastError())
+
+// Host-mapped status word of the current device (allocated once per device in
+// pinned host memory; kernels write a non-zero code when a bounded wait gives up).
+// Returns the device-side pointer, or nullptr with last_error() set.
+int* device_status_word();
+// Host view of the same word for the current device.
+volatile int* host_status_word();
+
+int sm_count();
+
+static inline size_t align_up(size_t x, size_t a) { return (x + a - 1) / a * a; }
+static inline int ceil_div(int a, int b) { return (a + b - 1) / b; }
+static inline bool is_aligned(const void* p, size_t a) { return (reinterpret_cast<uintptr_t>(p) % a) == 0; }
+
+// ---------------------------------------------------------------- device utils
+
+// 16-byte vector used by all streaming kernels (coalesced 128-bit accesses).
+struct __align__(16) Vec16 {
+    uint32_t x, y, z, w;
+};
+
+__device__ __forceinline__ Vec16 ld_nc16(const void* p) {
+    Vec16 v;
+    asm volatile("ld.global.nc.L1::no_allocate.v4.u32 {%0,%1,%2,%3}, [%4];"
+                 : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w)
+                 : "l"(p));
+    return v;
+}
+__device__ __forceinline__ void st16(void* p, const Vec16& v) {
+    asm volatile("st.global.v4.u32 [%0], {%1,%2,%3,%4};" ::"l"(p), "r"(v.x), "r"(v.y), "r"(v.z), "r"(v.w)
+                 : "memory");
+}
+
+__device__ __forceinline__ float bf16_lo(uint32_t w) { return __uint_as_float(w << 16); }
+__device__ __forceinline__ float bf16_hi(uint32_t w) { return __uint_as_float(w & 0xffff0000u); }
+
+// round-to-nearest-even fp32 -> bf16 bits (matches torch's .to(bfloat16))
+__device__ __forceinline__ uint32_t f2bf_bits(float f) {
+    return static_cast<uint32_t>(__bfloat16_as_ushort(__float2bfloat16_rn(f)));
+}
+__device__ __forceinline__ float bf_round(float f) { return __bfloat162float(__float2bfloat16_rn(f)); }
+__device__ __forceinline__ uint32_t pack_bf16x2(float lo, float hi) { return f2bf_bits(lo) | (f2bf_bits(hi) << 16); }
+
+// two fp32 -> two e4m3 bytes (round-to-nearest-even, saturating to +-448), lo in bits 0..7
+__device__ __forceinline__ uint32_t f2e4m3x2(float lo, float hi) {
+    uint16_t r;
+    asm("cvt.rn.satfinite.e4m3x2.f32 %0, %1, %2;" : "=h"(r) : "f"(hi), "f"(lo));
+    return r;
+}
+__device__ __forceinline__ uint32_t f2e4m3x4(float a, float b, float c, float d) {
+    return f2e4m3x2(a, b) | (f2e4m3x2(c, d) << 16);
+}
+
+// The reference's torch quantisers: sf = clamp(amax, 1e-4) / 448 ; inv = 1 / sf
+// (test/util.py:21-23). Both divisions are IEEE round-to-nearest.
+__device__ __forceinline__ float scale_from_amax(float amax) { return __fdiv_rn(fmaxf(amax, 1e-4f), 448.0f); }
+__device__ __forceinline__ float inv_scale(float sf) { return __fdiv_rn(1.0f, sf); }
+
+__device__ __forceinline__ float warp_max(float v) {
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, o));
+    return v;
+}
+__device__ __forceinline__ float warp_sum(float v) {
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+    return v;
+}
+
+// non-negative floats order like their bit patterns
+__device__ __forceinline__ void atomic_max_nonneg(float* addr, float v) {
+    atomicMax(reinterpret_cast<int*>(addr), __float_as_int(v));
+}
+
+}  // namespace dq

@@ -1,0 +1,623 @@
+// Grouped GEMM for expert-sorted rows on sm_100a: a persistent, warp-specialised
+// kernel with TMA-fed shared-memory stages, tcgen05 MMA (128 x 256 tiles, fp32
+// accumulators in TMEM) and fused epilogues:
+//   stage 1 (gated): SwiGLU, plus 1x128 dynamic FP8 re-quantisation in block mode
+//                    or amax collection in tensor/channel mode;
+//   stage 2        : dequantisation and row scatter into the [T, k, H] output.
+// In block mode (1x128 activation scales, 128x128 weight scales) the partial sum
+// of every 128-wide K block is drained from TMEM, multiplied by its scale pair
+// and accumulated in registers while the next K block runs on the tensor cores
+// into the other TMEM buffer.
+//
+// Replaces the six CUTLASS grouped-GEMM variants of the reference and their
+// per-expert "configure" kernels (csrc/moe_gemm_template.h:72-1039) together
+// with doGatedActivationKernel, scale_1x128_kernel and finalizeScatterKernel
+// (csrc/moe_kernels.h:301-444, 581-620).
+#include "common.cuh"
+#include "ptx_sm100.cuh"
+
+namespace dq {
+namespace gemm {
+
+constexpr int kBM = 128;                          // rows per tile = UMMA M
+constexpr int kBoxRows = 128;                     // weight rows per TMA box, two boxes per stage
+constexpr int kUmmaN = 2 * kBoxRows;              // 256 accumulator columns per tile
+constexpr int kBKBytes = 128;                     // K bytes per stage: one 128-byte swizzle row
+constexpr int kUmmaKBytes = 32;                   // K bytes per tcgen05.mma
+constexpr int kStages = 4;
+constexpr int kABytes = kBM * kBKBytes;           // 16 KiB
+constexpr int kBBytes = kUmmaN * kBKBytes;        // 32 KiB
+constexpr int kStageBytes = kABytes + kBBytes;    // 48 KiB
+constexpr int kThreads = 320;                     // warp 0 TMA, warp 1 MMA, warps 2..9 epilogue
+constexpr int kEpiWarps = 8;
+constexpr int kMaxExperts = 1024;
+constexpr int kTmemCols = 512;                    // two accumulator buffers of 256 columns
+constexpr long long kWaitLimit = 1000000000LL;    // clock cycles before a wait gives up (~0.5 s)
+
+enum Mode : int { kNone = 0, kTensor = 1, kChannel = 2, kBlock = 3 };
+
+struct Params {
+    int n_rows;          // rows of A (expanded rows n)
+    int N;               // output columns (stage 1: I, stage 2: H)
+    int K;               // reduction length in elements
+    int E;
+    int n_tiles;         // column tiles per row tile
+    int w_rows;          // weight rows per expert (stage 1: 2I, stage 2: H)
+    int tile_w_rows;     // weight rows advanced per column tile (stage 1: 128, stage 2: 256)
+    int box2_off;        // row offset of the second weight box (stage 1: I, stage 2: 128)
+    int kb_count;        // ceil(K bytes / 128)
+    const int* offsets;       // [E+1] first row of each expert
+    const int* mtile_prefix;  // [E+1] cumulative 128-row tiles
+    const float* sa;          // activation scales
+    const float* sb;          // weight scales
+    void* out;
+    float* out_scale;         // stage 1 block mode: [n, ceil(I/128)]
+    float* amax;              // stage 1 channel: [n]; tensor: [1]
+    const int* dest_to_src;   // stage 2 scatter map or nullptr
+    int* status;              // host-mapped status word
+};
+
+struct SharedTail {
+    uint64_t full[kStages];
+    uint64_t empty[kStages];
+    uint64_t tmem_full[2];
+    uint64_t tmem_empty[2];
+    uint64_t epi_sync;
+    uint32_t tmem_base;
+    int abort_flag;
+    float amax[2][2][kBM];
+    int mprefix[kMaxExperts + 1];
+    int offsets[kMaxExperts + 1];
+};
+
+constexpr size_t kSmemBytes = 1024 + size_t(kStages) * kStageBytes + sizeof(SharedTail);
+
+struct Tile {
+    int e, row0, row_end, nt;
+};
+
+// Tiles are numbered expert-major; inside an expert the row tile runs fastest so
+// that concurrently running CTAs share one weight tile and the expert's rows
+// stay in L2.
+__device__ __forceinline__ Tile decode_tile(int t, int& e_cursor, const SharedTail& st, int n_tiles) {
+    while (t >= st.mprefix[e_cursor + 1] * n_tiles) ++e_cursor;
+    const int local = t - st.mprefix[e_cursor] * n_tiles;
+    const int mtiles = st.mprefix[e_cursor + 1] - st.mprefix[e_cursor];
+    Tile tl;
+    tl.e = e_cursor;
+    tl.nt = local / mtiles;
+    tl.row0 = st.offsets[e_cursor] + (local % mtiles) * kBM;
+    tl.row_end = st.offsets[e_cursor + 1];
+    return tl;
+}
+
+__device__ __forceinline__ float silu_bf16(float g) {
+    // the torch oracle evaluates silu on bf16 and rounds the result to bf16 (test/util.py:141-142)
+    return bf_round(__fdividef(g, 1.0f + __expf(-g)));
+}
+
+template <bool kFp8, int kMode, bool kGated>
+__global__ void __maxnreg__(200)
+moe_GemmGrouped_GemmUniversal_tcgen05(const __grid_constant__ CUtensorMap tma_a,
+                                      const __grid_constant__ CUtensorMap tma_b, const Params p) {
+    extern __shared__ uint8_t smem_raw[];
+    uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+    SharedTail& st = *reinterpret_cast<SharedTail*>(smem + size_t(kStages) * kStageBytes);
+
+    const int warp = threadIdx.x >> 5;
+    const int lane = threadIdx.x & 31;
+    constexpr int kBKElems = kFp8 ? kBKBytes : kBKBytes / 2;
+
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < kStages; ++s) {
+            ptx::mbar_init(&st.full[s], 1);
+            ptx::mbar_init(&st.empty[s], 1);
+        }
+        for (int b = 0; b < 2; ++b) {
+            ptx::mbar_init(&st.tmem_full[b], 1);
+            ptx::mbar_init(&st.tmem_empty[b], kEpiWarps);
+        }
+        ptx::mbar_init(&st.epi_sync, kEpiWarps);
+        st.abort_flag = 0;
+        ptx::fence_barrier_init();
+        ptx::fence_proxy_async();
+    }
+    if (warp == 1) {
+        ptx::tmem_alloc(&st.tmem_base, kTmemCols);
+        ptx::tmem_relinquish();
+    }
+    for (int i = threadIdx.x; i <= p.E; i += kThreads) {
+        st.mprefix[i] = p.mtile_prefix[i];
+        st.offsets[i] = p.offsets[i];
+    }
+    ptx::tc_fence_before();
+    __syncthreads();
+    ptx::tc_fence_after();
+
+    const uint32_t tmem_base = st.tmem_base;
+    const int total_tiles = st.mprefix[p.E] * p.n_tiles;
+    volatile int* abort_flag = &st.abort_flag;
+    const int kb_count = p.kb_count;
+
+    if (warp == 0) {
+        // ------------------------------------------------------------ TMA producer
+        if (lane == 0) {
+            ptx::prefetch_tensormap(&tma_a);
+            ptx::prefetch_tensormap(&tma_b);
+            uint32_t it = 0;
+            int e_cursor = 0;
+            bool ok = true;
+            for (int t = blockIdx.x; ok && t < total_tiles; t += gridDim.x) {
+                const Tile tl = decode_tile(t, e_cursor, st, p.n_tiles);
+                const int wrow0 = tl.e * p.w_rows + tl.nt * p.tile_w_rows;
+                const int wrow1 = wrow0 + p.box2_off;
+                for (int kb = 0; kb < kb_count; ++kb, ++it) {
+                    const int s = it % kStages;
+                    const uint32_t ph = (it / kStages) & 1u;
+                    if (!ptx::mbar_wait(&st.empty[s], ph ^ 1u, abort_flag, kWaitLimit)) {
+                        ok = false;
+                        break;
+                    }
+                    uint8_t* sa = smem + size_t(s) * kStageBytes;
+                    uint8_t* sb = sa + kABytes;
+                    ptx::mbar_arrive_expect_tx(&st.full[s], kStageBytes);
+                    const int k0 = kb * kBKElems;
+                    ptx::tma_load_2d(sa, &tma_a, k0, tl.row0, &st.full[s]);
+                    ptx::tma_load_2d(sb, &tma_b, k0, wrow0, &st.full[s]);
+                    ptx::tma_load_2d(sb + kBoxRows * kBKBytes, &tma_b, k0, wrow1, &st.full[s]);
+                }
+            }
+        }
+        __syncwarp();
+    } else if (warp == 1) {
+        // ------------------------------------------------------------ MMA issuer
+        if (lane == 0) {
+            constexpr uint32_t idesc = ptx::make_idesc(kFp8 ? 0u : 1u, kBM, kUmmaN);
+            uint32_t it = 0;
+            uint32_t acc_it = 0;
+            bool ok = true;
+            for (int t = blockIdx.x; ok && t < total_tiles; t += gridDim.x) {
+                if constexpr (kMode != kBlock) {
+                    const uint32_t buf = acc_it & 1u;
+                    if (!ptx::mbar_wait(&st.tmem_empty[buf], ((acc_it >> 1) & 1u) ^ 1u, abort_flag, kWaitLimit)) {
+                        ok = false;
+                        break;
+                    }
+                    ptx::tc_fence_after();
+                    for (int kb = 0; kb < kb_count; ++kb, ++it) {
+                        const int s = it % kStages;
+                        if (!ptx::mbar_wait(&st.full[s], (it / kStages) & 1u, abort_flag, kWaitLimit)) {
+                            ok = false;
+                            break;
+                        }
+                        ptx::tc_fence_after();
+                        const uint32_t a_addr = ptx::smem_u32(smem + size_t(s) * kStageBytes);
+                        const uint32_t b_addr = a_addr + kABytes;
+#pragma unroll
+                        for (int k = 0; k < kBKBytes / kUmmaKBytes; ++k) {
+                            ptx::umma<kFp8>(tmem_base + buf * kUmmaN, ptx::smem_desc_sw128(a_addr + k * kUmmaKBytes),
+                                            ptx::smem_desc_sw128(b_addr + k * kUmmaKBytes), idesc,
+                                            (kb | k) != 0 ? 1u : 0u);
+                        }
+                        ptx::umma_commit(&st.empty[s]);
+                    }
+                    if (!ok) break;
+                    ptx::umma_commit(&st.tmem_full[buf]);
+                    ++acc_it;
+                } else {
+                    for (int kb = 0; kb < kb_count; ++kb, ++it, ++acc_it) {
+                        const uint32_t buf = acc_it & 1u;
+                        const int s = it % kStages;
+                        if (!ptx::mbar_wait(&st.tmem_empty[buf], ((acc_it >> 1) & 1u) ^ 1u, abort_flag,
+                                            kWaitLimit) ||
+                            !ptx::mbar_wait(&st.full[s], (it / kStages) & 1u, abort_flag, kWaitLimit)) {
+                            ok = false;
+                            break;
+                        }
+                        ptx::tc_fence_after();
+                        const uint32_t a_addr = ptx::smem_u32(smem + size_t(s) * kStageBytes);
+                        const uint32_t b_addr = a_addr + kABytes;
+#pragma unroll
+                        for (int k = 0; k < kBKBytes / kUmmaKBytes; ++k) {
+                            ptx::umma<kFp8>(tmem_base + buf * kUmmaN, ptx::smem_desc_sw128(a_addr + k * kUmmaKBytes),
+                                            ptx::smem_desc_sw128(b_addr + k * kUmmaKBytes), idesc, k != 0 ? 1u : 0u);
+                        }
+                        ptx::umma_commit(&st.empty[s]);
+                        ptx::umma_commit(&st.tmem_full[buf]);
+                    }
+                }
+            }
+        }
+        __syncwarp();
+    } else {
+        // ------------------------------------------------------------ epilogue warps
+        const int q = warp & 3;            // TMEM lane quarter this warp may read
+        const int h = (warp - 2) >> 2;     // which 64-column half of each 128-column group
+        const int r_in_tile = q * 32 + lane;
+        const uint32_t t_lane = tmem_base + (static_cast<uint32_t>(q * 32) << 16);
+        uint32_t acc_it = 0;
+        uint32_t tile_it = 0;
+        uint32_t epi_phase = 0;
+        int e_cursor = 0;
+        bool ok = true;
+        const int I_or_H = p.N;
+
+        for (int t = blockIdx.x; ok && t < total_tiles; t += gridDim.x, ++tile_it) {
+            const Tile tl = decode_tile(t, e_cursor, st, p.n_tiles);
+            const int grow = tl.row0 + r_in_tile;
+            const bool row_ok = grow < tl.row_end;
+            const int grow_ld = min(grow, p.n_rows - 1);
+
+            if constexpr (kMode != kBlock) {
+                const uint32_t buf = acc_it & 1u;
+                if (!ptx::mbar_wait(&st.tmem_full[buf], (acc_it >> 1) & 1u, abort_flag, kWaitLimit)) {
+                    ok = false;
+                    break;
+                }
+                ++acc_it;
+                ptx::tc_fence_after();
+                const uint32_t t_buf = t_lane + buf * kUmmaN;
+
+                if constexpr (kGated) {
+                    // columns [h*64, h*64+64) of the gate group and of the value group
+                    float row_scale = 1.0f;
+                    if constexpr (kMode == kTensor) row_scale = p.sa[0] * p.sb[tl.e];
+                    if constexpr (kMode == kChannel) row_scale = p.sa[grow_ld];
+                    float amax_local = 0.0f;
+#pragma unroll 1
+                    for (int j = 0; j < 2; ++j) {
+                        uint32_t g[32], v[32];
+                        const int c0 = h * 64 + j * 32;  // column inside the 128-wide act tile
+                        ptx::tmem_ld32(t_buf + c0, g);
+                        ptx::tmem_ld32(t_buf + kBoxRows + c0, v);
+                        ptx::tmem_wait_ld(g);
+                        ptx::tmem_wait_ld(v);
+                        const int col0 = tl.nt * kBoxRows + c0;
+                        uint32_t packed[16];
+#pragma unroll
+                        for (int i = 0; i < 32; i += 2) {
+                            float a2[2];
+#pragma unroll
+                            for (int u = 0; u < 2; ++u) {
+                                float sg = row_scale, sv = row_scale;
+                                if constexpr (kMode == kChannel) {
+                                    const int c = min(col0 + i + u, I_or_H - 1);
+                                    sg *= p.sb[size_t(tl.e) * p.w_rows + c];
+                                    sv *= p.sb[size_t(tl.e) * p.w_rows + I_or_H + c];
+                                }
+                                const float gate = bf_round(__uint_as_float(g[i + u]) * sg);
+                                const float val = bf_round(__uint_as_float(v[i + u]) * sv);
+                                const float act = bf_round(silu_bf16(gate) * val);
+                                a2[u] = act;
+                                if (col0 + i + u < I_or_H) amax_local = fmaxf(amax_local, fabsf(act));
+                            }
+                            packed[i >> 1] = pack_bf16x2(a2[0], a2[1]);
+                        }
+                        if (row_ok) {
+                            __nv_bfloat16* orow = reinterpret_cast<__nv_bfloat16*>(p.out) + size_t(grow) * I_or_H;
+#pragma unroll
+                            for (int g8 = 0; g8 < 4; ++g8) {
+                                if (col0 + g8 * 8 < I_or_H) {
+                                    Vec16 vv{packed[g8 * 4], packed[g8 * 4 + 1], packed[g8 * 4 + 2], packed[g8 * 4 + 3]};
+                                    st16(orow + col0 + g8 * 8, vv);
+                                }
+                            }
+                        }
+                    }
+                    if constexpr (kMode == kChannel) {
+                        if (row_ok) atomic_max_nonneg(p.amax + grow, amax_local);
+                    }
+                    if constexpr (kMode == kTensor) {
+                        float m = row_ok ? amax_local : 0.0f;
+                        m = warp_max(m);
+                        if (lane == 0) atomic_max_nonneg(p.amax, m);
+                    }
+                } else {
+                    // stage 2: columns h*64 + {0,32} of each of the two 128-column groups
+                    float row_scale = 1.0f;
+                    if constexpr (kMode == kTensor) row_scale = p.sa[0] * p.sb[tl.e];
+                    if constexpr (kMode == kChannel) row_scale = p.sa[grow_ld];
+                    int orow_idx = grow;
+                    if (row_ok && p.dest_to_src != nullptr) orow_idx = p.dest_to_src[grow];
+                    __nv_bfloat16* orow = reinterpret_cast<__nv_bfloat16*>(p.out) + size_t(orow_idx) * I_or_H;
+#pragma unroll 1
+                    for (int c = 0; c < 4; ++c) {
+                        uint32_t r[32];
+                        const int tc = (c >> 1) * kBoxRows + h * 64 + (c & 1) * 32;
+                        ptx::tmem_ld32(t_buf + tc, r);
+                        ptx::tmem_wait_ld(r);
+                        const int col0 = tl.nt * kUmmaN + tc;
+                        uint32_t packed[16];
+#pragma unroll
+                        for (int i = 0; i < 32; i += 2) {
+                            float s0 = row_scale, s1 = row_scale;
+                            if constexpr (kMode == kChannel) {
+                                s0 *= p.sb[size_t(tl.e) * p.w_rows + min(col0 + i, I_or_H - 1)];
+                                s1 *= p.sb[size_t(tl.e) * p.w_rows + min(col0 + i + 1, I_or_H - 1)];
+                            }
+                            packed[i >> 1] = pack_bf16x2(__uint_as_float(r[i]) * s0, __uint_as_float(r[i + 1]) * s1);
+                        }
+                        if (row_ok && orow_idx >= 0) {
+#pragma unroll
+                            for (int g8 = 0; g8 < 4; ++g8) {
+                                if (col0 + g8 * 8 < I_or_H) {
+                                    Vec16 vv{packed[g8 * 4], packed[g8 * 4 + 1], packed[g8 * 4 + 2], packed[g8 * 4 + 3]};
+                                    st16(orow + col0 + g8 * 8, vv);
+                                }
+                            }
+                        }
+                    }
+                }
+                ptx::tc_fence_before();
+                __syncwarp();
+                if (lane == 0) ptx::mbar_arrive(&st.tmem_empty[buf]);
+            } else {
+                // ---------------------------------------------------- block-scaled accumulation
+                // acc[c*32 + i]: chunk c of this thread's four 32-column chunks.
+                float acc[128];
+#pragma unroll
+                for (int i = 0; i < 128; ++i) acc[i] = 0.0f;
+
+                const int KB = kb_count;                      // scale blocks along K
+                const int NB = (p.w_rows + 127) / 128;        // weight scale block rows per expert
+                const float* sa_row = p.sa + size_t(grow_ld) * KB;
+                // weight-scale block row of the first group and of the second group (two candidates)
+                int nb0, nb1_lo, nb1_hi, c_switch;
+                if constexpr (kGated) {
+                    nb0 = tl.nt;                              // gate rows nt*128 ..
+                    const int v0 = I_or_H + tl.nt * kBoxRows; // first value row of this tile
+                    nb1_lo = v0 >> 7;
+                    c_switch = 128 - (v0 & 127);              // value columns >= c_switch use the next block row
+                    nb1_hi = nb1_lo + 1;
+                } else {
+                    nb0 = tl.nt * 2;
+                    nb1_lo = nb0 + 1;
+                    nb1_hi = nb1_lo;
+                    c_switch = 128;
+                }
+                nb0 = min(nb0, NB - 1);
+                nb1_lo = min(nb1_lo, NB - 1);
+                nb1_hi = min(nb1_hi, NB - 1);
+                const float* sb0 = p.sb + (size_t(tl.e) * NB + nb0) * KB;
+                const float* sb1l = p.sb + (size_t(tl.e) * NB + nb1_lo) * KB;
+                const float* sb1h = p.sb + (size_t(tl.e) * NB + nb1_hi) * KB;
+                const bool uniform = (c_switch & 31) == 0;
+
+                for (int kb = 0; kb < KB; ++kb, ++acc_it) {
+                    const float a_s = sa_row[kb];
+                    const float s0 = a_s * sb0[kb];
+                    const float s1l = a_s * sb1l[kb];
+                    const float s1h = a_s * sb1h[kb];
+                    const uint32_t buf = acc_it & 1u;
+                    if (!ptx::mbar_wait(&st.tmem_full[buf], (acc_it >> 1) & 1u, abort_flag, kWaitLimit)) {
+                        ok = false;
+                        break;
+                    }
+                    ptx::tc_fence_after();
+                    const uint32_t t_buf = t_lane + buf * kUmmaN;
+#pragma unroll
+                    for (int c = 0; c < 4; ++c) {
+                        uint32_t r[32];
+                        const int cin = h * 64 + (c & 1) * 32;  // column inside the 128-column group
+                        ptx::tmem_ld32(t_buf + (c >> 1) * kBoxRows + cin, r);
+                        ptx::tmem_wait_ld(r);
+                        if (c < 2) {
+#pragma unroll
+                            for (int i = 0; i < 32; ++i) acc[c * 32 + i] = fmaf(__uint_as_float(r[i]), s0, acc[c * 32 + i]);
+                        } else if (uniform) {
+                            const float s1 = cin < c_switch ? s1l : s1h;
+#pragma unroll
+                            for (int i = 0; i < 32; ++i) acc[c * 32 + i] = fmaf(__uint_as_float(r[i]), s1, acc[c * 32 + i]);
+                        } else {
+#pragma unroll
+                            for (int i = 0; i < 32; ++i)
+                                acc[c * 32 + i] =
+                                    fmaf(__uint_as_float(r[i]), (cin + i) < c_switch ? s1l : s1h, acc[c * 32 + i]);
+                        }
+                    }
+                    ptx::tc_fence_before();
+                    __syncwarp();
+                    if (lane == 0) ptx::mbar_arrive(&st.tmem_empty[buf]);
+                }
+                if (!ok) break;
+
+                if constexpr (kGated) {
+                    // act columns nt*128 + h*64 + [0, 64): gate = acc[0..63], value = acc[64..127]
+                    const int col0 = tl.nt * kBoxRows + h * 64;
+                    float amax_local = 0.0f;
+#pragma unroll
+                    for (int i = 0; i < 64; ++i) {
+                        const float gate = bf_round(acc[i]);
+                        const float val = bf_round(acc[64 + i]);
+                        float act = bf_round(silu_bf16(gate) * val);
+                        if (col0 + i >= I_or_H) act = 0.0f;
+                        acc[i] = act;
+                        amax_local = fmaxf(amax_local, fabsf(act));
+                    }
+                    // the 1x128 group spans both halves: exchange the partial amax through shared memory
+                    st.amax[tile_it & 1u][h][r_in_tile] = amax_local;
+                    __syncwarp();
+                    if (lane == 0) ptx::mbar_arrive(&st.epi_sync);
+                    if (!ptx::mbar_wait(&st.epi_sync, epi_phase, abort_flag, kWaitLimit)) {
+                        ok = false;
+                        break;
+                    }
+                    epi_phase ^= 1u;
+                    const float amax = fmaxf(amax_local, st.amax[tile_it & 1u][h ^ 1][r_in_tile]);
+                    const float sf = scale_from_amax(amax);
+                    const float inv = inv_scale(sf);
+                    if (row_ok) {
+                        uint8_t* orow = reinterpret_cast<uint8_t*>(p.out) + size_t(grow) * I_or_H;
+#pragma unroll
+                        for (int g16 = 0; g16 < 4; ++g16) {
+                            if (col0 + g16 * 16 < I_or_H) {
+                                Vec16 vv;
+                                const float* a = acc + g16 * 16;
+                                vv.x = f2e4m3x4(a[0] * inv, a[1] * inv, a[2] * inv, a[3] * inv);
+                                vv.y = f2e4m3x4(a[4] * inv, a[5] * inv, a[6] * inv, a[7] * inv);
+                                vv.z = f2e4m3x4(a[8] * inv, a[9] * inv, a[10] * inv, a[11] * inv);
+                                vv.w = f2e4m3x4(a[12] * inv, a[13] * inv, a[14] * inv, a[15] * inv);
+                                st16(orow + col0 + g16 * 16, vv);
+                            }
+                        }
+                        if (h == 0) p.out_scale[size_t(grow) * ((I_or_H + 127) / 128) + tl.nt] = sf;
+                    }
+                } else {
+                    int orow_idx = grow;
+                    if (row_ok && p.dest_to_src != nullptr) orow_idx = p.dest_to_src[grow];
+                    if (row_ok && orow_idx >= 0) {
+                        __nv_bfloat16* orow = reinterpret_cast<__nv_bfloat16*>(p.out) + size_t(orow_idx) * I_or_H;
+#pragma unroll
+                        for (int c = 0; c < 4; ++c) {
+                            const int col0 = tl.nt * kUmmaN + (c >> 1) * kBoxRows + h * 64 + (c & 1) * 32;
+#pragma unroll
+                            for (int g8 = 0; g8 < 4; ++g8) {
+                                if (col0 + g8 * 8 < I_or_H) {
+                                    const float* a = acc + c * 32 + g8 * 8;
+                                    Vec16 vv{pack_bf16x2(a[0], a[1]), pack_bf16x2(a[2], a[3]), pack_bf16x2(a[4], a[5]),
+                                             pack_bf16x2(a[6], a[7])};
+                                    st16(orow + col0 + g8 * 8, vv);
+                                }
+                            }
+                        }
+                    }
+                }
+            }
+        }
+    }
+
+    // ---------------------------------------------------------------- teardown
+    if (*abort_flag != 0) {
+        // a wait gave up: report instead of trapping, let copies in flight land, then free TMEM
+        if (threadIdx.x == 0 && p.status != nullptr) {
+            *reinterpret_cast<volatile int*>(p.status) = 100 + (kGated ? 0 : 10) + kMode;
+            __threadfence_system();
+        }
+        for (int i = 0; i < 2000; ++i) __nanosleep(1000);
+    }
+    ptx::tc_fence_before();
+    __syncthreads();
+    if (warp == 1) {
+        ptx::tc_fence_after();
+        ptx::tmem_dealloc(tmem_base, kTmemCols);
+    }
+}
+
+// ---------------------------------------------------------------- host side
+
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                  const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+static EncodeTiledFn encode_fn() {
+    static EncodeTiledFn fn = nullptr;
+    if (fn == nullptr) {
+        void* p = nullptr;
+        cudaDriverEntryPointQueryResult qres;
+        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &qres) == cudaSuccess &&
+            qres == cudaDriverEntryPointSuccess)
+            fn = reinterpret_cast<EncodeTiledFn>(p);
+    }
+    return fn;
+}
+
+// 2-D row-major matrix [rows, cols] of 1- or 2-byte elements, box = 128 bytes x 128 rows, 128B swizzle.
+static int make_map(CUtensorMap* map, const void* base, bool fp8, uint64_t rows, uint64_t cols) {
+    EncodeTiledFn fn = encode_fn();
+    if (fn == nullptr) return fail(DQMOE_ERR_CUDA, __FILE__, __LINE__, "cuTensorMapEncodeTiled", "driver entry point not found");
+    const uint64_t esz = fp8 ? 1 : 2;
+    cuuint64_t gdim[2] = {cols, rows};
+    cuuint64_t gstride[1] = {cols * esz};
+    cuuint32_t box[2] = {static_cast<cuuint32_t>(kBKBytes / esz), static_cast<cuuint32_t>(kBoxRows)};
+    cuuint32_t estr[2] = {1, 1};
+    CUresult r = fn(map, fp8 ? CU_TENSOR_MAP_DATA_TYPE_UINT8 : CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2,
+                    const_cast<void*>(base), gdim, gstride, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                    CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (r != CUDA_SUCCESS)
+        return fail(DQMOE_ERR_CUDA, __FILE__, __LINE__, "cuTensorMapEncodeTiled", "CUresult %d (rows %llu cols %llu)",
+                    int(r), (unsigned long long) rows, (unsigned long long) cols);
+    return DQMOE_OK;
+}
+
+template <bool kFp8, int kMode, bool kGated>
+static int launch(const CUtensorMap& ma, const CUtensorMap& mb, const Params& p, cudaStream_t stream) {
+    auto kern = moe_GemmGrouped_GemmUniversal_tcgen05<kFp8, kMode, kGated>;
+    static bool configured = false;  // per instantiation
+    static int configured_dev = -1;
+    int dev = 0;
+    DQ_CUDA(cudaGetDevice(&dev));
+    if (!configured || configured_dev != dev) {
+        DQ_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, int(kSmemBytes)));
+        configured = true;
+        configured_dev = dev;
+    }
+    kern<<<sm_count(), kThreads, kSmemBytes, stream>>>(ma, mb, p);
+    DQ_LAUNCH_CHECK();
+    return DQMOE_OK;
+}
+
+int grouped_gemm(const void* a, const float* a_scale, const void* w, const float* w_scale, const int* offsets,
+                 const int* mtile_prefix, int n, int N, int K, int E, int quant_mode, int gated, void* out,
+                 float* out_scale, float* amax, const int* dest_to_src, cudaStream_t stream) {
+    DQ_CHECK(quant_mode == DQMOE_QUANT_NONE || quant_mode == DQMOE_QUANT_FP8_TENSOR ||
+             quant_mode == DQMOE_QUANT_FP8_CHANNEL || quant_mode == DQMOE_QUANT_FP8_BLOCK);
+    DQ_CHECK(n >= 0 && N > 0 && K > 0 && E > 0 && E <= kMaxExperts);
+    if (n == 0) return DQMOE_OK;
+    const bool fp8 = quant_mode != DQMOE_QUANT_NONE;
+    const int esz = fp8 ? 1 : 2;
+    DQ_CHECK_FMT((size_t(K) * esz) % 16 == 0, "K=%d: rows must be a multiple of 16 bytes", K);
+    DQ_CHECK_FMT(N % (gated && quant_mode == DQMOE_QUANT_FP8_BLOCK ? 16 : 8) == 0, "N=%d: output rows must be 16-byte vectors", N);
+    DQ_CHECK(is_aligned(a, 16) && is_aligned(w, 16) && is_aligned(out, 16));
+    DQ_CHECK(a != nullptr && w != nullptr && out != nullptr && offsets != nullptr && mtile_prefix != nullptr);
+    if (fp8) DQ_CHECK(a_scale != nullptr && w_scale != nullptr);
+    if (gated && quant_mode == DQMOE_QUANT_FP8_BLOCK) DQ_CHECK(out_scale != nullptr);
+    if (gated && (quant_mode == DQMOE_QUANT_FP8_TENSOR || quant_mode == DQMOE_QUANT_FP8_CHANNEL)) DQ_CHECK(amax != nullptr);
+
+    Params p;
+    p.n_rows = n;
+    p.N = N;
+    p.K = K;
+    p.E = E;
+    p.w_rows = gated ? 2 * N : N;
+    p.n_tiles = gated ? ceil_div(N, kBoxRows) : ceil_div(N, kUmmaN);
+    p.tile_w_rows = gated ? kBoxRows : kUmmaN;
+    p.box2_off = gated ? N : kBoxRows;
+    p.kb_count = ceil_div(K * esz, kBKBytes);
+    p.offsets = offsets;
+    p.mtile_prefix = mtile_prefix;
+    p.sa = a_scale;
+    p.sb = w_scale;
+    p.out = out;
+    p.out_scale = out_scale;
+    p.amax = amax;
+    p.dest_to_src = dest_to_src;
+    p.status = device_status_word();
+    if (p.status == nullptr) return DQMOE_ERR_CUDA;
+
+    CUtensorMap ma, mb;
+    int rc = make_map(&ma, a, fp8, uint64_t(n), uint64_t(K));
+    if (rc != DQMOE_OK) return rc;
+    rc = make_map(&mb, w, fp8, uint64_t(E) * p.w_rows, uint64_t(K));
+    if (rc != DQMOE_OK) return rc;
+
+#define DQ_GEMM_CASE(FP8, MODE)                                                        \
+    return gated ? launch<FP8, MODE, true>(ma, mb, p, stream) : launch<FP8, MODE, false>(ma, mb, p, stream)
+    switch (quant_mode) {
+        case DQMOE_QUANT_NONE: DQ_GEMM_CASE(false, kNone);
+        case DQMOE_QUANT_FP8_TENSOR: DQ_GEMM_CASE(true, kTensor);
+        case DQMOE_QUANT_FP8_CHANNEL: DQ_GEMM_CASE(true, kChannel);
+        default: DQ_GEMM_CASE(true, kBlock);
+    }
+#undef DQ_GEMM_CASE
+}
+
+}  // namespace gemm
+}  // namespace dq
+
+extern "C" int dqmoe_grouped_gemm(const void* a, const float* a_scale, const void* w, const float* w_scale,
+                                  const int32_t* offsets, const int32_t* mtile_prefix, int n, int N, int K, int E,
+                                  int quant_mode, int gated, void* out, float* out_scale, float* amax,
+                                  const int32_t* dest_to_src, dqmoe_stream_t stream) {
+    return dq::gemm::grouped_gemm(a, a_scale, w, w_scale, offsets, mtile_prefix, n, N, K, E, quant_mode, gated, out,
+                                  out_scale, amax, dest_to_src, static_cast<cudaStream_t>(stream));
+}

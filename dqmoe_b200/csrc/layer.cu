@@ -1,0 +1,165 @@
+// Layer orchestrator: carves the caller's workspace and enqueues the MoE layer
+// pipeline on one stream with no host synchronisation:
+//   expert sort -> row (+scale) gather -> grouped fc1 with fused SwiGLU and
+//   intermediate quantisation -> [re-quantisation pass for tensor/channel modes]
+//   -> grouped fc2 with fused dequantisation and scatter into d[T, k, H].
+// Replaces MoeFCRunner::getWorkspaceDeviceBufferSizes / runMoe / Gemm of the
+// reference (csrc/moe_kernels.h:640-711, 770-947), which runs the same steps as
+// sixteen separate launches.
+#include "common.cuh"
+
+namespace dq {
+namespace route {
+size_t sort_workspace_bytes(int n, int E);
+int route_sort(const int* ids, int n, int E, int* counts, int* offsets, int* mtile_prefix, int* dest_to_src,
+               int* src_to_dest, void* ws, size_t ws_bytes, cudaStream_t stream);
+}  // namespace route
+namespace gemm {
+int grouped_gemm(const void* a, const float* a_scale, const void* w, const float* w_scale, const int* offsets,
+                 const int* mtile_prefix, int n, int N, int K, int E, int quant_mode, int gated, void* out,
+                 float* out_scale, float* amax, const int* dest_to_src, cudaStream_t stream);
+}  // namespace gemm
+
+namespace layer {
+
+constexpr size_t kAlign = 256;  // CUDA_MEM_ALIGN of the reference (csrc/util.h:54-59)
+
+struct Layout {
+    size_t offsets, counts, mtile_prefix, sort_ws, dest_to_src, perm_a, perm_a_scale, act, act_scale, act_bf16, amax;
+    size_t total;
+    size_t sort_ws_bytes;
+    int perm_scale_cols;
+};
+
+static bool valid_mode(int q) {
+    return q == DQMOE_QUANT_NONE || q == DQMOE_QUANT_FP8_TENSOR || q == DQMOE_QUANT_FP8_CHANNEL ||
+           q == DQMOE_QUANT_FP8_BLOCK;
+}
+
+static Layout make_layout(int T, int H, int I, int E, int k, int quant_mode) {
+    Layout L{};
+    const size_t n = size_t(T) * k;
+    const size_t esz = quant_mode == DQMOE_QUANT_NONE ? 2 : 1;
+    size_t off = 0;
+    auto add = [&](size_t bytes) {
+        const size_t at = off;
+        off += align_up(bytes, kAlign);
+        return at;
+    };
+    L.offsets = add((E + 1) * sizeof(int));
+    L.counts = add(E * sizeof(int));
+    L.mtile_prefix = add((E + 1) * sizeof(int));
+    L.sort_ws_bytes = route::sort_workspace_bytes(int(n), E);
+    L.sort_ws = add(L.sort_ws_bytes);
+    L.dest_to_src = add(n * sizeof(int));
+    L.perm_a = add(n * H * esz);
+    L.perm_scale_cols = quant_mode == DQMOE_QUANT_FP8_BLOCK ? ceil_div(H, 128)
+                        : quant_mode == DQMOE_QUANT_FP8_CHANNEL ? 1 : 0;
+    L.perm_a_scale = add(n * L.perm_scale_cols * sizeof(float));
+    L.act = add(n * I * esz);
+    const size_t act_scale_elems = quant_mode == DQMOE_QUANT_FP8_BLOCK ? n * ceil_div(I, 128)
+                                   : quant_mode == DQMOE_QUANT_FP8_CHANNEL ? n
+                                   : quant_mode == DQMOE_QUANT_FP8_TENSOR ? 1 : 0;
+    L.act_scale = add(act_scale_elems * sizeof(float));
+    const bool two_pass = quant_mode == DQMOE_QUANT_FP8_TENSOR || quant_mode == DQMOE_QUANT_FP8_CHANNEL;
+    L.act_bf16 = add(two_pass ? n * I * 2 : 0);
+    L.amax = add(quant_mode == DQMOE_QUANT_FP8_CHANNEL ? n * sizeof(float)
+                 : quant_mode == DQMOE_QUANT_FP8_TENSOR ? sizeof(float) : 0);
+    L.total = off;
+    return L;
+}
+
+}  // namespace layer
+}  // namespace dq
+
+using namespace dq;
+
+extern "C" {
+
+size_t dqmoe_moe_workspace_bytes(int T, int H, int I, int E, int k, int quant_mode) {
+    if (T < 0 || H <= 0 || I <= 0 || E <= 0 || k <= 0 || !layer::valid_mode(quant_mode)) return 0;
+    return layer::make_layout(T, H, I, E, k, quant_mode).total;
+}
+
+void* dqmoe_moe_workspace_ptr(void* workspace, int which, int T, int H, int I, int E, int k, int quant_mode) {
+    if (workspace == nullptr || T < 0 || H <= 0 || I <= 0 || E <= 0 || k <= 0 || !layer::valid_mode(quant_mode))
+        return nullptr;
+    const layer::Layout L = layer::make_layout(T, H, I, E, k, quant_mode);
+    char* ws = static_cast<char*>(workspace);
+    switch (which) {
+        case 0: return ws + L.offsets;
+        case 1: return ws + L.dest_to_src;
+        case 2: return ws + L.perm_a;
+        case 3: return ws + L.perm_a_scale;
+        case 4: return ws + L.act;
+        case 5: return ws + L.act_scale;
+        case 6: return ws + L.counts;
+        case 7: return ws + L.mtile_prefix;
+        default: return nullptr;
+    }
+}
+
+int dqmoe_moe_forward(const void* a, const float* a_scale, const void* b, const float* b_scale, const void* b1,
+                      const float* b1_scale, void* d, const int32_t* m_indices, void* workspace,
+                      size_t workspace_bytes, int T, int H, int I, int E, int k, int quant_mode, int fused,
+                      dqmoe_stream_t stream_) {
+    (void) fused;
+    cudaStream_t stream = static_cast<cudaStream_t>(stream_);
+    DQ_CHECK(T >= 0 && H > 0 && I > 0 && E > 0 && k > 0);
+    DQ_CHECK_FMT(layer::valid_mode(quant_mode), "quant_mode_value=%d is not one of 0, 256, 512, 1024", quant_mode);
+    if (T == 0) return DQMOE_OK;  // as csrc/pybind11_register.h:125-126
+    DQ_CHECK(a != nullptr && b != nullptr && b1 != nullptr && d != nullptr && m_indices != nullptr);
+    DQ_CHECK_FMT(workspace != nullptr && is_aligned(workspace, layer::kAlign), "workspace pointer %p is not aligned!",
+                 workspace);
+    const bool fp8 = quant_mode != DQMOE_QUANT_NONE;
+    if (fp8) DQ_CHECK(a_scale != nullptr && b_scale != nullptr && b1_scale != nullptr);
+    const size_t esz = fp8 ? 1 : 2;
+    DQ_CHECK_FMT((H * esz) % 16 == 0 && (I * esz) % 16 == 0,
+                 "hidden_size=%d and inter_size=%d rows must be multiples of 16 bytes", H, I);
+    DQ_CHECK(int64_t(T) * k < (int64_t(1) << 31));
+    const int n = T * k;
+    const layer::Layout L = layer::make_layout(T, H, I, E, k, quant_mode);
+    if (workspace_bytes != 0 && workspace_bytes < L.total)
+        return fail(DQMOE_ERR_WORKSPACE, __FILE__, __LINE__, "workspace_bytes >= dqmoe_moe_workspace_bytes(...)",
+                    "workspace has %zu bytes, the layer needs %zu", workspace_bytes, L.total);
+
+    char* ws = static_cast<char*>(workspace);
+    int* offsets = reinterpret_cast<int*>(ws + L.offsets);
+    int* counts = reinterpret_cast<int*>(ws + L.counts);
+    int* mtile_prefix = reinterpret_cast<int*>(ws + L.mtile_prefix);
+    int* dest_to_src = reinterpret_cast<int*>(ws + L.dest_to_src);
+    void* perm_a = ws + L.perm_a;
+    float* perm_a_scale = reinterpret_cast<float*>(ws + L.perm_a_scale);
+    void* act = ws + L.act;
+    float* act_scale = reinterpret_cast<float*>(ws + L.act_scale);
+    void* act_bf16 = ws + L.act_bf16;
+    float* amax = reinterpret_cast<float*>(ws + L.amax);
+
+    int rc = route::route_sort(m_indices, n, E, counts, offsets, mtile_prefix, dest_to_src, nullptr, ws + L.sort_ws,
+                               L.sort_ws_bytes, stream);
+    if (rc != DQMOE_OK) return rc;
+
+    rc = dqmoe_permute_rows(a, size_t(H) * esz, k, dest_to_src, n, perm_a, L.perm_scale_cols ? a_scale : nullptr,
+                            L.perm_scale_cols, L.perm_scale_cols ? perm_a_scale : nullptr, stream);
+    if (rc != DQMOE_OK) return rc;
+
+    const float* sa1 = quant_mode == DQMOE_QUANT_FP8_TENSOR ? a_scale : perm_a_scale;
+    const bool two_pass = quant_mode == DQMOE_QUANT_FP8_TENSOR || quant_mode == DQMOE_QUANT_FP8_CHANNEL;
+    if (two_pass) {
+        const size_t amax_bytes = quant_mode == DQMOE_QUANT_FP8_CHANNEL ? size_t(n) * sizeof(float) : sizeof(float);
+        DQ_CUDA(cudaMemsetAsync(amax, 0, amax_bytes, stream));
+    }
+    rc = gemm::grouped_gemm(perm_a, sa1, b, b_scale, offsets, mtile_prefix, n, I, H, E, quant_mode, 1,
+                            two_pass ? act_bf16 : act, act_scale, amax, nullptr, stream);
+    if (rc != DQMOE_OK) return rc;
+    if (two_pass) {
+        rc = dqmoe_requant_from_amax(act_bf16, n, I, amax, quant_mode == DQMOE_QUANT_FP8_CHANNEL ? 1 : 0, act,
+                                     act_scale, stream);
+        if (rc != DQMOE_OK) return rc;
+    }
+    rc = gemm::grouped_gemm(act, act_scale, b1, b1_scale, offsets, mtile_prefix, n, H, I, E, quant_mode, 0, d, nullptr,
+                            nullptr, dest_to_src, stream);
+    return rc;
+}
+
+}  // extern "C"

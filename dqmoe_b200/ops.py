@@ -1,0 +1,260 @@
+"""Torch-tensor front end of the C ABI: every function takes CUDA tensors,
+passes their device pointers to libdqmoe_b200.so on the current torch stream and
+returns without synchronising. Torch is used for memory and streams only.
+
+Names follow the reference's operator surface where it has one
+(csrc/pybind11_register.h:153-163) and the helper functions of its tests
+(test/util.py:18-68) for the quantisers.
+"""
+from __future__ import annotations
+
+import ctypes
+from typing import Optional, Tuple
+
+import torch
+
+from . import _lib
+
+QUANT_NONE = 0
+QUANT_FP8_TENSOR = 256
+QUANT_FP8_CHANNEL = 512
+QUANT_FP8_BLOCK = 1024
+SCORE_SOFTMAX = 0
+SCORE_SIGMOID = 1
+
+FP8 = torch.float8_e4m3fn
+
+
+def _p(t: Optional[torch.Tensor]):
+    return None if t is None else ctypes.c_void_p(t.data_ptr())
+
+
+def _stream(device) -> ctypes.c_void_p:
+    return ctypes.c_void_p(torch.cuda.current_stream(device).cuda_stream)
+
+
+def _cuda(t: torch.Tensor, name: str) -> torch.Tensor:
+    if not t.is_cuda:
+        raise RuntimeError(f"[ASSERT FAILED] ops.py  Condition: {name}.is_cuda  Info: dqmoe_b200 has no CPU path")
+    if not t.is_contiguous():
+        raise RuntimeError(f"[ASSERT FAILED] ops.py  Condition: {name}.is_contiguous()")
+    return t
+
+
+def device_status() -> int:
+    """Synchronise the current device and return (then clear) the kernels' sticky status word."""
+    code = ctypes.c_int(0)
+    _lib.check(_lib.load().dqmoe_device_status(ctypes.byref(code)))
+    return code.value
+
+
+# ---------------------------------------------------------------------- layer
+
+def moe_workspace_bytes(T: int, H: int, I: int, E: int, k: int, quant_mode: int) -> int:
+    return int(_lib.load().dqmoe_moe_workspace_bytes(T, H, I, E, k, quant_mode))
+
+
+def moe_forward(a, a_scale, b, b_scale, b1, b1_scale, d, m_indices, workspace, quant_mode: int,
+                fused: bool = True) -> None:
+    """One MoE layer into d[T, k, H]; see dqmoe_moe_forward in include/dqmoe.h."""
+    lib = _lib.load()
+    T, H = a.shape
+    E, I2, _ = b.shape
+    I = b1.shape[2]
+    k = d.shape[1]
+    for name, t in (("a", a), ("b", b), ("b1", b1), ("d", d), ("m_indices", m_indices), ("workspace", workspace)):
+        _cuda(t, name)
+    with torch.cuda.device(a.device):
+        _lib.check(lib.dqmoe_moe_forward(
+            _p(a), _p(a_scale), _p(b), _p(b_scale), _p(b1), _p(b1_scale), _p(d), _p(m_indices),
+            _p(workspace), workspace.numel() * workspace.element_size(), T, H, I, E, k,
+            int(quant_mode), int(bool(fused)), _stream(a.device)))
+
+
+# ---------------------------------------------------------------------- routing
+
+def route_topk(logits: torch.Tensor, k: int, scoring: str = "softmax") -> Tuple[torch.Tensor, torch.Tensor]:
+    """(indices int32 [T, k], weights fp32 [T, k]) from fp32 logits [T, E]."""
+    _cuda(logits, "logits")
+    if logits.dtype != torch.float32 or logits.dim() != 2:
+        raise RuntimeError("[ASSERT FAILED] ops.py  Condition: logits is fp32 [T, E]")
+    T, E = logits.shape
+    mode = {"softmax": SCORE_SOFTMAX, "sigmoid": SCORE_SIGMOID}[scoring]
+    idx = torch.empty((T, k), dtype=torch.int32, device=logits.device)
+    w = torch.empty((T, k), dtype=torch.float32, device=logits.device)
+    with torch.cuda.device(logits.device):
+        _lib.check(_lib.load().dqmoe_route_topk(_p(logits), T, E, k, mode, _p(idx), _p(w), _stream(logits.device)))
+    return idx, w
+
+
+def route_sort(m_indices: torch.Tensor, E: int):
+    """(counts[E], offsets[E+1], dest_to_src[n], src_to_dest[n]) int32 for m_indices [T, k]."""
+    _cuda(m_indices, "m_indices")
+    if m_indices.dtype != torch.int32:
+        raise RuntimeError("[ASSERT FAILED] ops.py  Condition: m_indices.scalar_type() == torch::kInt")
+    lib = _lib.load()
+    n = m_indices.numel()
+    dev = m_indices.device
+    counts = torch.empty(E, dtype=torch.int32, device=dev)
+    offsets = torch.empty(E + 1, dtype=torch.int32, device=dev)
+    d2s = torch.empty(n, dtype=torch.int32, device=dev)
+    s2d = torch.empty(n, dtype=torch.int32, device=dev)
+    ws_bytes = int(lib.dqmoe_route_sort_workspace_bytes(n, E))
+    ws = torch.empty(max(ws_bytes, 256), dtype=torch.uint8, device=dev)
+    with torch.cuda.device(dev):
+        _lib.check(lib.dqmoe_route_sort(_p(m_indices), n, E, _p(counts), _p(offsets), _p(d2s), _p(s2d),
+                                        _p(ws), ws_bytes, _stream(dev)))
+    return counts, offsets, d2s, s2d
+
+
+def mtile_prefix(offsets: torch.Tensor) -> torch.Tensor:
+    _cuda(offsets, "offsets")
+    E = offsets.numel() - 1
+    out = torch.empty(E + 1, dtype=torch.int32, device=offsets.device)
+    with torch.cuda.device(offsets.device):
+        _lib.check(_lib.load().dqmoe_mtile_prefix(_p(offsets), E, _p(out), _stream(offsets.device)))
+    return out
+
+
+# ---------------------------------------------------------------------- permute / finalize
+
+def moe_permute(a: torch.Tensor, dest_to_src: torch.Tensor, k: int,
+                scale: Optional[torch.Tensor] = None):
+    """Expert-order gather of rows of a [T, H] (and of a per-row scale matrix [T, C])."""
+    _cuda(a, "a")
+    _cuda(dest_to_src, "dest_to_src")
+    n = dest_to_src.numel()
+    H = a.shape[1]
+    out = torch.empty((n, H), dtype=a.dtype, device=a.device)
+    cols = 0
+    out_scale = None
+    if scale is not None:
+        _cuda(scale, "scale")
+        cols = scale.shape[1] if scale.dim() == 2 else 1
+        out_scale = torch.empty((n, cols), dtype=torch.float32, device=a.device)
+    with torch.cuda.device(a.device):
+        _lib.check(_lib.load().dqmoe_permute_rows(_p(a), H * a.element_size(), k, _p(dest_to_src), n, _p(out),
+                                                  _p(scale), cols, _p(out_scale), _stream(a.device)))
+    return (out, out_scale) if scale is not None else out
+
+
+def moe_permute_quant_block(x: torch.Tensor, dest_to_src: torch.Tensor, k: int):
+    """Gather fused with 1x128 FP8 quantisation of bf16 activations x [T, H]."""
+    _cuda(x, "x")
+    _cuda(dest_to_src, "dest_to_src")
+    assert x.dtype == torch.bfloat16
+    n = dest_to_src.numel()
+    H = x.shape[1]
+    q = torch.empty((n, H), dtype=FP8, device=x.device)
+    s = torch.empty((n, (H + 127) // 128), dtype=torch.float32, device=x.device)
+    with torch.cuda.device(x.device):
+        _lib.check(_lib.load().dqmoe_permute_quant_block_1x128(_p(x), H, k, _p(dest_to_src), n, _p(q), _p(s),
+                                                               _stream(x.device)))
+    return q, s
+
+
+def finalize_scatter(rows: torch.Tensor, dest_to_src: torch.Tensor, d: torch.Tensor) -> None:
+    """d.view(n, H)[dest_to_src[r]] = rows[r]."""
+    _cuda(rows, "rows")
+    _cuda(d, "d")
+    n = dest_to_src.numel()
+    with torch.cuda.device(rows.device):
+        _lib.check(_lib.load().dqmoe_finalize_scatter(_p(rows), rows.shape[1] * rows.element_size(),
+                                                      _p(dest_to_src), n, _p(d), _stream(rows.device)))
+
+
+def finalize_weighted(d: torch.Tensor, weights: torch.Tensor) -> torch.Tensor:
+    """out[t] = sum_j weights[t, j] * d[t, j]  (bf16 [T, k, H] -> bf16 [T, H])."""
+    _cuda(d, "d")
+    _cuda(weights, "weights")
+    assert d.dtype == torch.bfloat16 and weights.dtype == torch.float32
+    T, k, H = d.shape
+    out = torch.empty((T, H), dtype=torch.bfloat16, device=d.device)
+    with torch.cuda.device(d.device):
+        _lib.check(_lib.load().dqmoe_finalize_weighted(_p(d), _p(weights), _p(out), T, k, H, _stream(d.device)))
+    return out
+
+
+# ---------------------------------------------------------------------- quantisers (test/util.py:18-68)
+
+def per_token_cast_to_fp8(x: torch.Tensor):
+    _cuda(x, "x")
+    assert x.dim() == 2 and x.dtype == torch.bfloat16
+    m, n = x.shape
+    q = torch.empty((m, n), dtype=FP8, device=x.device)
+    s = torch.empty((m, 1), dtype=torch.float32, device=x.device)
+    with torch.cuda.device(x.device):
+        _lib.check(_lib.load().dqmoe_quant_fp8_rowwise(_p(x), m, n, _p(q), _p(s), _stream(x.device)))
+    return q, s
+
+
+def per_channel_cast_to_fp8(x: torch.Tensor):
+    _cuda(x, "x")
+    assert x.dim() == 3 and x.dtype == torch.bfloat16
+    e, m, n = x.shape
+    q = torch.empty((e, m, n), dtype=FP8, device=x.device)
+    s = torch.empty((e, m, 1), dtype=torch.float32, device=x.device)
+    with torch.cuda.device(x.device):
+        _lib.check(_lib.load().dqmoe_quant_fp8_rowwise(_p(x), e * m, n, _p(q), _p(s), _stream(x.device)))
+    return q, s
+
+
+def per_token_block_cast_to_fp8(x: torch.Tensor):
+    _cuda(x, "x")
+    assert x.dim() == 2 and x.dtype == torch.bfloat16
+    m, n = x.shape
+    q = torch.empty((m, n), dtype=FP8, device=x.device)
+    s = torch.empty((m, (n + 127) // 128), dtype=torch.float32, device=x.device)
+    with torch.cuda.device(x.device):
+        _lib.check(_lib.load().dqmoe_quant_fp8_block_1x128(_p(x), m, n, _p(q), _p(s), _stream(x.device)))
+    return q, s
+
+
+def per_block_cast_to_fp8(x: torch.Tensor):
+    _cuda(x, "x")
+    assert x.dtype == torch.bfloat16
+    x3 = x[None] if x.dim() == 2 else x
+    e, m, n = x3.shape
+    q = torch.empty((e, m, n), dtype=FP8, device=x.device)
+    s = torch.empty((e, (m + 127) // 128, (n + 127) // 128), dtype=torch.float32, device=x.device)
+    with torch.cuda.device(x.device):
+        _lib.check(_lib.load().dqmoe_quant_fp8_block_128x128(_p(x3), e, m, n, _p(q), _p(s), _stream(x.device)))
+    return q, s
+
+
+def per_tensor_cast_to_fp8(x: torch.Tensor, per_expert: bool = False):
+    """One scale for the tensor, or one per leading index when per_expert."""
+    _cuda(x, "x")
+    assert x.dtype == torch.bfloat16
+    e = x.shape[0] if per_expert else 1
+    numel_per = x.numel() // e
+    q = torch.empty(x.shape, dtype=FP8, device=x.device)
+    s = torch.empty(e, dtype=torch.float32, device=x.device)
+    scratch = torch.empty(e, dtype=torch.float32, device=x.device)
+    with torch.cuda.device(x.device):
+        _lib.check(_lib.load().dqmoe_quant_fp8_tensor(_p(x), e, numel_per, _p(q), _p(s), _p(scratch),
+                                                      _stream(x.device)))
+    return q, s
+
+
+# ---------------------------------------------------------------------- grouped GEMM
+
+def grouped_gemm(a, a_scale, w, w_scale, offsets, mtile_pref, N: int, quant_mode: int, gated: bool,
+                 out, out_scale=None, amax=None, dest_to_src=None) -> None:
+    """The MoeGemmRunner::runGemm step with fused epilogue; see dqmoe_grouped_gemm."""
+    n, K = a.shape
+    E = w.shape[0]
+    with torch.cuda.device(a.device):
+        _lib.check(_lib.load().dqmoe_grouped_gemm(
+            _p(a), _p(a_scale), _p(w), _p(w_scale), _p(offsets), _p(mtile_pref), n, N, K, E, int(quant_mode),
+            int(bool(gated)), _p(out), _p(out_scale), _p(amax), _p(dest_to_src), _stream(a.device)))
+
+
+def requant_from_amax(act: torch.Tensor, amax: torch.Tensor, per_row: bool):
+    n, I = act.shape
+    q = torch.empty((n, I), dtype=FP8, device=act.device)
+    s = torch.empty(n if per_row else 1, dtype=torch.float32, device=act.device)
+    with torch.cuda.device(act.device):
+        _lib.check(_lib.load().dqmoe_requant_from_amax(_p(act), n, I, _p(amax), int(per_row), _p(q), _p(s),
+                                                       _stream(act.device)))
+    return q, s

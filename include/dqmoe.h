@@ -1,0 +1,231 @@
+/*
+ * dqmoe.h — C ABI of the B200 (sm_100a) dynamic-quantization MoE layer library.
+ *
+ * Every entry point takes plain device pointers and sizes, enqueues its kernels
+ * on the CUDA stream it is given (a cudaStream_t passed as void*), never
+ * synchronises with the host and never allocates device memory: the caller
+ * owns all tensors and passes one workspace buffer, exactly as the reference
+ * operator does (csrc/pybind11_register.h:99-151).
+ *
+ * Return value: 0 on success, a DQMOE_ERR_* code otherwise; the message of the
+ * last failure on the calling thread is returned by dqmoe_last_error() and has
+ * the reference's "[ASSERT FAILED] file:line  Condition: ..." form
+ * (csrc/util.h:143-152) for argument checks.
+ *
+ * Layout conventions (all row-major, innermost dimension contiguous):
+ *   a        [T, H]        activations          (e4m3 bytes or bf16)
+ *   b        [E, 2I, H]    fc1 weights, rows 0..I-1 of an expert are the gate
+ *                          half, rows I..2I-1 the value half
+ *   b1       [E, H, I]     fc2 weights
+ *   d        [T, k, H]     bf16 output, slot j of token t holds the output of
+ *                          expert m_indices[t, j] (unweighted)
+ *   m_indices[T, k]        int32 expert ids; an id outside [0, E) drops the row
+ * Scale tensors are fp32; their shapes depend on the quantisation mode:
+ *   tensor  (256):  a_scale [1],             b_scale [E],                    b1_scale [E]
+ *   channel (512):  a_scale [T],             b_scale [E, 2I],                b1_scale [E, H]
+ *   block   (1024): a_scale [T, ceil(H/128)], b_scale [E, ceil(2I/128), ceil(H/128)],
+ *                   b1_scale [E, ceil(H/128), ceil(I/128)]
+ */
+#ifndef DQMOE_H_
+#define DQMOE_H_
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define DQMOE_ABI_VERSION 1
+
+/* error codes */
+#define DQMOE_OK 0
+#define DQMOE_ERR_INVALID 1   /* argument check failed (shape, alignment, mode) */
+#define DQMOE_ERR_CUDA 2      /* a CUDA runtime/driver call failed */
+#define DQMOE_ERR_WORKSPACE 3 /* workspace too small or misaligned */
+#define DQMOE_ERR_DEVICE 4    /* a kernel's bounded wait gave up (see dqmoe_device_status) */
+
+/* quantisation modes: the reference's QuantMode bit values (csrc/quantization.h:10-28) */
+#define DQMOE_QUANT_NONE 0          /* bf16 activations and weights */
+#define DQMOE_QUANT_FP8_TENSOR 256  /* FP8_QDQ      : per-tensor act scale, per-expert weight scale */
+#define DQMOE_QUANT_FP8_CHANNEL 512 /* FP8_ROWWISE  : per-token act scale, per-output-channel weight scale */
+#define DQMOE_QUANT_FP8_BLOCK 1024  /* FP8_BLOCKWISE: 1x128 act scales, 128x128 weight scales */
+
+/* router scoring functions */
+#define DQMOE_SCORE_SOFTMAX 0 /* softmax over experts, top-k, renormalised to sum 1 */
+#define DQMOE_SCORE_SIGMOID 1 /* sigmoid per expert, top-k, normalised by their sum */
+
+typedef void* dqmoe_stream_t; /* a cudaStream_t */
+
+/* Message of the last error raised on the calling thread ("" if none). */
+const char* dqmoe_last_error(void);
+int dqmoe_abi_version(void);
+
+/*
+ * Sticky device status. Kernels that wait on barriers bound every wait; one that
+ * gives up writes a code into a host-mapped word instead of trapping. This call
+ * synchronises the current device, returns the word through *code (0 = clean)
+ * and clears it. No counterpart in the reference, whose CUDA_CHECK exits the
+ * process (csrc/util.h:61-80).
+ */
+int dqmoe_device_status(int* code);
+
+/* ------------------------------------------------------------------ layer */
+
+/*
+ * Workspace bytes needed by dqmoe_moe_forward for a problem size.
+ * Replaces MoeFCRunner::getWorkspaceSize (csrc/moe_kernels.h:713-722).
+ */
+size_t dqmoe_moe_workspace_bytes(int T, int H, int I, int E, int k, int quant_mode);
+
+/*
+ * One MoE layer: expert sort -> row gather -> grouped fc1 + SwiGLU (+ dynamic
+ * FP8 re-quantisation of the intermediate) -> grouped fc2 -> scatter into d.
+ * Replaces m_grouped_moe_nt_contiguous<T,W,O> / MoeFCRunner::runMoe
+ * (csrc/pybind11_register.h:99-151, csrc/moe_kernels.h:770-892).
+ * quant_mode selects the element type: NONE = bf16 data (scale pointers are
+ * ignored and may be anything), the FP8 modes = e4m3 data.
+ * `fused` is accepted for signature compatibility; the dequantisation is always
+ * fused into the GEMM epilogue (csrc/moe_gemm_template.h:1111-1118 selects
+ * between two kernels with equal results).
+ * workspace must be 256-byte aligned (checked, as pybind11_register.h:141-142)
+ * and at least dqmoe_moe_workspace_bytes() long (checked; pass
+ * workspace_bytes = 0 to skip the size check as the reference does).
+ */
+int dqmoe_moe_forward(const void* a, const float* a_scale, const void* b, const float* b_scale,
+                      const void* b1, const float* b1_scale, void* d, const int32_t* m_indices,
+                      void* workspace, size_t workspace_bytes, int T, int H, int I, int E, int k,
+                      int quant_mode, int fused, dqmoe_stream_t stream);
+
+/*
+ * Addresses of intermediates inside a workspace laid out by dqmoe_moe_forward
+ * for the same problem size (debug/testing aid; the reference has the unused
+ * extractIntermediateResultsforTorch, csrc/moe_kernels.h:739-767).
+ * which: 0 offsets[E+1] int32, 1 dest_to_src[n] int32, 2 permuted activations,
+ *        3 permuted activation scales, 4 intermediate (fc2 input),
+ *        5 intermediate scales, 6 counts[E] int32, 7 m-tile prefix[E+1] int32.
+ * Returns NULL for an unknown id.
+ */
+void* dqmoe_moe_workspace_ptr(void* workspace, int which, int T, int H, int I, int E, int k,
+                              int quant_mode);
+
+/* ------------------------------------------------------------------ routing */
+
+/*
+ * Top-k router over fp32 logits [T, E]: indices [T, k] int32 in descending score
+ * order (ties: lower expert id first), weights [T, k] fp32 normalised to sum 1.
+ * The reference has no router kernel; its tests use torch.randn + torch.topk
+ * (test/torch_test.py:78-80). E <= 1024, k <= 32.
+ */
+int dqmoe_route_topk(const float* logits, int T, int E, int k, int scoring, int32_t* indices,
+                     float* weights, dqmoe_stream_t stream);
+
+/*
+ * Expert sort of n = T*k expanded rows: counts[E], exclusive offsets[E+1], the
+ * permutation dest_to_src[n] (dest row -> t*k+j) and, if not NULL, its inverse
+ * src_to_dest[n]. Order inside an expert is ascending source row (stable), which
+ * is the order torch.where gives (test/util.py:80). Rows whose id is outside
+ * [0, E) are dropped: src_to_dest = -1 and the tail of dest_to_src is -1.
+ * Replaces cubHistogramAndScan + GetGroupIndex (csrc/moe_kernels.h:108-127,
+ * 452-471), whose atomic slot assignment is not deterministic.
+ */
+size_t dqmoe_route_sort_workspace_bytes(int n, int E);
+int dqmoe_route_sort(const int32_t* expert_ids, int n, int E, int32_t* counts, int32_t* offsets,
+                     int32_t* dest_to_src, int32_t* src_to_dest, void* workspace,
+                     size_t workspace_bytes, dqmoe_stream_t stream);
+
+/* ------------------------------------------------------------------ permute / finalize */
+
+/*
+ * Row gather dst[r, :] = src[dest_to_src[r] / k, :] for r < n (rows with a
+ * negative map entry are skipped), row_bytes a multiple of 16; optionally the
+ * same gather over an fp32 scale matrix with scale_cols columns (0 = none).
+ * Replaces expandInputRowsGatherKernel and expandInputScale{,Block}GatherKernel
+ * (csrc/moe_kernels.h:487-576).
+ */
+int dqmoe_permute_rows(const void* src, size_t row_bytes, int k, const int32_t* dest_to_src, int n,
+                       void* dst, const float* src_scale, int scale_cols, float* dst_scale,
+                       dqmoe_stream_t stream);
+
+/*
+ * Fused gather + dynamic 1x128 FP8 quantisation of bf16 activations:
+ * q[r, :], scale[r, :] = quant_1x128(x[dest_to_src[r] / k, :]).
+ * The reference quantises in torch (test/util.py:34-45) and gathers afterwards.
+ */
+int dqmoe_permute_quant_block_1x128(const void* x_bf16, int H, int k, const int32_t* dest_to_src,
+                                    int n, void* q, float* scale, dqmoe_stream_t stream);
+
+/*
+ * Scatter of permuted rows back to slot order: d[dest_to_src[r], :] = rows[r, :].
+ * Replaces finalizeScatterKernel (csrc/moe_kernels.h:581-620).
+ */
+int dqmoe_finalize_scatter(const void* rows, size_t row_bytes, const int32_t* dest_to_src, int n,
+                           void* d, dqmoe_stream_t stream);
+
+/*
+ * Weighted combine out[t, :] = sum_j weights[t, j] * d[t, j, :] (bf16 in, fp32
+ * accumulate in slot order, bf16 out). Slots whose weight is exactly 0 are not
+ * read. No counterpart in the reference (its output stays [T, k, H]).
+ */
+int dqmoe_finalize_weighted(const void* d_bf16, const float* weights, void* out_bf16, int T, int k,
+                            int H, dqmoe_stream_t stream);
+
+/* ------------------------------------------------------------------ quantisers */
+
+/*
+ * Dynamic FP8 E4M3 quantisers over bf16 input, bit-exact to the torch
+ * expressions of the reference: sf = max(amax, 1e-4) / 448, q = e4m3(x * (1 / sf))
+ * with IEEE fp32 division and round-to-nearest-even (test/util.py:18-68).
+ */
+/* per row of a [rows, cols] matrix: per_token_cast_to_fp8 / per_channel_cast_to_fp8 (test/util.py:18-30) */
+int dqmoe_quant_fp8_rowwise(const void* x_bf16, int64_t rows, int cols, void* q, float* scale,
+                            dqmoe_stream_t stream);
+/* per 1x128 group of a row: per_token_block_cast_to_fp8 (test/util.py:34-45); scale [rows, ceil(cols/128)] */
+int dqmoe_quant_fp8_block_1x128(const void* x_bf16, int64_t rows, int cols, void* q, float* scale,
+                                dqmoe_stream_t stream);
+/* per 128x128 block of each of e matrices [rows, cols]: per_block_cast_to_fp8 (test/util.py:48-68) */
+int dqmoe_quant_fp8_block_128x128(const void* w_bf16, int e, int rows, int cols, void* q,
+                                  float* scale, dqmoe_stream_t stream);
+/*
+ * One scale per tensor (or per expert when e > 1: x is [e, numel_per] and scale [e]).
+ * amax_scratch is e floats of caller-owned device memory, overwritten.
+ * The reference has this mode only for the intermediate (csrc/moe_kernels.h:136-221).
+ */
+int dqmoe_quant_fp8_tensor(const void* x_bf16, int e, int64_t numel_per, void* q, float* scale,
+                           float* amax_scratch, dqmoe_stream_t stream);
+
+/* ------------------------------------------------------------------ grouped GEMM */
+
+/*
+ * Grouped GEMM over expert-sorted rows, the MoeGemmRunner::runGemm step
+ * (csrc/moe_gemm_template.h:43-70, 1099-1103) with the epilogues fused:
+ *   stage 1 (gated != 0): act = silu(A_e B_e[0:I]^T) * (A_e B_e[I:2I]^T), written as bf16
+ *       (NONE), as bf16 plus per-row/per-tensor amax (CHANNEL/TENSOR), or as
+ *       e4m3 with 1x128 scales (BLOCK);
+ *   stage 2 (gated == 0): out[map[r], :] = dequant(A_e B_e^T) as bf16, map = dest_to_src
+ *       or identity when NULL.
+ * a: [n, K] expert-sorted rows; w: [E, gated ? 2*N : N, K]; offsets [E+1] and
+ * mtile_prefix [E+1] (cumulative ceil(M_e/128)) as produced by dqmoe_route_sort's
+ * workspace. N is the number of output columns.
+ */
+int dqmoe_grouped_gemm(const void* a, const float* a_scale, const void* w, const float* w_scale,
+                       const int32_t* offsets, const int32_t* mtile_prefix, int n, int N, int K,
+                       int E, int quant_mode, int gated, void* out, float* out_scale, float* amax,
+                       const int32_t* dest_to_src, dqmoe_stream_t stream);
+
+/* cumulative 128-row tile counts per expert from offsets[E+1] (device to device) */
+int dqmoe_mtile_prefix(const int32_t* offsets, int E, int32_t* mtile_prefix, dqmoe_stream_t stream);
+
+/*
+ * Re-quantise the bf16 intermediate [n, I] written by a TENSOR/CHANNEL stage-1
+ * GEMM using the amax it accumulated: per row (CHANNEL: scale [n]) or one value
+ * (TENSOR: scale [1]). Replaces perTokendynamicFp8QuantKernel /
+ * perTensorDynamicFp8QuantKernel (csrc/moe_kernels.h:136-282).
+ */
+int dqmoe_requant_from_amax(const void* act_bf16, int64_t n, int I, const float* amax,
+                            int per_row, void* q, float* scale, dqmoe_stream_t stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* DQMOE_H_ */
