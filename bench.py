@@ -1,0 +1,387 @@
+"""Benchmark of the MoE-layer hot path.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--workload c2|c3|c4|c5] [--impl ours|reference]
+
+One step = one MoE layer call (expert sort, gather, grouped fc1 + SwiGLU +
+re-quantisation, grouped fc2 + scatter) over one batch of synthetic, seeded
+inputs. Prints ONE JSON line: whole-job FP8 TFLOP/s (`value`), the same through
+the drop-in `moe_test` call with host buffers (`e2e`), the roofline of the
+dominant kernel (the fc1 grouped GEMM) and the CPU oracle timed on a bounded
+sample (`cpu_baseline`).
+
+With --gpus N > 1 (launched by torch.distributed.run) the layer runs
+expert-parallel: every rank keeps T tokens (weak scaling) and E/N experts, rows
+travel by all-to-all.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import statistics
+import subprocess
+import sys
+import threading
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+for p in (ROOT, os.path.join(ROOT, "dqmoe_b200", "dropin")):
+    if p not in sys.path:
+        sys.path.insert(0, p)
+
+import torch  # noqa: E402
+
+WORKLOADS = {
+    # name: T, H, I, E, k, quant mode, scoring
+    "c1": dict(T=64, H=1024, I=2048, E=8, k=2, mode=256, scoring="softmax",
+               desc="CPU-size layer, per-tensor FP8"),
+    "c2": dict(T=4096, H=4096, I=14336, E=8, k=2, mode=1024, scoring="softmax",
+               desc="Mixtral-8x7B-shape prefill layer, 1x128/128x128 block FP8"),
+    "c3": dict(T=8192, H=7168, I=2048, E=256, k=8, mode=1024, scoring="sigmoid",
+               desc="DeepSeek-V3-shape routed-expert layer, block FP8"),
+    "c4": dict(T=16384, H=2048, I=768, E=128, k=8, mode=512, scoring="softmax",
+               desc="Qwen-MoE-shape channel-wise layer, Zipf(1.1) expert bias"),
+}
+MODE_NAME = {0: "bf16", 256: "fp8-tensor", 512: "fp8-channel", 1024: "fp8-block"}
+
+
+def peaks():
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(path):
+        with open(path) as f:
+            p = json.load(f)
+        return dict(hbm_gbs=p["hbm_gbs"], bf16=p["bf16_tflops"], bf16_sustained=p["bf16_tflops_sustained"],
+                    source="measured")
+    return dict(hbm_gbs=6650.0, bf16=1590.0, bf16_sustained=1400.0, source="fallback")
+
+
+class ClockSampler:
+    """Samples SM clocks and throttle reasons with nvidia-smi while the timed region runs."""
+
+    FIELDS = ("clocks.sm,clocks.max.sm,clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+              "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, index: int):
+        self.index = index
+        self.proc = None
+        self.lines = []
+
+    def start(self):
+        try:
+            self.proc = subprocess.Popen(
+                ["nvidia-smi", "-i", str(self.index), f"--query-gpu={self.FIELDS}", "--format=csv,noheader,nounits",
+                 "-lms", "100"], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+            threading.Thread(target=self._pump, daemon=True).start()
+        except OSError:
+            self.proc = None
+
+    def _pump(self):
+        for line in self.proc.stdout:
+            self.lines.append(line.strip())
+
+    def stop(self):
+        if self.proc is None:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        time.sleep(0.15)
+        self.proc.terminate()
+        try:
+            self.proc.wait(timeout=5)
+        except subprocess.TimeoutExpired:
+            self.proc.kill()
+        mhz, mx, reasons = [], [], set()
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        for ln in self.lines:
+            parts = [x.strip() for x in ln.split(",")]
+            if len(parts) < 6:
+                continue
+            try:
+                mhz.append(float(parts[0]))
+                mx.append(float(parts[1]))
+            except ValueError:
+                continue
+            for nm, val in zip(names, parts[2:6]):
+                if val.lower().startswith("active"):
+                    reasons.add(nm)
+        return {"sm_mhz": statistics.median(mhz) if mhz else None, "sm_max_mhz": max(mx) if mx else None,
+                "samples": len(mhz), "reasons": sorted(reasons)}
+
+
+def synth_inputs(wl, seed, device, T=None):
+    """Seeded synthetic inputs of a workload on `device` (bf16 activations N(0,1), weights N(0,0.02))."""
+    T = wl["T"] if T is None else T
+    g = torch.Generator(device=device).manual_seed(seed)
+    H, I, E, k = wl["H"], wl["I"], wl["E"], wl["k"]
+    x = torch.randn(T, H, generator=g, device=device, dtype=torch.float32).to(torch.bfloat16)
+    logits = torch.randn(T, E, generator=g, device=device, dtype=torch.float32)
+    if wl.get("desc", "").find("Zipf") >= 0:
+        perm = torch.randperm(E, generator=g, device=device)
+        bias = -1.1 * torch.log(torch.arange(1, E + 1, device=device, dtype=torch.float32))
+        logits = logits + bias[perm]
+    return x, logits
+
+
+def synth_weights(wl, seed, device, experts=None):
+    g = torch.Generator(device=device).manual_seed(seed + 1000)
+    H, I = wl["H"], wl["I"]
+    E = wl["E"] if experts is None else experts
+    b = torch.empty(E, 2 * I, H, device=device, dtype=torch.bfloat16)
+    b1 = torch.empty(E, H, I, device=device, dtype=torch.bfloat16)
+    for e in range(E):  # per expert to bound the fp32 temporaries
+        b[e] = (torch.randn(2 * I, H, generator=g, device=device) * 0.02).to(torch.bfloat16)
+        b1[e] = (torch.randn(H, I, generator=g, device=device) * 0.02).to(torch.bfloat16)
+    return b, b1
+
+
+def quantize_gpu(ops, x, b, b1, mode):
+    if mode == 1024:
+        return (*ops.per_token_block_cast_to_fp8(x), *ops.per_block_cast_to_fp8(b), *ops.per_block_cast_to_fp8(b1))
+    if mode == 512:
+        aq, as_ = ops.per_token_cast_to_fp8(x)
+        bq, bs = ops.per_channel_cast_to_fp8(b)
+        b1q, b1s = ops.per_channel_cast_to_fp8(b1)
+        return aq, as_.view(-1), bq, bs.view(b.shape[0], -1), b1q, b1s.view(b1.shape[0], -1)
+    if mode == 256:
+        return (*ops.per_tensor_cast_to_fp8(x), *ops.per_tensor_cast_to_fp8(b, per_expert=True),
+                *ops.per_tensor_cast_to_fp8(b1, per_expert=True))
+    return x, None, b, None, b1, None
+
+
+def launches_per_step(n, mode):
+    sort = 1 if n <= 2048 else 3
+    return sort + 1 + 1 + (1 if mode in (256, 512) else 0) + 1
+
+
+def cpu_baseline(wl, sample_tokens, seed=0, threads=None):
+    """The oracle (torch on the host cores) on a bounded sample of the workload."""
+    from oracle import moe_oracle as orc
+    if threads:
+        torch.set_num_threads(threads)
+    T = min(sample_tokens, wl["T"])
+    H, I, E, k, mode = wl["H"], wl["I"], wl["E"], wl["k"], wl["mode"]
+    x, logits = synth_inputs(wl, seed, "cpu", T=T)
+    idx, _ = orc.route_topk(logits, k, wl["scoring"])
+    # the sample touches only the experts its tokens hit; weights are made for those
+    b, b1 = synth_weights(wl, seed, "cpu")
+    qs = orc.quantize_inputs(x, b, b1, mode) if mode else None
+    t0 = time.perf_counter()
+    if mode:
+        orc.moe_layer_fp8(*qs, idx, E, mode)
+    else:
+        orc.moe_layer_bf16(x, b, b1, idx, E)
+    dt = time.perf_counter() - t0
+    flops = 6.0 * T * k * H * I
+    return dict(value=flops / dt / 1e12, unit="TFLOP/s", cores=torch.get_num_threads(), kind="port",
+                sample=f"{T} of {wl['T']} tokens, all {E} experts, one layer call ({dt:.2f} s)",
+                tokens_per_s=T / dt)
+
+
+def run_reference(args, wl, rank):
+    """--impl reference: the reference's CPU implementation of the path (the oracle port of its torch code)."""
+    if rank != 0:
+        return
+    sample = 256 if wl["T"] >= 256 else wl["T"]
+    times = []
+    base = None
+    for i in range(args.warmup + args.steps):
+        base = cpu_baseline(wl, sample)
+        if i >= args.warmup:
+            times.append(base["value"])
+        if i == 0 and float(base["sample"].split("(")[1].split(" s")[0]) > 20:
+            times = [base["value"]]
+            break
+    val = statistics.mean(times)
+    base["value"] = val
+    out = {"impl": "reference", "metric": "moe_layer_fp8_tflops", "value": val, "unit": "TFLOP/s", "n_gpus": args.gpus,
+           "steps": len(times), "warmup": args.warmup, "ms_per_step": None, "higher_is_better": True,
+           "scaling": "weak", "vs_baseline": None, "dtype": "f32 (dequantised e4m3)", "data": "synthetic",
+           "config": {"workload": args.workload, **{k: wl[k] for k in ("T", "H", "I", "E", "k")},
+                      "quant": MODE_NAME[wl["mode"]]},
+           "cpu_baseline": base,
+           "e2e": {"value": val, "unit": "TFLOP/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0}}
+    print(json.dumps(out))
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=20)
+    ap.add_argument("--warmup", type=int, default=5)
+    ap.add_argument("--workload", default="c2", choices=sorted(WORKLOADS))
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--no-cpu-baseline", action="store_true")
+    args = ap.parse_args()
+    wl = WORKLOADS[args.workload]
+    rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+
+    if args.impl == "reference":
+        run_reference(args, wl, rank)
+        return
+
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py needs a CUDA device: dqmoe_b200 has no CPU path "
+                         "(use --impl reference for the CPU oracle)")
+    from dqmoe_b200 import ops
+    import moe_test
+
+    torch.cuda.set_device(local_rank)
+    dev = torch.device("cuda", local_rank)
+    if world > 1:
+        import torch.distributed as dist
+        dist.init_process_group("nccl", device_id=dev)
+        from dqmoe_b200 import ep
+    T, H, I, E, k, mode = wl["T"], wl["H"], wl["I"], wl["E"], wl["k"], wl["mode"]
+    n = T * k
+    pk = peaks()
+
+    # ---- inputs resident in HBM
+    x, logits = synth_inputs(wl, 1234 + rank, dev)
+    idx, weights = ops.route_topk(logits, k, wl["scoring"])
+    if world == 1:
+        b, b1 = synth_weights(wl, 0, dev)
+        aq, as_, bq, bs, b1q, b1s = quantize_gpu(ops, x, b, b1, mode)
+        del b, b1
+        ws = torch.empty(ops.moe_workspace_bytes(T, H, I, E, k, mode), dtype=torch.uint8, device=dev)
+        d = torch.empty(T, k, H, dtype=torch.bfloat16, device=dev)
+
+        def step():
+            ops.moe_forward(aq, as_, bq, bs, b1q, b1s, d, idx, ws, mode)
+    else:
+        layer = ep.ExpertParallelMoE(wl, dev, seed=0, ops=ops)
+        aq, as_ = layer.quantize_activations(x)
+
+        def step():
+            layer.forward(aq, as_, idx, weights)
+    torch.cuda.synchronize()
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    # ---- device-timed region: inputs in HBM
+    for _ in range(max(args.warmup, 3)):
+        step()
+    barrier()
+    sampler = ClockSampler(local_rank)
+    if rank == 0:
+        sampler.start()
+    ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    barrier()
+    ev0.record()
+    for _ in range(args.steps):
+        step()
+    ev1.record()
+    barrier()
+    ms_total = ev0.elapsed_time(ev1)
+    clocks = sampler.stop() if rank == 0 else None
+    code = ops.device_status()
+    if code != 0:
+        raise SystemExit(f"device status {code}: a kernel's bounded wait gave up; no number reported")
+    if world > 1:
+        tmax = torch.tensor([ms_total], device=dev)
+        dist.all_reduce(tmax, op=dist.ReduceOp.MAX)
+        ms_total = float(tmax.item())
+    ms_step = ms_total / args.steps
+    flops_step = 6.0 * T * k * H * I * world
+    value = flops_step / (ms_step * 1e-3) / 1e12
+
+    # ---- end to end through the drop-in call with host buffers (rank-local copies inside the timed region)
+    e2e = None
+    if world == 1:
+        h_aq = aq.cpu().pin_memory()
+        h_as = as_.cpu().pin_memory() if as_ is not None else None
+        h_idx = idx.cpu().pin_memory()
+        h_d = torch.empty(d.shape, dtype=d.dtype).pin_memory()
+        d_aq, d_as, d_idx = torch.empty_like(aq), (torch.empty_like(as_) if as_ is not None else None), torch.empty_like(idx)
+        fn = moe_test.m_grouped_moe_nt_contiguous_fp8_bf16 if mode else moe_test.m_grouped_moe_nt_contiguous_bf16
+        dummy = torch.ones(1, device=dev)
+
+        def e2e_step():
+            d_aq.copy_(h_aq, non_blocking=True)
+            if h_as is not None:
+                d_as.copy_(h_as, non_blocking=True)
+            d_idx.copy_(h_idx, non_blocking=True)
+            fn((d_aq, d_as if mode else dummy), (bq, bs if mode else dummy), (b1q, b1s if mode else dummy), d, d_idx,
+               ws, mode)
+            h_d.copy_(d, non_blocking=True)
+
+        for _ in range(3):
+            e2e_step()
+        torch.cuda.synchronize()
+        ev0.record()
+        for _ in range(args.steps):
+            e2e_step()
+        ev1.record()
+        torch.cuda.synchronize()
+        e2e_ms = ev0.elapsed_time(ev1) / args.steps
+        h2d = h_aq.numel() * h_aq.element_size() + (h_as.numel() * 4 if h_as is not None else 0) + h_idx.numel() * 4
+        e2e = {"value": flops_step / (e2e_ms * 1e-3) / 1e12, "unit": "TFLOP/s", "ms_per_step": e2e_ms,
+               "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": h_d.numel() * h_d.element_size()}
+
+    # ---- roofline of the dominant kernel: the fc1 grouped GEMM timed alone on this step's own operands
+    roofline = None
+    if world == 1:
+        import ctypes
+        from dqmoe_b200 import _lib
+        lib = _lib.load()
+
+        def wptr(which):
+            return lib.dqmoe_moe_workspace_ptr(ctypes.c_void_p(ws.data_ptr()), which, T, H, I, E, k, mode)
+        p_off, p_perm, p_perm_s, p_act, p_act_s, p_mt = wptr(0), wptr(2), wptr(3), wptr(4), wptr(5), wptr(7)
+        stream = ctypes.c_void_p(torch.cuda.current_stream().cuda_stream)
+        scratch_amax = torch.zeros(max(n, 1), dtype=torch.float32, device=dev)
+        gated_out = torch.empty(n * I * 2, dtype=torch.uint8, device=dev)
+        sa1 = as_.data_ptr() if mode == 256 else p_perm_s
+
+        def fc1():
+            _lib.check(lib.dqmoe_grouped_gemm(p_perm, sa1, bq.data_ptr(), bs.data_ptr() if bs is not None else None,
+                                              p_off, p_mt, n, I, H, E, mode, 1, gated_out.data_ptr(), p_act_s,
+                                              scratch_amax.data_ptr(), None, stream))
+        for _ in range(3):
+            fc1()
+        torch.cuda.synchronize()
+        ev0.record()
+        for _ in range(args.steps):
+            fc1()
+        ev1.record()
+        torch.cuda.synchronize()
+        fc1_ms = ev0.elapsed_time(ev1) / args.steps
+        fc1_flops = 2.0 * n * (2 * I) * H
+        achieved = fc1_flops / (fc1_ms * 1e-3) / 1e12
+        peak = pk["bf16"] * (2.0 if mode else 1.0)
+        roofline = {"bound": "tensor", "kernel": "moe_GemmGrouped_GemmUniversal_tcgen05 (fc1, gated)",
+                    "achieved": achieved, "peak": peak, "unit": "TFLOP/s", "frac": achieved / peak,
+                    "peak_note": ("2 x measured bf16 burst (no FP8 peak was measured); " if mode else "") +
+                                 f"of {pk['source']}; nominal dense {'FP8 4500' if mode else 'BF16 2250'} TFLOP/s",
+                    "ms_per_launch": fc1_ms, "traffic": None}
+        tr = os.path.join(ROOT, "profiles", "traffic.json")
+        if os.path.exists(tr):
+            with open(tr) as f:
+                roofline["traffic"] = json.load(f).get(args.workload + "_fc1_dram_bytes_per_launch")
+
+    if rank != 0:
+        if world > 1:
+            dist.destroy_process_group()
+        return
+    base = None if args.no_cpu_baseline else cpu_baseline(wl, 256)
+    out = {
+        "metric": "moe_layer_fp8_tflops" if mode else "moe_layer_bf16_tflops",
+        "value": value, "unit": "TFLOP/s", "n_gpus": world, "steps": args.steps, "warmup": max(args.warmup, 3),
+        "ms_per_step": ms_step, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+        "dtype": "e4m3 x e4m3 -> f32" if mode else "bf16 x bf16 -> f32", "data": "synthetic",
+        "tokens_per_s": T * world / (ms_step * 1e-3),
+        "config": {"workload": f"{args.workload}: {wl['desc']}", "T_per_gpu": T, "H": H, "I": I, "E": E, "k": k,
+                   "quant": MODE_NAME[mode], "parallelism": f"ep{world}" if world > 1 else "single",
+                   "l2": "operands larger than L2 (weights %.2f GB); no flush" % ((3.0 * E * H * I * (1 if mode else 2)) / 1e9)},
+        "gpu_launches": launches_per_step(n, mode) * args.steps if world == 1 else None,
+        "clocks": clocks, "e2e": e2e, "roofline": roofline, "cpu_baseline": base,
+    }
+    print(json.dumps(out))
+    if world > 1:
+        dist.destroy_process_group()
+
+
+if __name__ == "__main__":
+    main()

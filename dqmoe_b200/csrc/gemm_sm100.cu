@@ -28,7 +28,9 @@ constexpr int kStages = 4;
 constexpr int kABytes = kBM * kBKBytes;           // 16 KiB
 constexpr int kBBytes = kUmmaN * kBKBytes;        // 32 KiB
 constexpr int kStageBytes = kABytes + kBBytes;    // 48 KiB
-constexpr int kThreads = 320;                     // warp 0 TMA, warp 1 MMA, warps 2..9 epilogue
+constexpr int kThreads = 384;                     // warp 0 TMA, warp 1 MMA, warps 2-3 idle, warps 4..11 epilogue
+constexpr int kRegsControl = 56;                  // registers per thread of the TMA/MMA warpgroup
+constexpr int kRegsEpilogue = 224;                // registers per thread of the two epilogue warpgroups
 constexpr int kEpiWarps = 8;
 constexpr int kMaxExperts = 1024;
 constexpr int kTmemCols = 512;                    // two accumulator buffers of 256 columns
@@ -97,7 +99,7 @@ __device__ __forceinline__ float silu_bf16(float g) {
 }
 
 template <bool kFp8, int kMode, bool kGated>
-__global__ void __maxnreg__(200)
+__global__ void __launch_bounds__(kThreads, 1)
 moe_GemmGrouped_GemmUniversal_tcgen05(const __grid_constant__ CUtensorMap tma_a,
                                       const __grid_constant__ CUtensorMap tma_b, const Params p) {
     extern __shared__ uint8_t smem_raw[];
@@ -139,7 +141,11 @@ moe_GemmGrouped_GemmUniversal_tcgen05(const __grid_constant__ CUtensorMap tma_a,
     volatile int* abort_flag = &st.abort_flag;
     const int kb_count = p.kb_count;
 
-    if (warp == 0) {
+    // The launch gives every thread 168 registers; the control warpgroup hands most of its
+    // share to the epilogue warpgroups, whose block-scaled accumulators live in registers.
+    if (warp < 4) {
+      ptx::setmaxnreg_dec<kRegsControl>();
+      if (warp == 0) {
         // ------------------------------------------------------------ TMA producer
         if (lane == 0) {
             ptx::prefetch_tensormap(&tma_a);
@@ -169,7 +175,7 @@ moe_GemmGrouped_GemmUniversal_tcgen05(const __grid_constant__ CUtensorMap tma_a,
             }
         }
         __syncwarp();
-    } else if (warp == 1) {
+      } else if (warp == 1) {
         // ------------------------------------------------------------ MMA issuer
         if (lane == 0) {
             constexpr uint32_t idesc = ptx::make_idesc(kFp8 ? 0u : 1u, kBM, kUmmaN);
@@ -229,10 +235,12 @@ moe_GemmGrouped_GemmUniversal_tcgen05(const __grid_constant__ CUtensorMap tma_a,
             }
         }
         __syncwarp();
+      }
     } else {
+        ptx::setmaxnreg_inc<kRegsEpilogue>();
         // ------------------------------------------------------------ epilogue warps
         const int q = warp & 3;            // TMEM lane quarter this warp may read
-        const int h = (warp - 2) >> 2;     // which 64-column half of each 128-column group
+        const int h = (warp - 4) >> 2;     // which 64-column half of each 128-column group
         const int r_in_tile = q * 32 + lane;
         const uint32_t t_lane = tmem_base + (static_cast<uint32_t>(q * 32) << 16);
         uint32_t acc_it = 0;

@@ -64,6 +64,18 @@ __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, volati
     return true;
 }
 
+// ---------------------------------------------------------------- register budget
+
+// Move registers between warpgroups (all four warps of a warpgroup execute the same one).
+template <int kRegs>
+__device__ __forceinline__ void setmaxnreg_inc() {
+    asm volatile("setmaxnreg.inc.sync.aligned.u32 %0;" ::"n"(kRegs));
+}
+template <int kRegs>
+__device__ __forceinline__ void setmaxnreg_dec() {
+    asm volatile("setmaxnreg.dec.sync.aligned.u32 %0;" ::"n"(kRegs));
+}
+
 // ---------------------------------------------------------------- TMA
 
 // 2-D tiled load global -> this CTA's shared memory, completion on an mbarrier.

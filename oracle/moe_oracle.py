@@ -218,7 +218,8 @@ def moe_layer_fp8(a_q, a_s, b_q, b_s, b1_q, b1_s, m_indices, E: int, quant_mode:
     if quant_mode == QUANT_TENSOR:
         # one scale for the whole intermediate (csrc/moe_kernels.h:136-204), torch formula
         amax = max([v[2].abs().float().amax().item() for v in acts.values()] + [0.0])
-        sf_all = torch.tensor(amax, dtype=torch.float32).clamp(min=AMAX_FLOOR) / FP8_MAX
+        # shape [1], not 0-dim: a 0-dim fp32 factor would leave the product below in bf16
+        sf_all = torch.tensor([amax], dtype=torch.float32).clamp(min=AMAX_FLOOR) / FP8_MAX
 
     for e, (tok, slot, act) in acts.items():
         if quant_mode == QUANT_BLOCK:
