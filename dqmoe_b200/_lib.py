@@ -37,6 +37,7 @@ SIGNATURES = {
     "dqmoe_quant_fp8_block_1x128": (_c_int, [_ptr, _c_i64, _c_int, _ptr, _ptr, _ptr]),
     "dqmoe_quant_fp8_block_128x128": (_c_int, [_ptr, _c_int, _c_int, _c_int, _ptr, _ptr, _ptr]),
     "dqmoe_quant_fp8_tensor": (_c_int, [_ptr, _c_int, _c_i64, _ptr, _ptr, _ptr, _ptr]),
+    "dqmoe_quant_fp8_tensor_static": (_c_int, [_ptr, _c_int, _c_i64, _ptr, _ptr, _ptr]),
     "dqmoe_grouped_gemm": (_c_int, [_ptr] * 6 + [_c_int] * 6 + [_ptr] * 5),
     "dqmoe_mtile_prefix": (_c_int, [_ptr, _c_int, _ptr, _ptr]),
     "dqmoe_requant_from_amax": (_c_int, [_ptr, _c_i64, _c_int, _ptr, _c_int, _ptr, _ptr, _ptr]),

@@ -148,6 +148,30 @@ __global__ void __launch_bounds__(kThreads) tensor_quant_kernel(const uint8_t* _
     }
 }
 
+// Scratch of dqmoe_quant_fp8_tensor_static: lives in the library image of every GPU that
+// loads it (4 KiB per device) so that the call needs no caller- or library-made allocation.
+constexpr int kStaticMaxSlices = 1024;
+static __device__ __align__(256) float g_static_amax[kStaticMaxSlices];
+
+// Device address of g_static_amax on the current device. In host code the array's name is
+// only a handle for the runtime, not an address a kernel may use, so the address is looked
+// up once per device (with that device current) and cached.
+static int static_amax_address(float** out) {
+    constexpr int kMaxDevices = 64;
+    static float* cached[kMaxDevices] = {nullptr};
+    int dev = 0;
+    DQ_CUDA(cudaGetDevice(&dev));
+    DQ_CHECK(dev >= 0 && dev < kMaxDevices);
+    if (cached[dev] == nullptr) {
+        float* p = nullptr;
+        DQ_CUDA(cudaGetSymbolAddress(reinterpret_cast<void**>(&p), g_static_amax));
+        DQ_CHECK(p != nullptr);
+        cached[dev] = p;
+    }
+    *out = cached[dev];
+    return DQMOE_OK;
+}
+
 static int grid_cap(int64_t want, int per_sm) {
     const int64_t cap = int64_t(sm_count()) * per_sm;
     return int(want < cap ? (want > 0 ? want : 1) : cap);
@@ -215,6 +239,40 @@ int dqmoe_quant_fp8_tensor(const void* x_bf16, int e, int64_t numel_per, void* q
     quant::tensor_amax_kernel<<<grid, quant::kThreads, 0, s>>>(static_cast<const uint8_t*>(x_bf16), vecs, amax_scratch);
     DQ_LAUNCH_CHECK();
     quant::tensor_quant_kernel<<<grid, quant::kThreads, 0, s>>>(static_cast<const uint8_t*>(x_bf16), vecs, amax_scratch,
+                                                               static_cast<uint8_t*>(q), scale);
+    DQ_LAUNCH_CHECK();
+    return DQMOE_OK;
+}
+
+// Per-tensor / per-expert FP8 quantiser for callers that cannot allocate device memory and
+// have no spare buffer to lend: the amax scratch is the library's own static device array.
+// Same kernels and results as dqmoe_quant_fp8_tensor. Limits and rules:
+//   * at most 1024 slices (e <= 1024); larger e is rejected with an error;
+//   * the first call on each device looks up the array's device address (a host-side runtime
+//     query, no allocation) - make that first call outside any stream capture;
+//   * all calls on one device share the array: it is cleared at the start of every call, and
+//     two calls whose kernels overlap on the GPU (different streams) race on it.
+int dqmoe_quant_fp8_tensor_static(const void* x_bf16, int e, int64_t numel_per, void* q, float* scale,
+                                  dqmoe_stream_t stream) {
+    DQ_CHECK(e >= 0 && numel_per >= 0);
+    DQ_CHECK_FMT(e <= quant::kStaticMaxSlices, "e=%d exceeds the %d slices the static scratch holds", e,
+                 quant::kStaticMaxSlices);
+    if (e == 0 || numel_per == 0) return DQMOE_OK;
+    DQ_CHECK(x_bf16 != nullptr && q != nullptr && scale != nullptr);
+    DQ_CHECK_FMT(numel_per % 8 == 0, "numel_per=%lld must be a multiple of 8", (long long) numel_per);
+    DQ_CHECK(is_aligned(x_bf16, 16) && is_aligned(q, 8));
+    float* amax = nullptr;
+    const int rc = quant::static_amax_address(&amax);
+    if (rc != DQMOE_OK) return rc;
+    cudaStream_t s = static_cast<cudaStream_t>(stream);
+    // the array keeps the previous call's maxima: the reduction must start from zero
+    DQ_CUDA(cudaMemsetAsync(amax, 0, size_t(e) * sizeof(float), s));
+    const int64_t vecs = numel_per / 8;
+    const int gx = quant::grid_cap((vecs + quant::kThreads - 1) / quant::kThreads, e >= 8 ? 2 : 8);
+    dim3 grid(gx, e);
+    quant::tensor_amax_kernel<<<grid, quant::kThreads, 0, s>>>(static_cast<const uint8_t*>(x_bf16), vecs, amax);
+    DQ_LAUNCH_CHECK();
+    quant::tensor_quant_kernel<<<grid, quant::kThreads, 0, s>>>(static_cast<const uint8_t*>(x_bf16), vecs, amax,
                                                                static_cast<uint8_t*>(q), scale);
     DQ_LAUNCH_CHECK();
     return DQMOE_OK;

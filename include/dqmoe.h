@@ -194,6 +194,20 @@ int dqmoe_quant_fp8_block_128x128(const void* w_bf16, int e, int rows, int cols,
 int dqmoe_quant_fp8_tensor(const void* x_bf16, int e, int64_t numel_per, void* q, float* scale,
                            float* amax_scratch, dqmoe_stream_t stream);
 
+/*
+ * dqmoe_quant_fp8_tensor without the amax_scratch argument, for callers that must not
+ * allocate device memory and own no spare buffer: code running between fixed, pre-planned
+ * buffers (an inference-engine plugin's enqueue step, a step being recorded for replay, a
+ * host with a locked memory budget). It has no counterpart in the reference. The scratch
+ * is a 4 KiB static device array inside the library (held by every GPU that loads it), so
+ * e is limited to 1024 slices; a larger e returns DQMOE_ERR_INVALID. The first call on a
+ * device queries the array's address from the runtime and should happen before any stream
+ * capture begins. All calls on a device share the array (it is zeroed per call): calls that
+ * overlap on the GPU race. Results are identical to dqmoe_quant_fp8_tensor.
+ */
+int dqmoe_quant_fp8_tensor_static(const void* x_bf16, int e, int64_t numel_per, void* q, float* scale,
+                                  dqmoe_stream_t stream);
+
 /* ------------------------------------------------------------------ grouped GEMM */
 
 /*
