@@ -10,7 +10,8 @@ import os
 import re
 
 _PKG_DIR = os.path.dirname(os.path.abspath(__file__))
-LIB_PATH = os.path.join(_PKG_DIR, "libdqmoe_b200.so")
+# DQMOE_B200_LIB selects another build of the same library (e.g. one compiled with diagnostics)
+LIB_PATH = os.environ.get("DQMOE_B200_LIB") or os.path.join(_PKG_DIR, "libdqmoe_b200.so")
 HEADER_PATH = os.path.join(os.path.dirname(_PKG_DIR), "include", "dqmoe.h")
 
 _c_int = ctypes.c_int

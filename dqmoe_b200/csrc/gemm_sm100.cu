@@ -33,6 +33,7 @@ constexpr int kRegsControl = 56;                  // registers per thread of the
 constexpr int kRegsEpilogue = 224;                // registers per thread of the two epilogue warpgroups
 constexpr int kEpiWarps = 8;
 constexpr int kMaxExperts = 1024;
+constexpr int kScaleSlots = 8;                     // ring of per-K-block scale sets (block mode)
 constexpr int kTmemCols = 512;                    // two accumulator buffers of 256 columns
 constexpr long long kWaitLimit = 1000000000LL;    // clock cycles before a wait gives up (~0.5 s)
 
@@ -57,7 +58,21 @@ struct Params {
     float* amax;              // stage 1 channel: [n]; tensor: [1]
     const int* dest_to_src;   // stage 2 scatter map or nullptr
     int* status;              // host-mapped status word
+#ifdef DQ_TRACE
+    long long* trace;         // [3 roles][kTraceEvents][4] clock64 stamps of CTA 0 (diagnostic builds only)
+#endif
 };
+
+#ifdef DQ_TRACE
+constexpr int kTraceEvents = 96;
+#define DQ_STAMP(role, idx, slot)                                                        \
+    do {                                                                                \
+        if (blockIdx.x == 0 && p.trace != nullptr && (idx) < kTraceEvents)               \
+            p.trace[((role) * kTraceEvents + (idx)) * 8 + (slot)] = clock64();           \
+    } while (0)
+#else
+#define DQ_STAMP(role, idx, slot) do { } while (0)
+#endif
 
 struct SharedTail {
     uint64_t full[kStages];
@@ -65,9 +80,13 @@ struct SharedTail {
     uint64_t tmem_full[2];
     uint64_t tmem_empty[2];
     uint64_t epi_sync;
+    uint64_t sc_full[kScaleSlots];
+    uint64_t sc_empty[kScaleSlots];
     uint32_t tmem_base;
     int abort_flag;
     float amax[2][2][kBM];
+    float sc_a[kScaleSlots][kBM];   // activation scale of each tile row for one K block
+    float sc_b[kScaleSlots][4];     // weight scales: first group, second group (low / high block row)
     int mprefix[kMaxExperts + 1];
     int offsets[kMaxExperts + 1];
 };
@@ -93,9 +112,43 @@ __device__ __forceinline__ Tile decode_tile(int t, int& e_cursor, const SharedTa
     return tl;
 }
 
+// Rows of the weight-scale grid a block-mode tile reads: the first 128-column group uses one
+// block row; the second group uses `lo` for columns below `c_switch` and `hi` from there on
+// (the gate/value boundary of stage 1 need not fall on a 128-row block boundary).
+struct ScaleRows {
+    int nb0, nb1_lo, nb1_hi, c_switch;
+};
+__device__ __forceinline__ ScaleRows scale_rows(bool gated, int nt, int N, int NB) {
+    ScaleRows r;
+    if (gated) {
+        r.nb0 = nt;
+        const int v0 = N + nt * kBoxRows;  // first value row of this tile
+        r.nb1_lo = v0 >> 7;
+        r.c_switch = 128 - (v0 & 127);
+        r.nb1_hi = r.nb1_lo + 1;
+    } else {
+        r.nb0 = nt * 2;
+        r.nb1_lo = r.nb0 + 1;
+        r.nb1_hi = r.nb1_lo;
+        r.c_switch = 128;
+    }
+    r.nb0 = min(r.nb0, NB - 1);
+    r.nb1_lo = min(r.nb1_lo, NB - 1);
+    r.nb1_hi = min(r.nb1_hi, NB - 1);
+    return r;
+}
+
 __device__ __forceinline__ float silu_bf16(float g) {
     // the torch oracle evaluates silu on bf16 and rounds the result to bf16 (test/util.py:141-142)
     return bf_round(__fdividef(g, 1.0f + __expf(-g)));
+}
+
+// two fp32 FMAs in one instruction (packed fp32 of sm_100): a += x * s
+__device__ __forceinline__ void ffma2(float& a0, float& a1, uint32_t x0, uint32_t x1, float s0, float s1) {
+    const float2 r = __ffma2_rn(make_float2(__uint_as_float(x0), __uint_as_float(x1)), make_float2(s0, s1),
+                                make_float2(a0, a1));
+    a0 = r.x;
+    a1 = r.y;
 }
 
 template <bool kFp8, int kMode, bool kGated>
@@ -120,6 +173,10 @@ moe_GemmGrouped_GemmUniversal_tcgen05(const __grid_constant__ CUtensorMap tma_a,
             ptx::mbar_init(&st.tmem_empty[b], kEpiWarps);
         }
         ptx::mbar_init(&st.epi_sync, kEpiWarps);
+        for (int i = 0; i < kScaleSlots; ++i) {
+            ptx::mbar_init(&st.sc_full[i], 32);         // every lane of the scale-loader warp
+            ptx::mbar_init(&st.sc_empty[i], kEpiWarps);
+        }
         st.abort_flag = 0;
         ptx::fence_barrier_init();
         ptx::fence_proxy_async();
@@ -160,6 +217,7 @@ moe_GemmGrouped_GemmUniversal_tcgen05(const __grid_constant__ CUtensorMap tma_a,
                 for (int kb = 0; kb < kb_count; ++kb, ++it) {
                     const int s = it % kStages;
                     const uint32_t ph = (it / kStages) & 1u;
+                    DQ_STAMP(0, it, 0);
                     if (!ptx::mbar_wait(&st.empty[s], ph ^ 1u, abort_flag, kWaitLimit)) {
                         ok = false;
                         break;
@@ -171,6 +229,7 @@ moe_GemmGrouped_GemmUniversal_tcgen05(const __grid_constant__ CUtensorMap tma_a,
                     ptx::tma_load_2d(sa, &tma_a, k0, tl.row0, &st.full[s]);
                     ptx::tma_load_2d(sb, &tma_b, k0, wrow0, &st.full[s]);
                     ptx::tma_load_2d(sb + kBoxRows * kBKBytes, &tma_b, k0, wrow1, &st.full[s]);
+                    DQ_STAMP(0, it, 1);
                 }
             }
         }
@@ -211,15 +270,21 @@ moe_GemmGrouped_GemmUniversal_tcgen05(const __grid_constant__ CUtensorMap tma_a,
                     ptx::umma_commit(&st.tmem_full[buf]);
                     ++acc_it;
                 } else {
+                    // Block mode: every K block gets its own TMEM buffer (two alternate).
                     for (int kb = 0; kb < kb_count; ++kb, ++it, ++acc_it) {
                         const uint32_t buf = acc_it & 1u;
                         const int s = it % kStages;
-                        if (!ptx::mbar_wait(&st.tmem_empty[buf], ((acc_it >> 1) & 1u) ^ 1u, abort_flag,
-                                            kWaitLimit) ||
-                            !ptx::mbar_wait(&st.full[s], (it / kStages) & 1u, abort_flag, kWaitLimit)) {
+                        DQ_STAMP(1, it, 0);
+                        if (!ptx::mbar_wait(&st.tmem_empty[buf], ((acc_it >> 1) & 1u) ^ 1u, abort_flag, kWaitLimit)) {
                             ok = false;
                             break;
                         }
+                        DQ_STAMP(1, it, 1);
+                        if (!ptx::mbar_wait(&st.full[s], (it / kStages) & 1u, abort_flag, kWaitLimit)) {
+                            ok = false;
+                            break;
+                        }
+                        DQ_STAMP(1, it, 2);
                         ptx::tc_fence_after();
                         const uint32_t a_addr = ptx::smem_u32(smem + size_t(s) * kStageBytes);
                         const uint32_t b_addr = a_addr + kABytes;
@@ -228,13 +293,47 @@ moe_GemmGrouped_GemmUniversal_tcgen05(const __grid_constant__ CUtensorMap tma_a,
                             ptx::umma<kFp8>(tmem_base + buf * kUmmaN, ptx::smem_desc_sw128(a_addr + k * kUmmaKBytes),
                                             ptx::smem_desc_sw128(b_addr + k * kUmmaKBytes), idesc, k != 0 ? 1u : 0u);
                         }
-                        ptx::umma_commit(&st.empty[s]);
                         ptx::umma_commit(&st.tmem_full[buf]);
+                        ptx::umma_commit(&st.empty[s]);
+                        DQ_STAMP(1, it, 3);
                     }
                 }
             }
         }
         __syncwarp();
+      } else if (warp == 2) {
+        // ------------------------------------------------------------ scale loader (block mode)
+        // Stages the scales of every K block in shared memory ahead of the epilogue warps with
+        // 4-byte asynchronous copies, so no global-load latency sits in the accumulation loop.
+        if constexpr (kMode == kBlock) {
+            const int KB = kb_count;
+            const int NB = (p.w_rows + 127) / 128;
+            uint32_t it = 0;
+            int e_cursor = 0;
+            bool ok = true;
+            for (int t = blockIdx.x; ok && t < total_tiles; t += gridDim.x) {
+                const Tile tl = decode_tile(t, e_cursor, st, p.n_tiles);
+                const ScaleRows sr = scale_rows(kGated, tl.nt, p.N, NB);
+                const float* src_a[4];
+#pragma unroll
+                for (int j = 0; j < 4; ++j)
+                    src_a[j] = p.sa + size_t(min(tl.row0 + lane + 32 * j, p.n_rows - 1)) * KB;
+                const int nb = lane == 0 ? sr.nb0 : (lane == 1 ? sr.nb1_lo : sr.nb1_hi);
+                const float* src_b = p.sb + (size_t(tl.e) * NB + nb) * KB;
+                for (int kb = 0; kb < KB; ++kb, ++it) {
+                    const int slot = it % kScaleSlots;
+                    if (!ptx::mbar_wait(&st.sc_empty[slot], ((it / kScaleSlots) & 1u) ^ 1u, abort_flag, kWaitLimit)) {
+                        ok = false;
+                        break;
+                    }
+#pragma unroll
+                    for (int j = 0; j < 4; ++j) ptx::cp_async4(&st.sc_a[slot][lane + 32 * j], src_a[j] + kb);
+                    if (lane < 3) ptx::cp_async4(&st.sc_b[slot][lane], src_b + kb);
+                    ptx::cp_async_arrive(&st.sc_full[slot]);
+                }
+            }
+            ptx::cp_async_wait_all();
+        }
       }
     } else {
         ptx::setmaxnreg_inc<kRegsEpilogue>();
@@ -244,6 +343,7 @@ moe_GemmGrouped_GemmUniversal_tcgen05(const __grid_constant__ CUtensorMap tma_a,
         const int r_in_tile = q * 32 + lane;
         const uint32_t t_lane = tmem_base + (static_cast<uint32_t>(q * 32) << 16);
         uint32_t acc_it = 0;
+        uint32_t sc_it = 0;
         uint32_t tile_it = 0;
         uint32_t epi_phase = 0;
         int e_cursor = 0;
@@ -368,64 +468,70 @@ moe_GemmGrouped_GemmUniversal_tcgen05(const __grid_constant__ CUtensorMap tma_a,
 
                 const int KB = kb_count;                      // scale blocks along K
                 const int NB = (p.w_rows + 127) / 128;        // weight scale block rows per expert
-                const float* sa_row = p.sa + size_t(grow_ld) * KB;
-                // weight-scale block row of the first group and of the second group (two candidates)
-                int nb0, nb1_lo, nb1_hi, c_switch;
-                if constexpr (kGated) {
-                    nb0 = tl.nt;                              // gate rows nt*128 ..
-                    const int v0 = I_or_H + tl.nt * kBoxRows; // first value row of this tile
-                    nb1_lo = v0 >> 7;
-                    c_switch = 128 - (v0 & 127);              // value columns >= c_switch use the next block row
-                    nb1_hi = nb1_lo + 1;
-                } else {
-                    nb0 = tl.nt * 2;
-                    nb1_lo = nb0 + 1;
-                    nb1_hi = nb1_lo;
-                    c_switch = 128;
-                }
-                nb0 = min(nb0, NB - 1);
-                nb1_lo = min(nb1_lo, NB - 1);
-                nb1_hi = min(nb1_hi, NB - 1);
-                const float* sb0 = p.sb + (size_t(tl.e) * NB + nb0) * KB;
-                const float* sb1l = p.sb + (size_t(tl.e) * NB + nb1_lo) * KB;
-                const float* sb1h = p.sb + (size_t(tl.e) * NB + nb1_hi) * KB;
+                const int c_switch = scale_rows(kGated, tl.nt, I_or_H, NB).c_switch;
                 const bool uniform = (c_switch & 31) == 0;
 
-                for (int kb = 0; kb < KB; ++kb, ++acc_it) {
-                    const float a_s = sa_row[kb];
-                    const float s0 = a_s * sb0[kb];
-                    const float s1l = a_s * sb1l[kb];
-                    const float s1h = a_s * sb1h[kb];
+                // Software pipeline over the four 32-column chunks of a K block: while 32 FMAs run
+                // on one register set the TMEM load of the next chunk lands in the other, and the
+                // first two chunks of the next K block are requested before the last two are added.
+                auto tcol = [&](int c) { return (c >> 1) * kBoxRows + h * 64 + (c & 1) * 32; };
+                auto fma_chunk = [&](int c, const uint32_t (&r)[32], float s0, float s1l, float s1h) {
+                    const int cin = h * 64 + (c & 1) * 32;  // column inside the 128-column group
+                    if (c < 2) {
+#pragma unroll
+                        for (int i = 0; i < 32; i += 2) ffma2(acc[c * 32 + i], acc[c * 32 + i + 1], r[i], r[i + 1], s0, s0);
+                    } else if (uniform) {
+                        const float s1 = cin < c_switch ? s1l : s1h;
+#pragma unroll
+                        for (int i = 0; i < 32; i += 2) ffma2(acc[c * 32 + i], acc[c * 32 + i + 1], r[i], r[i + 1], s1, s1);
+                    } else {
+#pragma unroll
+                        for (int i = 0; i < 32; i += 2)
+                            ffma2(acc[c * 32 + i], acc[c * 32 + i + 1], r[i], r[i + 1], (cin + i) < c_switch ? s1l : s1h,
+                                  (cin + i + 1) < c_switch ? s1l : s1h);
+                    }
+                };
+                // The TMEM buffer must go back to the MMA warp as early as possible (the round trip
+                // MMA -> drain -> MMA of one buffer bounds the K-block rate), so per K block: fetch the
+                // scales, wait for the buffer, pull the four 32-column chunks through two register
+                // sets, release the buffer, and only then add the last two chunks.
+                uint32_t r0[32], r1[32];
+                for (int kb = 0; kb < KB; ++kb, ++acc_it, ++sc_it) {
+                    const int slot = sc_it % kScaleSlots;
+                    if (!ptx::mbar_wait(&st.sc_full[slot], (sc_it / kScaleSlots) & 1u, abort_flag, kWaitLimit)) {
+                        ok = false;
+                        break;
+                    }
+                    const float a_s = st.sc_a[slot][r_in_tile];
+                    const float s0 = a_s * st.sc_b[slot][0], s1l = a_s * st.sc_b[slot][1], s1h = a_s * st.sc_b[slot][2];
+                    __syncwarp();
+                    if (lane == 0) ptx::mbar_arrive(&st.sc_empty[slot]);
+
                     const uint32_t buf = acc_it & 1u;
                     if (!ptx::mbar_wait(&st.tmem_full[buf], (acc_it >> 1) & 1u, abort_flag, kWaitLimit)) {
                         ok = false;
                         break;
                     }
+                    if (lane == 0) DQ_STAMP(warp - 2, acc_it, 0);
                     ptx::tc_fence_after();
                     const uint32_t t_buf = t_lane + buf * kUmmaN;
-#pragma unroll
-                    for (int c = 0; c < 4; ++c) {
-                        uint32_t r[32];
-                        const int cin = h * 64 + (c & 1) * 32;  // column inside the 128-column group
-                        ptx::tmem_ld32(t_buf + (c >> 1) * kBoxRows + cin, r);
-                        ptx::tmem_wait_ld(r);
-                        if (c < 2) {
-#pragma unroll
-                            for (int i = 0; i < 32; ++i) acc[c * 32 + i] = fmaf(__uint_as_float(r[i]), s0, acc[c * 32 + i]);
-                        } else if (uniform) {
-                            const float s1 = cin < c_switch ? s1l : s1h;
-#pragma unroll
-                            for (int i = 0; i < 32; ++i) acc[c * 32 + i] = fmaf(__uint_as_float(r[i]), s1, acc[c * 32 + i]);
-                        } else {
-#pragma unroll
-                            for (int i = 0; i < 32; ++i)
-                                acc[c * 32 + i] =
-                                    fmaf(__uint_as_float(r[i]), (cin + i) < c_switch ? s1l : s1h, acc[c * 32 + i]);
-                        }
-                    }
+                    ptx::tmem_ld32(t_buf + tcol(0), r0);
+                    ptx::tmem_ld32(t_buf + tcol(1), r1);
+                    if (lane == 0) DQ_STAMP(warp - 2, acc_it, 1);
+                    ptx::tmem_wait_ld2(r0, r1);
+                    if (lane == 0) DQ_STAMP(warp - 2, acc_it, 2);
+                    fma_chunk(0, r0, s0, s1l, s1h);
+                    ptx::tmem_ld32(t_buf + tcol(2), r0);
+                    fma_chunk(1, r1, s0, s1l, s1h);
+                    ptx::tmem_ld32(t_buf + tcol(3), r1);
+                    ptx::tmem_wait_ld2(r0, r1);
+                    if (lane == 0) DQ_STAMP(warp - 2, acc_it, 3);
                     ptx::tc_fence_before();
                     __syncwarp();
                     if (lane == 0) ptx::mbar_arrive(&st.tmem_empty[buf]);
+                    fma_chunk(2, r0, s0, s1l, s1h);
+                    fma_chunk(3, r1, s0, s1l, s1h);
+                    if (lane == 0) DQ_STAMP(warp - 2, acc_it, 4);
                 }
                 if (!ok) break;
 
@@ -512,6 +618,10 @@ moe_GemmGrouped_GemmUniversal_tcgen05(const __grid_constant__ CUtensorMap tma_a,
 }
 
 // ---------------------------------------------------------------- host side
+
+#ifdef DQ_TRACE
+static long long* g_trace = nullptr;
+#endif
 
 typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
                                   const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
@@ -600,6 +710,9 @@ int grouped_gemm(const void* a, const float* a_scale, const void* w, const float
     p.amax = amax;
     p.dest_to_src = dest_to_src;
     p.status = device_status_word();
+#ifdef DQ_TRACE
+    p.trace = g_trace;
+#endif
     if (p.status == nullptr) return DQMOE_ERR_CUDA;
 
     CUtensorMap ma, mb;
@@ -621,6 +734,10 @@ int grouped_gemm(const void* a, const float* a_scale, const void* w, const float
 
 }  // namespace gemm
 }  // namespace dq
+
+#ifdef DQ_TRACE
+extern "C" void dqmoe_debug_set_trace(long long* p) { dq::gemm::g_trace = p; }
+#endif
 
 extern "C" int dqmoe_grouped_gemm(const void* a, const float* a_scale, const void* w, const float* w_scale,
                                   const int32_t* offsets, const int32_t* mtile_prefix, int n, int N, int K, int E,
