@@ -30,6 +30,7 @@ SIGNATURES = {
     "dqmoe_route_topk": (_c_int, [_ptr, _c_int, _c_int, _c_int, _c_int, _ptr, _ptr, _ptr]),
     "dqmoe_route_sort_workspace_bytes": (_c_size, [_c_int, _c_int]),
     "dqmoe_route_sort": (_c_int, [_ptr, _c_int, _c_int, _ptr, _ptr, _ptr, _ptr, _ptr, _c_size, _ptr]),
+    "dqmoe_segment_ids": (_c_int, [_ptr, _ptr, _c_int, _ptr, _c_int, _ptr]),
     "dqmoe_permute_rows": (_c_int, [_ptr, _c_size, _c_int, _ptr, _c_int, _ptr, _ptr, _c_int, _ptr, _ptr]),
     "dqmoe_permute_quant_block_1x128": (_c_int, [_ptr, _c_int, _c_int, _ptr, _c_int, _ptr, _ptr, _ptr]),
     "dqmoe_finalize_scatter": (_c_int, [_ptr, _c_size, _ptr, _c_int, _ptr, _ptr]),

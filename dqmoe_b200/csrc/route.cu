@@ -200,6 +200,25 @@ __global__ void mtile_prefix_kernel(const int* __restrict__ offsets, int E, int*
     for (int b = threadIdx.x; b <= E; b += blockDim.x) mtile_prefix[b] = s_tiles[b];
 }
 
+// out[r] = values[s] for the rows r of segment s, segments laid out back to back with
+// counts[s] rows each (S <= kMaxExperts). Every block rebuilds the small prefix in shared memory.
+__global__ void __launch_bounds__(256) segment_ids_kernel(const int* __restrict__ counts, const int* __restrict__ values,
+                                                         int S, int* __restrict__ out, int n) {
+    __shared__ int s_pref[kMaxExperts + 2];
+    __shared__ int s_warp_tot[33];
+    for (int i = threadIdx.x; i < S; i += blockDim.x) s_pref[i] = counts[i];
+    __syncthreads();
+    block_exclusive_scan(s_pref, S, s_warp_tot);  // s_pref[S] = total
+    for (int r = blockIdx.x * blockDim.x + threadIdx.x; r < n; r += gridDim.x * blockDim.x) {
+        int lo = 0, hi = S;  // last segment whose start is <= r and which is not empty before r
+        while (hi - lo > 1) {
+            const int mid = (lo + hi) >> 1;
+            if (s_pref[mid] <= r) lo = mid; else hi = mid;
+        }
+        out[r] = r < s_pref[S] ? values[lo] : -1;
+    }
+}
+
 size_t sort_workspace_bytes(int n, int E) {
     const int chunks = ceil_div(n > 0 ? n : 1, kChunk);
     return align_up(size_t(chunks) * (E + 1) * sizeof(int), 256);
@@ -345,6 +364,17 @@ int dqmoe_route_sort(const int32_t* expert_ids, int n, int E, int32_t* counts, i
 int dqmoe_mtile_prefix(const int32_t* offsets, int E, int32_t* mtile_prefix, dqmoe_stream_t stream) {
     DQ_CHECK(E > 0 && E <= dq::route::kMaxExperts && offsets != nullptr && mtile_prefix != nullptr);
     dq::route::mtile_prefix_kernel<<<1, 256, 0, static_cast<cudaStream_t>(stream)>>>(offsets, E, mtile_prefix);
+    DQ_LAUNCH_CHECK();
+    return DQMOE_OK;
+}
+
+int dqmoe_segment_ids(const int32_t* counts, const int32_t* values, int S, int32_t* out, int n,
+                      dqmoe_stream_t stream) {
+    DQ_CHECK(S > 0 && S <= dq::route::kMaxExperts && n >= 0);
+    if (n == 0) return DQMOE_OK;
+    DQ_CHECK(counts != nullptr && values != nullptr && out != nullptr);
+    const int blocks = dq::ceil_div(n, 256) < dq::sm_count() * 4 ? dq::ceil_div(n, 256) : dq::sm_count() * 4;
+    dq::route::segment_ids_kernel<<<blocks, 256, 0, static_cast<cudaStream_t>(stream)>>>(counts, values, S, out, n);
     DQ_LAUNCH_CHECK();
     return DQMOE_OK;
 }

@@ -1,0 +1,192 @@
+"""Expert-parallel MoE layer over the GPUs of one node.
+
+Rank r owns experts [r*E/W, (r+1)*E/W) (weights sharded, never moved); every rank
+keeps its own tokens (data parallel). One layer call is
+
+  1. expert sort of the local rows by global expert id  -> rows grouped by
+     destination rank, then by expert (experts are partitioned contiguously);
+  2. all-to-all of the per-(rank, expert) row counts;
+  3. dispatch: variable-size all-to-all of the packed rows (+ their scales);
+  4. regroup the received rows by local expert, grouped fc1 -> SwiGLU -> fc2 on the
+     local experts, results written back in receive order;
+  5. combine: the reverse all-to-all; scatter to d[T, k, H] (and weighted combine).
+
+The reference has no distributed code at all (device 0 is hard-coded,
+csrc/moe_kernels.h:633); this is the expert-parallel extension of its layer
+(m_grouped_moe_nt_contiguous, csrc/pybind11_register.h:99-151). The collectives
+are torch.distributed calls (NCCL on GPUs); received rows always land in this
+GPU's memory before a kernel touches them. All compute goes through a `backend`
+object: `CudaBackend` below (libdqmoe_b200.so) is the only one the package has.
+"""
+from __future__ import annotations
+
+from typing import List, Optional, Tuple
+
+import torch
+import torch.distributed as dist
+
+
+def expert_range(rank: int, world: int, E: int) -> Tuple[int, int]:
+    """Experts owned by `rank`: a contiguous block of E / world."""
+    if E % world != 0:
+        raise RuntimeError(f"[ASSERT FAILED] ep.py  Condition: E % world == 0  Info: E={E} world={world}")
+    per = E // world
+    return rank * per, (rank + 1) * per
+
+
+def send_splits(counts: torch.Tensor, world: int) -> List[int]:
+    """Rows going to each rank, from the per-expert counts [E] of the local sort."""
+    return counts.view(world, -1).sum(dim=1).tolist()
+
+
+class CudaBackend:
+    """The kernels of libdqmoe_b200.so behind the small interface the EP layer needs."""
+
+    def __init__(self, ops):
+        self.ops = ops
+
+    def route_sort(self, ids, E):
+        return self.ops.route_sort(ids, E)
+
+    def permute(self, a, dest_to_src, k, scale=None):
+        return self.ops.moe_permute(a, dest_to_src, k, scale)
+
+    def segment_ids(self, counts, values, n):
+        return self.ops.segment_ids(counts, values, n)
+
+    def experts(self, rows, row_scale, ids, weights_q, E_local, mode, out):
+        """Grouped fc1 -> SwiGLU -> fc2 of `rows` (expert id per row in `ids`) into out[rows, H]."""
+        b, bs, b1, b1s = weights_q
+        n = rows.shape[0]
+        H = rows.shape[1]
+        I = b1.shape[2]
+        ws = torch.empty(max(self.ops.moe_workspace_bytes(n, H, I, E_local, 1, mode), 256), dtype=torch.uint8,
+                         device=rows.device)
+        # the layer with k = 1: row i is "token" i with the single expert ids[i]
+        self.ops.moe_forward(rows, row_scale, b, bs, b1, b1s, out.view(n, 1, H), ids.view(n, 1), ws, mode)
+
+    def finalize_scatter(self, rows, dest_to_src, d):
+        self.ops.finalize_scatter(rows, dest_to_src, d)
+
+    def finalize_weighted(self, d, weights):
+        return self.ops.finalize_weighted(d, weights)
+
+
+class ExpertParallelLayer:
+    """One expert-parallel MoE layer; `weights_q` holds this rank's experts only."""
+
+    def __init__(self, E: int, k: int, mode: int, weights_q, backend, group=None):
+        self.group = group
+        self.world = dist.get_world_size(group)
+        self.rank = dist.get_rank(group)
+        self.E, self.k, self.mode = E, k, mode
+        self.lo, self.hi = expert_range(self.rank, self.world, E)
+        self.E_local = self.hi - self.lo
+        self.weights_q = weights_q
+        self.backend = backend
+
+    # ------------------------------------------------------------------ plumbing
+
+    def exchange_counts(self, counts: torch.Tensor) -> torch.Tensor:
+        """counts [E] (rows per global expert on this rank) -> recv_counts [W, E_local]
+        (rows arriving from each rank for each local expert)."""
+        W = self.world
+        send = counts.view(W, self.E_local).contiguous()
+        recv = torch.empty_like(send)
+        dist.all_to_all_single(recv, send, group=self.group)
+        return recv
+
+    def all_to_all_rows(self, x: torch.Tensor, out_rows: int, in_splits, out_splits) -> torch.Tensor:
+        """Variable-size all-to-all over the leading (row) dimension; bytes are moved as uint8."""
+        flat = x.reshape(x.shape[0], -1)
+        as_bytes = flat.view(torch.uint8) if flat.dtype != torch.uint8 else flat
+        out = torch.empty((out_rows, as_bytes.shape[1]), dtype=torch.uint8, device=x.device)
+        dist.all_to_all_single(out, as_bytes, output_split_sizes=out_splits, input_split_sizes=in_splits,
+                               group=self.group)
+        return out.view(x.dtype).view((out_rows,) + tuple(x.shape[1:]))
+
+    # ------------------------------------------------------------------ layer
+
+    def forward(self, a: torch.Tensor, a_scale: Optional[torch.Tensor], m_indices: torch.Tensor,
+                route_weights: Optional[torch.Tensor] = None) -> torch.Tensor:
+        """a [T, H] (e4m3 or bf16) with its scales, m_indices [T, k] global expert ids.
+        Returns d [T, k, H] bf16, or the weighted combine [T, H] when route_weights is given."""
+        be, k, W = self.backend, self.k, self.world
+        T, H = a.shape
+        n = T * k
+        if a_scale is not None and self.mode == 256:
+            raise RuntimeError("[ASSERT FAILED] ep.py  Condition: mode != FP8_TENSOR  "
+                               "Info: a per-tensor scale differs per rank; use channel or block mode with EP")
+        # 1. local sort by global expert id: rows for rank 0's experts first, then rank 1's, ...
+        counts, offsets, d2s, _ = be.route_sort(m_indices, self.E)
+        # 2. counts to the owners; split sizes must reach the host (one small synchronising copy)
+        recv_counts = self.exchange_counts(counts)
+        in_splits = send_splits(counts.cpu(), W)
+        out_splits = recv_counts.sum(dim=1).tolist()
+        n_recv = int(sum(out_splits))
+        kept = int(sum(in_splits))
+        # 3. dispatch: gather the kept rows (expert-sorted = destination-sorted) and send them
+        if a_scale is not None:
+            sc = a_scale.view(T, -1)
+            rows, row_scale = be.permute(a, d2s[:kept], k, sc)
+            recv_scale = self.all_to_all_rows(row_scale, n_recv, in_splits, out_splits)
+        else:
+            rows, recv_scale = be.permute(a, d2s[:kept], k), None
+        recv_rows = self.all_to_all_rows(rows, n_recv, in_splits, out_splits)
+        # 4. expert id of every received row: segments (src rank, local expert) of recv_counts
+        local_ids = torch.arange(self.E_local, dtype=torch.int32, device=a.device).repeat(W)
+        ids = be.segment_ids(recv_counts.reshape(-1), local_ids, n_recv)
+        out_rows = torch.empty((n_recv, H), dtype=torch.bfloat16, device=a.device)
+        if n_recv > 0:
+            be.experts(recv_rows, recv_scale, ids, self.weights_q, self.E_local, self.mode, out_rows)
+        # 5. combine: rows travel back in the same order, then scatter to slot order
+        back = self.all_to_all_rows(out_rows, kept, out_splits, in_splits)
+        d = torch.zeros((T, k, H), dtype=torch.bfloat16, device=a.device) if kept < n else \
+            torch.empty((T, k, H), dtype=torch.bfloat16, device=a.device)
+        if kept > 0:
+            be.finalize_scatter(back, d2s[:kept], d)
+        if route_weights is None:
+            return d
+        return be.finalize_weighted(d, route_weights)
+
+
+class ExpertParallelMoE:
+    """Bench/test helper: seeded synthetic weights of one workload, sharded by expert, quantised
+    on this rank's GPU with the library's own quantisers."""
+
+    def __init__(self, wl: dict, device, seed: int, ops, group=None):
+        from . import ops as _ops  # noqa: F401  (the CUDA front end; there is no other backend)
+        self.ops = ops
+        world, rank = dist.get_world_size(group), dist.get_rank(group)
+        E, H, I, mode = wl["E"], wl["H"], wl["I"], wl["mode"]
+        lo, hi = expert_range(rank, world, E)
+        b = torch.empty(hi - lo, 2 * I, H, device=device, dtype=torch.bfloat16)
+        b1 = torch.empty(hi - lo, H, I, device=device, dtype=torch.bfloat16)
+        for e in range(lo, hi):  # one generator per global expert: the model is the same for every world size
+            g = torch.Generator(device=device).manual_seed(seed * 100003 + e)
+            b[e - lo] = (torch.randn(2 * I, H, generator=g, device=device) * 0.02).to(torch.bfloat16)
+            b1[e - lo] = (torch.randn(H, I, generator=g, device=device) * 0.02).to(torch.bfloat16)
+        self.mode = mode
+        if mode == 1024:
+            wq = (*ops.per_block_cast_to_fp8(b), *ops.per_block_cast_to_fp8(b1))
+        elif mode == 512:
+            bq, bs = ops.per_channel_cast_to_fp8(b)
+            b1q, b1s = ops.per_channel_cast_to_fp8(b1)
+            wq = (bq, bs.view(hi - lo, -1), b1q, b1s.view(hi - lo, -1))
+        elif mode == 0:
+            wq = (b, None, b1, None)
+        else:
+            raise RuntimeError("[ASSERT FAILED] ep.py  Condition: mode in (0, 512, 1024)")
+        del b, b1
+        self.layer = ExpertParallelLayer(E, wl["k"], mode, wq, CudaBackend(ops), group)
+
+    def quantize_activations(self, x):
+        if self.mode == 1024:
+            return self.ops.per_token_block_cast_to_fp8(x)
+        if self.mode == 512:
+            q, s = self.ops.per_token_cast_to_fp8(x)
+            return q, s.view(-1)
+        return x, None
+
+    def forward(self, aq, a_scale, idx, weights):
+        return self.layer.forward(aq, a_scale, idx, weights)

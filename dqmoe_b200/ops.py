@@ -116,6 +116,17 @@ def mtile_prefix(offsets: torch.Tensor) -> torch.Tensor:
     return out
 
 
+def segment_ids(counts: torch.Tensor, values: torch.Tensor, n: int) -> torch.Tensor:
+    """out[r] = values[s] for the counts[s] rows of segment s (run-length expansion, int32)."""
+    _cuda(counts, "counts")
+    _cuda(values, "values")
+    out = torch.empty(n, dtype=torch.int32, device=counts.device)
+    with torch.cuda.device(counts.device):
+        _lib.check(_lib.load().dqmoe_segment_ids(_p(counts), _p(values), counts.numel(), _p(out), n,
+                                                 _stream(counts.device)))
+    return out
+
+
 # ---------------------------------------------------------------------- permute / finalize
 
 def moe_permute(a: torch.Tensor, dest_to_src: torch.Tensor, k: int,

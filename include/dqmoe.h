@@ -134,6 +134,15 @@ int dqmoe_route_sort(const int32_t* expert_ids, int n, int E, int32_t* counts, i
                      int32_t* dest_to_src, int32_t* src_to_dest, void* workspace,
                      size_t workspace_bytes, dqmoe_stream_t stream);
 
+/*
+ * Expand run lengths: out[r] = values[s] for the counts[s] consecutive rows of segment s
+ * (S <= 1024 segments, n rows in all; rows beyond the sum of counts get -1). Used by the
+ * expert-parallel layer to label received rows with their local expert id. No counterpart in
+ * the reference, which has no multi-GPU path.
+ */
+int dqmoe_segment_ids(const int32_t* counts, const int32_t* values, int S, int32_t* out, int n,
+                      dqmoe_stream_t stream);
+
 /* ------------------------------------------------------------------ permute / finalize */
 
 /*
