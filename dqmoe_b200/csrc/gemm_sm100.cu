@@ -13,6 +13,8 @@
 // per-expert "configure" kernels (csrc/moe_gemm_template.h:72-1039) together
 // with doGatedActivationKernel, scale_1x128_kernel and finalizeScatterKernel
 // (csrc/moe_kernels.h:301-444, 581-620).
+#include <cstdlib>
+
 #include "common.cuh"
 #include "ptx_sm100.cuh"
 
@@ -24,10 +26,14 @@ constexpr int kBoxRows = 128;                     // weight rows per TMA box, tw
 constexpr int kUmmaN = 2 * kBoxRows;              // 256 accumulator columns per tile
 constexpr int kBKBytes = 128;                     // K bytes per stage: one 128-byte swizzle row
 constexpr int kUmmaKBytes = 32;                   // K bytes per tcgen05.mma
-constexpr int kStages = 4;
+constexpr int kStages = 4;                          // single-CTA tiles: 4 stages of A 16 KiB + B 32 KiB
+constexpr int kStagesPair = 6;                      // CTA pairs: 6 stages of A 16 KiB + B-half 16 KiB
+constexpr int kMaxStages = 6;
 constexpr int kABytes = kBM * kBKBytes;           // 16 KiB
 constexpr int kBBytes = kUmmaN * kBKBytes;        // 32 KiB
 constexpr int kStageBytes = kABytes + kBBytes;    // 48 KiB
+constexpr int kStageBytesPair = kABytes + kBBytes / 2;  // 32 KiB per CTA of a pair
+static_assert(kStages * kStageBytes == kStagesPair * kStageBytesPair, "both layouts fill the same stage area");
 constexpr int kThreads = 384;                     // warp 0 TMA, warp 1 MMA, warps 2-3 idle, warps 4..11 epilogue
 constexpr int kRegsControl = 56;                  // registers per thread of the TMA/MMA warpgroup
 constexpr int kRegsEpilogue = 224;                // registers per thread of the two epilogue warpgroups
@@ -75,8 +81,8 @@ constexpr int kTraceEvents = 96;
 #endif
 
 struct SharedTail {
-    uint64_t full[kStages];
-    uint64_t empty[kStages];
+    uint64_t full[kMaxStages];
+    uint64_t empty[kMaxStages];
     uint64_t tmem_full[2];
     uint64_t tmem_empty[2];
     uint64_t epi_sync;
@@ -100,14 +106,17 @@ struct Tile {
 // Tiles are numbered expert-major; inside an expert the row tile runs fastest so
 // that concurrently running CTAs share one weight tile and the expert's rows
 // stay in L2.
-__device__ __forceinline__ Tile decode_tile(int t, int& e_cursor, const SharedTail& st, int n_tiles) {
+// With CTA pairs a tile is 256 rows: mprefix then counts pairs of 128-row tiles and CTA `sub`
+// of the pair takes row tile 2j + sub (the second one is empty when the expert's tile count is odd).
+template <bool kPair>
+__device__ __forceinline__ Tile decode_tile(int t, int& e_cursor, const SharedTail& st, int n_tiles, int sub) {
     while (t >= st.mprefix[e_cursor + 1] * n_tiles) ++e_cursor;
     const int local = t - st.mprefix[e_cursor] * n_tiles;
     const int mtiles = st.mprefix[e_cursor + 1] - st.mprefix[e_cursor];
     Tile tl;
     tl.e = e_cursor;
     tl.nt = local / mtiles;
-    tl.row0 = st.offsets[e_cursor] + (local % mtiles) * kBM;
+    tl.row0 = st.offsets[e_cursor] + ((local % mtiles) * (kPair ? 2 : 1) + sub) * kBM;
     tl.row_end = st.offsets[e_cursor + 1];
     return tl;
 }
@@ -151,7 +160,7 @@ __device__ __forceinline__ void ffma2(float& a0, float& a1, uint32_t x0, uint32_
     a1 = r.y;
 }
 
-template <bool kFp8, int kMode, bool kGated>
+template <bool kFp8, int kMode, bool kGated, bool kPair>
 __global__ void __launch_bounds__(kThreads, 1)
 moe_GemmGrouped_GemmUniversal_tcgen05(const __grid_constant__ CUtensorMap tma_a,
                                       const __grid_constant__ CUtensorMap tma_b, const Params p) {
@@ -162,15 +171,22 @@ moe_GemmGrouped_GemmUniversal_tcgen05(const __grid_constant__ CUtensorMap tma_a,
     const int warp = threadIdx.x >> 5;
     const int lane = threadIdx.x & 31;
     constexpr int kBKElems = kFp8 ? kBKBytes : kBKBytes / 2;
+    constexpr int kNumStages = kPair ? kStagesPair : kStages;
+    constexpr int kStageSz = kPair ? kStageBytesPair : kStageBytes;
+    // In a pair, CTA 0 (the leader) issues the MMAs for both and owns the barriers they wait on.
+    const uint32_t cta_rank = kPair ? ptx::cluster_ctarank() : 0u;
+    const bool leader = cta_rank == 0u;
+    const int tile_first = kPair ? int(blockIdx.x >> 1) : int(blockIdx.x);
+    const int tile_step = kPair ? int(gridDim.x >> 1) : int(gridDim.x);
 
     if (threadIdx.x == 0) {
-        for (int s = 0; s < kStages; ++s) {
+        for (int s = 0; s < kNumStages; ++s) {
             ptx::mbar_init(&st.full[s], 1);
             ptx::mbar_init(&st.empty[s], 1);
         }
         for (int b = 0; b < 2; ++b) {
             ptx::mbar_init(&st.tmem_full[b], 1);
-            ptx::mbar_init(&st.tmem_empty[b], kEpiWarps);
+            ptx::mbar_init(&st.tmem_empty[b], kPair ? 2 * kEpiWarps : kEpiWarps);  // both CTAs' epilogue warps
         }
         ptx::mbar_init(&st.epi_sync, kEpiWarps);
         for (int i = 0; i < kScaleSlots; ++i) {
@@ -181,9 +197,15 @@ moe_GemmGrouped_GemmUniversal_tcgen05(const __grid_constant__ CUtensorMap tma_a,
         ptx::fence_barrier_init();
         ptx::fence_proxy_async();
     }
+    if constexpr (kPair) ptx::cluster_sync();  // the peer's barriers exist before anything signals them
     if (warp == 1) {
-        ptx::tmem_alloc(&st.tmem_base, kTmemCols);
-        ptx::tmem_relinquish();
+        if constexpr (kPair) {
+            ptx::tmem_alloc_pair(&st.tmem_base, kTmemCols);
+            ptx::tmem_relinquish_pair();
+        } else {
+            ptx::tmem_alloc(&st.tmem_base, kTmemCols);
+            ptx::tmem_relinquish();
+        }
     }
     for (int i = threadIdx.x; i <= p.E; i += kThreads) {
         st.mprefix[i] = p.mtile_prefix[i];
@@ -192,6 +214,20 @@ moe_GemmGrouped_GemmUniversal_tcgen05(const __grid_constant__ CUtensorMap tma_a,
     ptx::tc_fence_before();
     __syncthreads();
     ptx::tc_fence_after();
+    if constexpr (kPair) {
+        if (threadIdx.x == 0) {  // tiles of 128 rows -> pairs of tiles, in place
+            int prev = st.mprefix[0], run = 0;
+            st.mprefix[0] = 0;
+            for (int e = 0; e < p.E; ++e) {
+                const int next = st.mprefix[e + 1];
+                run += (next - prev + 1) >> 1;
+                prev = next;
+                st.mprefix[e + 1] = run;
+            }
+        }
+        __syncthreads();
+        ptx::cluster_sync();  // both CTAs hold their TMEM before the first pair MMA
+    }
 
     const uint32_t tmem_base = st.tmem_base;
     const int total_tiles = st.mprefix[p.E] * p.n_tiles;
@@ -210,25 +246,34 @@ moe_GemmGrouped_GemmUniversal_tcgen05(const __grid_constant__ CUtensorMap tma_a,
             uint32_t it = 0;
             int e_cursor = 0;
             bool ok = true;
-            for (int t = blockIdx.x; ok && t < total_tiles; t += gridDim.x) {
-                const Tile tl = decode_tile(t, e_cursor, st, p.n_tiles);
+            for (int t = tile_first; ok && t < total_tiles; t += tile_step) {
+                const Tile tl = decode_tile<kPair>(t, e_cursor, st, p.n_tiles, cta_rank);
                 const int wrow0 = tl.e * p.w_rows + tl.nt * p.tile_w_rows;
                 const int wrow1 = wrow0 + p.box2_off;
                 for (int kb = 0; kb < kb_count; ++kb, ++it) {
-                    const int s = it % kStages;
-                    const uint32_t ph = (it / kStages) & 1u;
+                    const int s = it % kNumStages;
+                    const uint32_t ph = (it / kNumStages) & 1u;
                     DQ_STAMP(0, it, 0);
                     if (!ptx::mbar_wait(&st.empty[s], ph ^ 1u, abort_flag, kWaitLimit)) {
                         ok = false;
                         break;
                     }
-                    uint8_t* sa = smem + size_t(s) * kStageBytes;
+                    uint8_t* sa = smem + size_t(s) * kStageSz;
                     uint8_t* sb = sa + kABytes;
-                    ptx::mbar_arrive_expect_tx(&st.full[s], kStageBytes);
                     const int k0 = kb * kBKElems;
-                    ptx::tma_load_2d(sa, &tma_a, k0, tl.row0, &st.full[s]);
-                    ptx::tma_load_2d(sb, &tma_b, k0, wrow0, &st.full[s]);
-                    ptx::tma_load_2d(sb + kBoxRows * kBKBytes, &tma_b, k0, wrow1, &st.full[s]);
+                    if constexpr (kPair) {
+                        // Each CTA loads its own 128 rows of A and its half of the weight tile (CTA 0 the
+                        // first 128 rows, CTA 1 the second); all bytes are credited to the leader's barrier.
+                        const uint32_t full_leader = ptx::map_to_cta(&st.full[s], 0);
+                        if (leader) ptx::mbar_arrive_expect_tx(&st.full[s], 2 * kStageBytesPair);
+                        ptx::tma_load_2d_pair(sa, &tma_a, k0, tl.row0, full_leader);
+                        ptx::tma_load_2d_pair(sb, &tma_b, k0, leader ? wrow0 : wrow1, full_leader);
+                    } else {
+                        ptx::mbar_arrive_expect_tx(&st.full[s], kStageBytes);
+                        ptx::tma_load_2d(sa, &tma_a, k0, tl.row0, &st.full[s]);
+                        ptx::tma_load_2d(sb, &tma_b, k0, wrow0, &st.full[s]);
+                        ptx::tma_load_2d(sb + kBoxRows * kBKBytes, &tma_b, k0, wrow1, &st.full[s]);
+                    }
                     DQ_STAMP(0, it, 1);
                 }
             }
@@ -236,12 +281,28 @@ moe_GemmGrouped_GemmUniversal_tcgen05(const __grid_constant__ CUtensorMap tma_a,
         __syncwarp();
       } else if (warp == 1) {
         // ------------------------------------------------------------ MMA issuer
-        if (lane == 0) {
-            constexpr uint32_t idesc = ptx::make_idesc(kFp8 ? 0u : 1u, kBM, kUmmaN);
+        if (lane == 0 && leader) {
+            constexpr uint32_t idesc = ptx::make_idesc(kFp8 ? 0u : 1u, kPair ? 2 * kBM : kBM, kUmmaN);
+            // issue one K step; in a pair the same call drives both CTAs' tensor cores
+            auto mma_step = [&](uint32_t d_tmem, uint32_t a_addr, uint32_t b_addr, uint32_t accumulate) {
+                if constexpr (kPair)
+                    ptx::umma_pair<kFp8>(d_tmem, ptx::smem_desc_sw128(a_addr), ptx::smem_desc_sw128(b_addr), idesc, accumulate);
+                else
+                    ptx::umma<kFp8>(d_tmem, ptx::smem_desc_sw128(a_addr), ptx::smem_desc_sw128(b_addr), idesc, accumulate);
+            };
+            // completion of everything issued so far -> one barrier (of both CTAs in a pair)
+            auto commit = [&](uint64_t* bar) {
+                if constexpr (kPair) {
+                    ptx::umma_commit_pair(ptx::map_to_cta(bar, 0));
+                    ptx::umma_commit_pair(ptx::map_to_cta(bar, 1));
+                } else {
+                    ptx::umma_commit(bar);
+                }
+            };
             uint32_t it = 0;
             uint32_t acc_it = 0;
             bool ok = true;
-            for (int t = blockIdx.x; ok && t < total_tiles; t += gridDim.x) {
+            for (int t = tile_first; ok && t < total_tiles; t += tile_step) {
                 if constexpr (kMode != kBlock) {
                     const uint32_t buf = acc_it & 1u;
                     if (!ptx::mbar_wait(&st.tmem_empty[buf], ((acc_it >> 1) & 1u) ^ 1u, abort_flag, kWaitLimit)) {
@@ -250,51 +311,48 @@ moe_GemmGrouped_GemmUniversal_tcgen05(const __grid_constant__ CUtensorMap tma_a,
                     }
                     ptx::tc_fence_after();
                     for (int kb = 0; kb < kb_count; ++kb, ++it) {
-                        const int s = it % kStages;
-                        if (!ptx::mbar_wait(&st.full[s], (it / kStages) & 1u, abort_flag, kWaitLimit)) {
+                        const int s = it % kNumStages;
+                        if (!ptx::mbar_wait(&st.full[s], (it / kNumStages) & 1u, abort_flag, kWaitLimit)) {
                             ok = false;
                             break;
                         }
                         ptx::tc_fence_after();
-                        const uint32_t a_addr = ptx::smem_u32(smem + size_t(s) * kStageBytes);
+                        const uint32_t a_addr = ptx::smem_u32(smem + size_t(s) * kStageSz);
                         const uint32_t b_addr = a_addr + kABytes;
 #pragma unroll
-                        for (int k = 0; k < kBKBytes / kUmmaKBytes; ++k) {
-                            ptx::umma<kFp8>(tmem_base + buf * kUmmaN, ptx::smem_desc_sw128(a_addr + k * kUmmaKBytes),
-                                            ptx::smem_desc_sw128(b_addr + k * kUmmaKBytes), idesc,
-                                            (kb | k) != 0 ? 1u : 0u);
-                        }
-                        ptx::umma_commit(&st.empty[s]);
+                        for (int k = 0; k < kBKBytes / kUmmaKBytes; ++k)
+                            mma_step(tmem_base + buf * kUmmaN, a_addr + k * kUmmaKBytes, b_addr + k * kUmmaKBytes,
+                                     (kb | k) != 0 ? 1u : 0u);
+                        commit(&st.empty[s]);
                     }
                     if (!ok) break;
-                    ptx::umma_commit(&st.tmem_full[buf]);
+                    commit(&st.tmem_full[buf]);
                     ++acc_it;
                 } else {
                     // Block mode: every K block gets its own TMEM buffer (two alternate).
                     for (int kb = 0; kb < kb_count; ++kb, ++it, ++acc_it) {
                         const uint32_t buf = acc_it & 1u;
-                        const int s = it % kStages;
+                        const int s = it % kNumStages;
                         DQ_STAMP(1, it, 0);
                         if (!ptx::mbar_wait(&st.tmem_empty[buf], ((acc_it >> 1) & 1u) ^ 1u, abort_flag, kWaitLimit)) {
                             ok = false;
                             break;
                         }
                         DQ_STAMP(1, it, 1);
-                        if (!ptx::mbar_wait(&st.full[s], (it / kStages) & 1u, abort_flag, kWaitLimit)) {
+                        if (!ptx::mbar_wait(&st.full[s], (it / kNumStages) & 1u, abort_flag, kWaitLimit)) {
                             ok = false;
                             break;
                         }
                         DQ_STAMP(1, it, 2);
                         ptx::tc_fence_after();
-                        const uint32_t a_addr = ptx::smem_u32(smem + size_t(s) * kStageBytes);
+                        const uint32_t a_addr = ptx::smem_u32(smem + size_t(s) * kStageSz);
                         const uint32_t b_addr = a_addr + kABytes;
 #pragma unroll
-                        for (int k = 0; k < kBKBytes / kUmmaKBytes; ++k) {
-                            ptx::umma<kFp8>(tmem_base + buf * kUmmaN, ptx::smem_desc_sw128(a_addr + k * kUmmaKBytes),
-                                            ptx::smem_desc_sw128(b_addr + k * kUmmaKBytes), idesc, k != 0 ? 1u : 0u);
-                        }
-                        ptx::umma_commit(&st.tmem_full[buf]);
-                        ptx::umma_commit(&st.empty[s]);
+                        for (int k = 0; k < kBKBytes / kUmmaKBytes; ++k)
+                            mma_step(tmem_base + buf * kUmmaN, a_addr + k * kUmmaKBytes, b_addr + k * kUmmaKBytes,
+                                     k != 0 ? 1u : 0u);
+                        commit(&st.tmem_full[buf]);
+                        commit(&st.empty[s]);
                         DQ_STAMP(1, it, 3);
                     }
                 }
@@ -311,8 +369,8 @@ moe_GemmGrouped_GemmUniversal_tcgen05(const __grid_constant__ CUtensorMap tma_a,
             uint32_t it = 0;
             int e_cursor = 0;
             bool ok = true;
-            for (int t = blockIdx.x; ok && t < total_tiles; t += gridDim.x) {
-                const Tile tl = decode_tile(t, e_cursor, st, p.n_tiles);
+            for (int t = tile_first; ok && t < total_tiles; t += tile_step) {
+                const Tile tl = decode_tile<kPair>(t, e_cursor, st, p.n_tiles, cta_rank);
                 const ScaleRows sr = scale_rows(kGated, tl.nt, p.N, NB);
                 const float* src_a[4];
 #pragma unroll
@@ -349,9 +407,16 @@ moe_GemmGrouped_GemmUniversal_tcgen05(const __grid_constant__ CUtensorMap tma_a,
         int e_cursor = 0;
         bool ok = true;
         const int I_or_H = p.N;
+        // hand a drained accumulator buffer back to the MMA thread (which lives in the leader CTA)
+        auto release_tmem = [&](uint32_t b) {
+            if constexpr (kPair)
+                ptx::mbar_arrive_cluster(ptx::map_to_cta(&st.tmem_empty[b], 0));
+            else
+                ptx::mbar_arrive(&st.tmem_empty[b]);
+        };
 
-        for (int t = blockIdx.x; ok && t < total_tiles; t += gridDim.x, ++tile_it) {
-            const Tile tl = decode_tile(t, e_cursor, st, p.n_tiles);
+        for (int t = tile_first; ok && t < total_tiles; t += tile_step, ++tile_it) {
+            const Tile tl = decode_tile<kPair>(t, e_cursor, st, p.n_tiles, cta_rank);
             const int grow = tl.row0 + r_in_tile;
             const bool row_ok = grow < tl.row_end;
             const int grow_ld = min(grow, p.n_rows - 1);
@@ -458,7 +523,7 @@ moe_GemmGrouped_GemmUniversal_tcgen05(const __grid_constant__ CUtensorMap tma_a,
                 }
                 ptx::tc_fence_before();
                 __syncwarp();
-                if (lane == 0) ptx::mbar_arrive(&st.tmem_empty[buf]);
+                if (lane == 0) release_tmem(buf);
             } else {
                 // ---------------------------------------------------- block-scaled accumulation
                 // acc[c*32 + i]: chunk c of this thread's four 32-column chunks.
@@ -528,7 +593,7 @@ moe_GemmGrouped_GemmUniversal_tcgen05(const __grid_constant__ CUtensorMap tma_a,
                     if (lane == 0) DQ_STAMP(warp - 2, acc_it, 3);
                     ptx::tc_fence_before();
                     __syncwarp();
-                    if (lane == 0) ptx::mbar_arrive(&st.tmem_empty[buf]);
+                    if (lane == 0) release_tmem(buf);
                     fma_chunk(2, r0, s0, s1l, s1h);
                     fma_chunk(3, r1, s0, s1l, s1h);
                     if (lane == 0) DQ_STAMP(warp - 2, acc_it, 4);
@@ -611,9 +676,13 @@ moe_GemmGrouped_GemmUniversal_tcgen05(const __grid_constant__ CUtensorMap tma_a,
     }
     ptx::tc_fence_before();
     __syncthreads();
+    if constexpr (kPair) ptx::cluster_sync();  // the peer has stopped using this CTA's barriers and TMEM
     if (warp == 1) {
         ptx::tc_fence_after();
-        ptx::tmem_dealloc(tmem_base, kTmemCols);
+        if constexpr (kPair)
+            ptx::tmem_dealloc_pair(tmem_base, kTmemCols);
+        else
+            ptx::tmem_dealloc(tmem_base, kTmemCols);
     }
 }
 
@@ -657,9 +726,9 @@ static int make_map(CUtensorMap* map, const void* base, bool fp8, uint64_t rows,
     return DQMOE_OK;
 }
 
-template <bool kFp8, int kMode, bool kGated>
+template <bool kFp8, int kMode, bool kGated, bool kPair>
 static int launch(const CUtensorMap& ma, const CUtensorMap& mb, const Params& p, cudaStream_t stream) {
-    auto kern = moe_GemmGrouped_GemmUniversal_tcgen05<kFp8, kMode, kGated>;
+    auto kern = moe_GemmGrouped_GemmUniversal_tcgen05<kFp8, kMode, kGated, kPair>;
     static bool configured = false;  // per instantiation
     static int configured_dev = -1;
     int dev = 0;
@@ -669,9 +738,40 @@ static int launch(const CUtensorMap& ma, const CUtensorMap& mb, const Params& p,
         configured = true;
         configured_dev = dev;
     }
-    kern<<<sm_count(), kThreads, kSmemBytes, stream>>>(ma, mb, p);
+    if constexpr (kPair) {
+        // clusters of two CTAs on neighbouring SMs; an even grid
+        cudaLaunchConfig_t cfg = {};
+        cfg.gridDim = dim3(unsigned(sm_count() & ~1), 1, 1);
+        cfg.blockDim = dim3(kThreads, 1, 1);
+        cfg.dynamicSmemBytes = kSmemBytes;
+        cfg.stream = stream;
+        cudaLaunchAttribute attr[1];
+        attr[0].id = cudaLaunchAttributeClusterDimension;
+        attr[0].val.clusterDim.x = 2;
+        attr[0].val.clusterDim.y = 1;
+        attr[0].val.clusterDim.z = 1;
+        cfg.attrs = attr;
+        cfg.numAttrs = 1;
+        DQ_CUDA(cudaLaunchKernelEx(&cfg, kern, ma, mb, p));
+    } else {
+        kern<<<sm_count(), kThreads, kSmemBytes, stream>>>(ma, mb, p);
+    }
     DQ_LAUNCH_CHECK();
     return DQMOE_OK;
+}
+
+// CTA pairs halve the weight bytes each SM stages per flop; they pay off once experts have
+// several row tiles. DQMOE_GEMM_PAIR=0/1 overrides the choice (for measurements).
+static bool use_pairs(int n, int E, int quant_mode) {
+    static int forced = -2;
+    if (forced == -2) {
+        const char* env = getenv("DQMOE_GEMM_PAIR");
+        forced = env == nullptr ? -1 : (env[0] == '0' ? 0 : 1);
+    }
+    if (forced >= 0) return forced == 1;
+    // Block mode hands a TMEM buffer back every K block; the cross-CTA hops of a pair lengthen that
+    // round trip (measured: 0.5x), the other modes gain a few percent.
+    return quant_mode != DQMOE_QUANT_FP8_BLOCK && n / E >= 512;
 }
 
 int grouped_gemm(const void* a, const float* a_scale, const void* w, const float* w_scale, const int* offsets,
@@ -721,8 +821,12 @@ int grouped_gemm(const void* a, const float* a_scale, const void* w, const float
     rc = make_map(&mb, w, fp8, uint64_t(E) * p.w_rows, uint64_t(K));
     if (rc != DQMOE_OK) return rc;
 
-#define DQ_GEMM_CASE(FP8, MODE)                                                        \
-    return gated ? launch<FP8, MODE, true>(ma, mb, p, stream) : launch<FP8, MODE, false>(ma, mb, p, stream)
+#define DQ_GEMM_CASE(FP8, MODE)                                                                       \
+    return pair ? (gated ? launch<FP8, MODE, true, true>(ma, mb, p, stream)                            \
+                         : launch<FP8, MODE, false, true>(ma, mb, p, stream))                          \
+                : (gated ? launch<FP8, MODE, true, false>(ma, mb, p, stream)                           \
+                         : launch<FP8, MODE, false, false>(ma, mb, p, stream))
+    const bool pair = use_pairs(n, E, quant_mode);
     switch (quant_mode) {
         case DQMOE_QUANT_NONE: DQ_GEMM_CASE(false, kNone);
         case DQMOE_QUANT_FP8_TENSOR: DQ_GEMM_CASE(true, kTensor);

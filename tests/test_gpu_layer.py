@@ -148,10 +148,15 @@ def test_errors_raise_runtime_error(ops, workspace):
     assert ops.device_status() == 0
 
 
+RAGGED = [0, 1, 127, 128, 129, 0, 300, 5]
+# mean rows per expert >= 512: the non-block modes run on CTA pairs (256-row tiles, odd tile counts included)
+LARGE = [641, 0, 1300, 129]
+
+
+@pytest.mark.parametrize("counts", [RAGGED, LARGE], ids=["ragged", "pairs"])
 @pytest.mark.parametrize("mode,gated", [(0, False), (0, True), (256, True), (512, False), (512, True), (1024, False), (1024, True)])
-def test_grouped_gemm_ragged_groups(ops, mode, gated):
+def test_grouped_gemm_ragged_groups(ops, mode, gated, counts):
     """dqmoe_grouped_gemm alone on ragged expert sizes (0, 1, 127, 128, 129 rows ...)."""
-    counts = [0, 1, 127, 128, 129, 0, 300, 5]
     E, N, K = len(counts), 384, 640
     n = sum(counts)
     g = torch.Generator().manual_seed(mode + gated)
