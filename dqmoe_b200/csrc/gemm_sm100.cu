@@ -160,7 +160,9 @@ __device__ __forceinline__ void ffma2(float& a0, float& a1, uint32_t x0, uint32_
     a1 = r.y;
 }
 
-template <bool kFp8, int kMode, bool kGated, bool kPair>
+// kBox = weight rows per TMA box (two boxes per stage, 2*kBox accumulator columns): 128 for
+// throughput, 64 when a launch would otherwise have fewer tiles than SMs (decode shapes).
+template <bool kFp8, int kMode, bool kGated, bool kPair, int kBox>
 __global__ void __launch_bounds__(kThreads, 1)
 moe_GemmGrouped_GemmUniversal_tcgen05(const __grid_constant__ CUtensorMap tma_a,
                                       const __grid_constant__ CUtensorMap tma_b, const Params p) {
@@ -171,8 +173,12 @@ moe_GemmGrouped_GemmUniversal_tcgen05(const __grid_constant__ CUtensorMap tma_a,
     const int warp = threadIdx.x >> 5;
     const int lane = threadIdx.x & 31;
     constexpr int kBKElems = kFp8 ? kBKBytes : kBKBytes / 2;
-    constexpr int kNumStages = kPair ? kStagesPair : kStages;
-    constexpr int kStageSz = kPair ? kStageBytesPair : kStageBytes;
+    static_assert(kBox == 128 || (kBox == 64 && !kPair && kMode != kBlock), "narrow tiles: single CTA, non-block modes");
+    constexpr int kN = 2 * kBox;                      // accumulator columns of a tile
+    constexpr int kStageSz = kPair ? kStageBytesPair : kABytes + kN * kBKBytes;
+    constexpr int kNumStages = (kStages * kStageBytes) / kStageSz;   // 4 (wide), 6 (pairs, narrow)
+    constexpr int kHalf = kBox / 2;                   // columns of each group owned by one epilogue warpgroup
+    constexpr int kChunks = kBox / 64;                // 32-column chunks per thread and group
     // In a pair, CTA 0 (the leader) issues the MMAs for both and owns the barriers they wait on.
     const uint32_t cta_rank = kPair ? ptx::cluster_ctarank() : 0u;
     const bool leader = cta_rank == 0u;
@@ -269,10 +275,10 @@ moe_GemmGrouped_GemmUniversal_tcgen05(const __grid_constant__ CUtensorMap tma_a,
                         ptx::tma_load_2d_pair(sa, &tma_a, k0, tl.row0, full_leader);
                         ptx::tma_load_2d_pair(sb, &tma_b, k0, leader ? wrow0 : wrow1, full_leader);
                     } else {
-                        ptx::mbar_arrive_expect_tx(&st.full[s], kStageBytes);
+                        ptx::mbar_arrive_expect_tx(&st.full[s], kStageSz);
                         ptx::tma_load_2d(sa, &tma_a, k0, tl.row0, &st.full[s]);
                         ptx::tma_load_2d(sb, &tma_b, k0, wrow0, &st.full[s]);
-                        ptx::tma_load_2d(sb + kBoxRows * kBKBytes, &tma_b, k0, wrow1, &st.full[s]);
+                        ptx::tma_load_2d(sb + kBox * kBKBytes, &tma_b, k0, wrow1, &st.full[s]);
                     }
                     DQ_STAMP(0, it, 1);
                 }
@@ -282,7 +288,7 @@ moe_GemmGrouped_GemmUniversal_tcgen05(const __grid_constant__ CUtensorMap tma_a,
       } else if (warp == 1) {
         // ------------------------------------------------------------ MMA issuer
         if (lane == 0 && leader) {
-            constexpr uint32_t idesc = ptx::make_idesc(kFp8 ? 0u : 1u, kPair ? 2 * kBM : kBM, kUmmaN);
+            constexpr uint32_t idesc = ptx::make_idesc(kFp8 ? 0u : 1u, kPair ? 2 * kBM : kBM, kN);
             // issue one K step; in a pair the same call drives both CTAs' tensor cores
             auto mma_step = [&](uint32_t d_tmem, uint32_t a_addr, uint32_t b_addr, uint32_t accumulate) {
                 if constexpr (kPair)
@@ -432,20 +438,20 @@ moe_GemmGrouped_GemmUniversal_tcgen05(const __grid_constant__ CUtensorMap tma_a,
                 const uint32_t t_buf = t_lane + buf * kUmmaN;
 
                 if constexpr (kGated) {
-                    // columns [h*64, h*64+64) of the gate group and of the value group
+                    // columns [h*kHalf, (h+1)*kHalf) of the gate group and of the value group
                     float row_scale = 1.0f;
                     if constexpr (kMode == kTensor) row_scale = p.sa[0] * p.sb[tl.e];
                     if constexpr (kMode == kChannel) row_scale = p.sa[grow_ld];
                     float amax_local = 0.0f;
 #pragma unroll 1
-                    for (int j = 0; j < 2; ++j) {
+                    for (int j = 0; j < kChunks; ++j) {
                         uint32_t g[32], v[32];
-                        const int c0 = h * 64 + j * 32;  // column inside the 128-wide act tile
+                        const int c0 = h * kHalf + j * 32;  // column inside the kBox-wide act tile
                         ptx::tmem_ld32(t_buf + c0, g);
-                        ptx::tmem_ld32(t_buf + kBoxRows + c0, v);
+                        ptx::tmem_ld32(t_buf + kBox + c0, v);
                         ptx::tmem_wait_ld(g);
                         ptx::tmem_wait_ld(v);
-                        const int col0 = tl.nt * kBoxRows + c0;
+                        const int col0 = tl.nt * kBox + c0;
                         uint32_t packed[16];
 #pragma unroll
                         for (int i = 0; i < 32; i += 2) {
@@ -486,7 +492,7 @@ moe_GemmGrouped_GemmUniversal_tcgen05(const __grid_constant__ CUtensorMap tma_a,
                         if (lane == 0) atomic_max_nonneg(p.amax, m);
                     }
                 } else {
-                    // stage 2: columns h*64 + {0,32} of each of the two 128-column groups
+                    // stage 2: this warpgroup's half of each of the two kBox-column groups
                     float row_scale = 1.0f;
                     if constexpr (kMode == kTensor) row_scale = p.sa[0] * p.sb[tl.e];
                     if constexpr (kMode == kChannel) row_scale = p.sa[grow_ld];
@@ -494,12 +500,12 @@ moe_GemmGrouped_GemmUniversal_tcgen05(const __grid_constant__ CUtensorMap tma_a,
                     if (row_ok && p.dest_to_src != nullptr) orow_idx = p.dest_to_src[grow];
                     __nv_bfloat16* orow = reinterpret_cast<__nv_bfloat16*>(p.out) + size_t(orow_idx) * I_or_H;
 #pragma unroll 1
-                    for (int c = 0; c < 4; ++c) {
+                    for (int c = 0; c < 2 * kChunks; ++c) {
                         uint32_t r[32];
-                        const int tc = (c >> 1) * kBoxRows + h * 64 + (c & 1) * 32;
+                        const int tc = (c / kChunks) * kBox + h * kHalf + (c % kChunks) * 32;
                         ptx::tmem_ld32(t_buf + tc, r);
                         ptx::tmem_wait_ld(r);
-                        const int col0 = tl.nt * kUmmaN + tc;
+                        const int col0 = tl.nt * kN + tc;
                         uint32_t packed[16];
 #pragma unroll
                         for (int i = 0; i < 32; i += 2) {
@@ -709,13 +715,13 @@ static EncodeTiledFn encode_fn() {
 }
 
 // 2-D row-major matrix [rows, cols] of 1- or 2-byte elements, box = 128 bytes x 128 rows, 128B swizzle.
-static int make_map(CUtensorMap* map, const void* base, bool fp8, uint64_t rows, uint64_t cols) {
+static int make_map(CUtensorMap* map, const void* base, bool fp8, uint64_t rows, uint64_t cols, int box_rows) {
     EncodeTiledFn fn = encode_fn();
     if (fn == nullptr) return fail(DQMOE_ERR_CUDA, __FILE__, __LINE__, "cuTensorMapEncodeTiled", "driver entry point not found");
     const uint64_t esz = fp8 ? 1 : 2;
     cuuint64_t gdim[2] = {cols, rows};
     cuuint64_t gstride[1] = {cols * esz};
-    cuuint32_t box[2] = {static_cast<cuuint32_t>(kBKBytes / esz), static_cast<cuuint32_t>(kBoxRows)};
+    cuuint32_t box[2] = {static_cast<cuuint32_t>(kBKBytes / esz), static_cast<cuuint32_t>(box_rows)};
     cuuint32_t estr[2] = {1, 1};
     CUresult r = fn(map, fp8 ? CU_TENSOR_MAP_DATA_TYPE_UINT8 : CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2,
                     const_cast<void*>(base), gdim, gstride, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
@@ -726,9 +732,9 @@ static int make_map(CUtensorMap* map, const void* base, bool fp8, uint64_t rows,
     return DQMOE_OK;
 }
 
-template <bool kFp8, int kMode, bool kGated, bool kPair>
+template <bool kFp8, int kMode, bool kGated, bool kPair, int kBox>
 static int launch(const CUtensorMap& ma, const CUtensorMap& mb, const Params& p, cudaStream_t stream) {
-    auto kern = moe_GemmGrouped_GemmUniversal_tcgen05<kFp8, kMode, kGated, kPair>;
+    auto kern = moe_GemmGrouped_GemmUniversal_tcgen05<kFp8, kMode, kGated, kPair, kBox>;
     static bool configured = false;  // per instantiation
     static int configured_dev = -1;
     int dev = 0;
@@ -791,15 +797,23 @@ int grouped_gemm(const void* a, const float* a_scale, const void* w, const float
     if (gated && quant_mode == DQMOE_QUANT_FP8_BLOCK) DQ_CHECK(out_scale != nullptr);
     if (gated && (quant_mode == DQMOE_QUANT_FP8_TENSOR || quant_mode == DQMOE_QUANT_FP8_CHANNEL)) DQ_CHECK(amax != nullptr);
 
+    // Tile width: 256 accumulator columns, or 128 when the launch would leave SMs without a tile.
+    // The row-tile count is known only on the device; ceil(n/128) + min(E, n) - 1 bounds it.
+    const bool pair = use_pairs(n, E, quant_mode);
+    const int mtiles_max = ceil_div(n, kBM) + (E < n ? E : n) - 1;
+    const int wide_tiles = mtiles_max * (gated ? ceil_div(N, kBoxRows) : ceil_div(N, kUmmaN));
+    const bool narrow = quant_mode != DQMOE_QUANT_FP8_BLOCK && !pair && wide_tiles < 2 * sm_count();
+    const int box = narrow ? 64 : kBoxRows;
+
     Params p;
     p.n_rows = n;
     p.N = N;
     p.K = K;
     p.E = E;
     p.w_rows = gated ? 2 * N : N;
-    p.n_tiles = gated ? ceil_div(N, kBoxRows) : ceil_div(N, kUmmaN);
-    p.tile_w_rows = gated ? kBoxRows : kUmmaN;
-    p.box2_off = gated ? N : kBoxRows;
+    p.n_tiles = gated ? ceil_div(N, box) : ceil_div(N, 2 * box);
+    p.tile_w_rows = gated ? box : 2 * box;
+    p.box2_off = gated ? N : box;
     p.kb_count = ceil_div(K * esz, kBKBytes);
     p.offsets = offsets;
     p.mtile_prefix = mtile_prefix;
@@ -816,24 +830,24 @@ int grouped_gemm(const void* a, const float* a_scale, const void* w, const float
     if (p.status == nullptr) return DQMOE_ERR_CUDA;
 
     CUtensorMap ma, mb;
-    int rc = make_map(&ma, a, fp8, uint64_t(n), uint64_t(K));
+    int rc = make_map(&ma, a, fp8, uint64_t(n), uint64_t(K), kBM);
     if (rc != DQMOE_OK) return rc;
-    rc = make_map(&mb, w, fp8, uint64_t(E) * p.w_rows, uint64_t(K));
+    rc = make_map(&mb, w, fp8, uint64_t(E) * p.w_rows, uint64_t(K), box);
     if (rc != DQMOE_OK) return rc;
 
-#define DQ_GEMM_CASE(FP8, MODE)                                                                       \
-    return pair ? (gated ? launch<FP8, MODE, true, true>(ma, mb, p, stream)                            \
-                         : launch<FP8, MODE, false, true>(ma, mb, p, stream))                          \
-                : (gated ? launch<FP8, MODE, true, false>(ma, mb, p, stream)                           \
-                         : launch<FP8, MODE, false, false>(ma, mb, p, stream))
-    const bool pair = use_pairs(n, E, quant_mode);
+#define DQ_GEMM_LAUNCH(FP8, MODE, PAIR, BOX)                                                 \
+    (gated ? launch<FP8, MODE, true, PAIR, BOX>(ma, mb, p, stream) : launch<FP8, MODE, false, PAIR, BOX>(ma, mb, p, stream))
+#define DQ_GEMM_CASE(FP8, MODE)                                                              \
+    return pair ? DQ_GEMM_LAUNCH(FP8, MODE, true, 128)                                        \
+                : (narrow ? DQ_GEMM_LAUNCH(FP8, MODE, false, 64) : DQ_GEMM_LAUNCH(FP8, MODE, false, 128))
     switch (quant_mode) {
         case DQMOE_QUANT_NONE: DQ_GEMM_CASE(false, kNone);
         case DQMOE_QUANT_FP8_TENSOR: DQ_GEMM_CASE(true, kTensor);
         case DQMOE_QUANT_FP8_CHANNEL: DQ_GEMM_CASE(true, kChannel);
-        default: DQ_GEMM_CASE(true, kBlock);
+        default: return pair ? DQ_GEMM_LAUNCH(true, kBlock, true, 128) : DQ_GEMM_LAUNCH(true, kBlock, false, 128);
     }
 #undef DQ_GEMM_CASE
+#undef DQ_GEMM_LAUNCH
 }
 
 }  // namespace gemm

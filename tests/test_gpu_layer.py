@@ -153,11 +153,17 @@ RAGGED = [0, 1, 127, 128, 129, 0, 300, 5]
 LARGE = [641, 0, 1300, 129]
 
 
-@pytest.mark.parametrize("counts", [RAGGED, LARGE], ids=["ragged", "pairs"])
+# many experts and wide outputs: enough tiles for the 256-column single-CTA kernel (few tiles select 128 columns)
+MANY = [200, 131, 0, 256, 77, 300, 128, 129, 1, 255, 190, 260, 140, 222, 180, 250]
+
+
+@pytest.mark.parametrize("counts,N,K", [(RAGGED, 384, 640), (LARGE, 384, 640), (MANY, 1280, 256)],
+                         ids=["ragged-narrow", "pairs", "many-wide"])
 @pytest.mark.parametrize("mode,gated", [(0, False), (0, True), (256, True), (512, False), (512, True), (1024, False), (1024, True)])
-def test_grouped_gemm_ragged_groups(ops, mode, gated, counts):
-    """dqmoe_grouped_gemm alone on ragged expert sizes (0, 1, 127, 128, 129 rows ...)."""
-    E, N, K = len(counts), 384, 640
+def test_grouped_gemm_ragged_groups(ops, mode, gated, counts, N, K):
+    """dqmoe_grouped_gemm alone on ragged expert sizes (0, 1, 127, 128, 129 rows ...); the three
+    shape sets reach the three tile configurations (128-column, CTA-pair and 256-column tiles)."""
+    E = len(counts)
     n = sum(counts)
     g = torch.Generator().manual_seed(mode + gated)
     a = torch.randn(n, K, generator=g).to(torch.bfloat16)
@@ -188,7 +194,7 @@ def test_grouped_gemm_ragged_groups(ops, mode, gated, counts):
         act = torch.nn.functional.silu(gt) * vl
         if mode == 1024:
             out = torch.zeros(n, N, dtype=torch.float8_e4m3fn, device=DEV)
-            osc = torch.zeros(n, 3, dtype=torch.float32, device=DEV)
+            osc = torch.zeros(n, (N + 127) // 128, dtype=torch.float32, device=DEV)
             ops.grouped_gemm(dev(aq), dev(asc), dev(wq), dev(wsc), off_d, mt, N, mode, True, out, out_scale=osc)
             got = out.cpu().float() * orc._expand(osc.cpu(), n, N)
             rq, rs = orc.quant_block_1x128(act)
@@ -207,4 +213,5 @@ def test_grouped_gemm_ragged_groups(ops, mode, gated, counts):
         ops.grouped_gemm(dev(aq), dev(asc), dev(wq), dev(wsc), off_d, mt, N, mode, False, out)
         got, want = out.cpu().float(), ref
     assert ops.device_status() == 0
-    assert orc.cosine(got, want) >= 0.9999 and orc.max_rel_err(got, want) <= 1e-2
+    # one e4m3 step of the re-quantised output at the largest magnitude is 1/16 of it: the layer tolerance applies
+    assert orc.cosine(got, want) >= 0.9999 and orc.max_rel_err(got, want) <= REL_MAX
