@@ -151,54 +151,123 @@ def launches_per_step(n, mode):
     return sort + 1 + 1 + (1 if mode in (256, 512) else 0) + 1
 
 
-def cpu_baseline(wl, sample_tokens, seed=0, threads=None):
-    """The oracle (torch on the host cores) on a bounded sample of the workload."""
+def config_of(name, wl, world):
+    mode = wl["mode"]
+    return {"workload": f"{name}: {wl['desc']}", "T_per_gpu": wl["T"], "H": wl["H"], "I": wl["I"], "E": wl["E"],
+            "k": wl["k"], "quant": MODE_NAME[mode], "parallelism": f"ep{world}" if world > 1 else "single",
+            "l2": "operands larger than L2 (weights %.2f GB); no flush" % (3.0 * wl["E"] * wl["H"] * wl["I"] * (1 if mode else 2) / 1e9)}
+
+
+def cpu_baseline(wl, sample_tokens, seed=0, steps=1, warmup=0):
+    """The oracle (torch on the host cores) on a bounded sample of the workload: `sample_tokens`
+    tokens and, for workloads with many experts, the first 16 experts only (weights for all 256
+    would take minutes to generate on the host). Inputs are prepared once, the layer call is timed."""
     from oracle import moe_oracle as orc
-    if threads:
-        torch.set_num_threads(threads)
     T = min(sample_tokens, wl["T"])
-    H, I, E, k, mode = wl["H"], wl["I"], wl["E"], wl["k"], wl["mode"]
-    x, logits = synth_inputs(wl, seed, "cpu", T=T)
+    H, I, k, mode = wl["H"], wl["I"], wl["k"], wl["mode"]
+    E = min(wl["E"], 16)
+    sub = dict(wl, E=E)
+    x, logits = synth_inputs(sub, seed, "cpu", T=T)
     idx, _ = orc.route_topk(logits, k, wl["scoring"])
-    # the sample touches only the experts its tokens hit; weights are made for those
-    b, b1 = synth_weights(wl, seed, "cpu")
+    b, b1 = synth_weights(sub, seed, "cpu")
     qs = orc.quantize_inputs(x, b, b1, mode) if mode else None
-    t0 = time.perf_counter()
-    if mode:
-        orc.moe_layer_fp8(*qs, idx, E, mode)
-    else:
-        orc.moe_layer_bf16(x, b, b1, idx, E)
-    dt = time.perf_counter() - t0
+    times = []
+    for i in range(warmup + steps):
+        t0 = time.perf_counter()
+        if mode:
+            orc.moe_layer_fp8(*qs, idx, E, mode)
+        else:
+            orc.moe_layer_bf16(x, b, b1, idx, E)
+        dt = time.perf_counter() - t0
+        if i >= warmup:
+            times.append(dt)
+        if dt > 30 and times:  # keep the whole run within minutes
+            break
+    dt = statistics.mean(times)
     flops = 6.0 * T * k * H * I
     return dict(value=flops / dt / 1e12, unit="TFLOP/s", cores=torch.get_num_threads(), kind="port",
-                sample=f"{T} of {wl['T']} tokens, all {E} experts, one layer call ({dt:.2f} s)",
-                tokens_per_s=T / dt)
+                sample=f"{T} of {wl['T']} tokens, {E} of {wl['E']} experts, {len(times)} layer call(s) of {dt:.2f} s",
+                tokens_per_s=T / dt, steps=len(times))
 
 
 def run_reference(args, wl, rank):
-    """--impl reference: the reference's CPU implementation of the path (the oracle port of its torch code)."""
+    """--impl reference: the reference's CPU implementation of the path (the oracle port of its torch code;
+    the reference's CUDA path cannot be built here), all host threads, a bounded sample per step."""
     if rank != 0:
         return
-    sample = 256 if wl["T"] >= 256 else wl["T"]
-    times = []
-    base = None
-    for i in range(args.warmup + args.steps):
-        base = cpu_baseline(wl, sample)
-        if i >= args.warmup:
-            times.append(base["value"])
-        if i == 0 and float(base["sample"].split("(")[1].split(" s")[0]) > 20:
-            times = [base["value"]]
-            break
-    val = statistics.mean(times)
-    base["value"] = val
-    out = {"impl": "reference", "metric": "moe_layer_fp8_tflops", "value": val, "unit": "TFLOP/s", "n_gpus": args.gpus,
-           "steps": len(times), "warmup": args.warmup, "ms_per_step": None, "higher_is_better": True,
+    base = cpu_baseline(wl, 2048, steps=args.steps, warmup=min(args.warmup, 1))
+    val = base["value"]
+    out = {"impl": "reference", "metric": "moe_layer_fp8_tflops" if wl["mode"] else "moe_layer_bf16_tflops",
+           "value": val, "unit": "TFLOP/s", "n_gpus": args.gpus,
+           "steps": base["steps"], "warmup": min(args.warmup, 1), "ms_per_step": None, "higher_is_better": True,
            "scaling": "weak", "vs_baseline": None, "dtype": "f32 (dequantised e4m3)", "data": "synthetic",
-           "config": {"workload": args.workload, **{k: wl[k] for k in ("T", "H", "I", "E", "k")},
-                      "quant": MODE_NAME[wl["mode"]]},
+           "config": config_of(args.workload, wl, max(args.gpus, 1)),
            "cpu_baseline": base,
            "e2e": {"value": val, "unit": "TFLOP/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0}}
     print(json.dumps(out))
+
+
+def run_decode(args, rank):
+    """--workload c5: decode-shape latency sweep (Mixtral shape, memory-bound). One JSON line with the
+    p50 layer latency and the weight-streaming bandwidth for T in {1,16,64,256}, bf16 and per-tensor FP8."""
+    if rank != 0:
+        return
+    from dqmoe_b200 import ops
+    dev = torch.device("cuda", int(os.environ.get("LOCAL_RANK", "0")))
+    torch.cuda.set_device(dev)
+    H, I, E, k = 4096, 14336, 8, 2
+    wl = dict(H=H, I=I, E=E, k=k)
+    b, b1 = synth_weights(wl, 0, dev)
+    bq, bs = ops.per_tensor_cast_to_fp8(b, per_expert=True)
+    b1q, b1s = ops.per_tensor_cast_to_fp8(b1, per_expert=True)
+    flush = torch.empty(256 << 20, dtype=torch.uint8, device=dev)  # larger than the 126 MB L2
+    pk = peaks()
+    rows = []
+    sampler = ClockSampler(dev.index or 0)
+    sampler.start()
+    for mode in (0, 256):
+        for T in (1, 16, 64, 256):
+            g = torch.Generator(device=dev).manual_seed(T)
+            x = torch.randn(T, H, generator=g, device=dev).to(torch.bfloat16)
+            idx, _ = ops.route_topk(torch.randn(T, E, generator=g, device=dev), k, "softmax")
+            active = int(torch.unique(idx).numel())
+            ws = torch.empty(ops.moe_workspace_bytes(T, H, I, E, k, mode), dtype=torch.uint8, device=dev)
+            d = torch.empty(T, k, H, dtype=torch.bfloat16, device=dev)
+            if mode:
+                aq, as_ = ops.per_tensor_cast_to_fp8(x)
+                call = (aq, as_, bq, bs, b1q, b1s)
+            else:
+                call = (x, None, b, None, b1, None)
+            times = []
+            for i in range(max(args.warmup, 3) + args.steps):
+                flush.zero_()
+                e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                e0.record()
+                ops.moe_forward(*call, d, idx, ws, mode)
+                e1.record()
+                torch.cuda.synchronize()
+                if i >= max(args.warmup, 3):
+                    times.append(e0.elapsed_time(e1))
+            p50 = statistics.median(times)
+            # algorithmic bytes: weights of the experts hit + activations in and out
+            nbytes = active * 3 * H * I * (1 if mode else 2) + T * H * (1 if mode else 2) + T * k * H * 2
+            rows.append({"quant": MODE_NAME[mode], "T": T, "active_experts": active, "p50_us": p50 * 1e3,
+                         "bytes": nbytes, "gbs": nbytes / (p50 * 1e-3) / 1e9,
+                         "frac_of_measured_hbm": nbytes / (p50 * 1e-3) / 1e9 / pk["hbm_gbs"]})
+    clocks = sampler.stop()
+    if ops.device_status() != 0:
+        raise SystemExit("device status non-zero: a kernel's bounded wait gave up; no number reported")
+    head = next(r for r in rows if r["quant"] == "fp8-tensor" and r["T"] == 64)
+    print(json.dumps({
+        "metric": "moe_layer_decode_p50_latency_us", "value": head["p50_us"], "unit": "us", "n_gpus": 1,
+        "steps": args.steps, "warmup": max(args.warmup, 3), "ms_per_step": head["p50_us"] / 1e3,
+        "higher_is_better": False, "scaling": "weak", "vs_baseline": None, "dtype": "e4m3 x e4m3 -> f32", "data": "synthetic",
+        "config": {"workload": "c5: decode-shape sweep, Mixtral shape, T in {1,16,64,256}; headline = fp8-tensor T=64",
+                   "H": H, "I": I, "E": E, "k": k, "l2": "256 MB flush write before every timed call"},
+        "clocks": clocks, "sweep": rows,
+        "roofline": {"bound": "hbm", "achieved": head["gbs"], "peak": pk["hbm_gbs"], "unit": "GB/s",
+                     "frac": head["gbs"] / pk["hbm_gbs"], "traffic": None,
+                     "peak_note": f"of {pk['source']} copy bandwidth; nominal 8000 GB/s"}}))
 
 
 def main():
@@ -206,12 +275,17 @@ def main():
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=20)
     ap.add_argument("--warmup", type=int, default=5)
-    ap.add_argument("--workload", default="c2", choices=sorted(WORKLOADS))
+    ap.add_argument("--workload", default="c2", choices=sorted(WORKLOADS) + ["c5"])
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
     args = ap.parse_args()
-    wl = WORKLOADS[args.workload]
     rank = int(os.environ.get("RANK", "0"))
+    if args.workload == "c5":
+        if args.impl == "reference":
+            args.workload = "c1"  # the CPU path is timed on the CPU-size layer for the decode sweep
+        else:
+            return run_decode(args, rank)
+    wl = WORKLOADS[args.workload]
     world = int(os.environ.get("WORLD_SIZE", "1"))
     local_rank = int(os.environ.get("LOCAL_RANK", "0"))
 
@@ -365,16 +439,14 @@ def main():
         if world > 1:
             dist.destroy_process_group()
         return
-    base = None if args.no_cpu_baseline else cpu_baseline(wl, 256)
+    base = None if args.no_cpu_baseline else cpu_baseline(wl, 2048)
     out = {
         "metric": "moe_layer_fp8_tflops" if mode else "moe_layer_bf16_tflops",
         "value": value, "unit": "TFLOP/s", "n_gpus": world, "steps": args.steps, "warmup": max(args.warmup, 3),
         "ms_per_step": ms_step, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
         "dtype": "e4m3 x e4m3 -> f32" if mode else "bf16 x bf16 -> f32", "data": "synthetic",
         "tokens_per_s": T * world / (ms_step * 1e-3),
-        "config": {"workload": f"{args.workload}: {wl['desc']}", "T_per_gpu": T, "H": H, "I": I, "E": E, "k": k,
-                   "quant": MODE_NAME[mode], "parallelism": f"ep{world}" if world > 1 else "single",
-                   "l2": "operands larger than L2 (weights %.2f GB); no flush" % ((3.0 * E * H * I * (1 if mode else 2)) / 1e9)},
+        "config": config_of(args.workload, wl, world),
         "gpu_launches": launches_per_step(n, mode) * args.steps if world == 1 else None,
         "clocks": clocks, "e2e": e2e, "roofline": roofline, "cpu_baseline": base,
     }
