@@ -1,0 +1,76 @@
+"""Expert-parallel layer on real GPUs (needs >= 2 devices; skipped otherwise): NCCL all-to-all
+dispatch/combine with the CUDA kernels, checked against the single-GPU layer holding all experts."""
+import os
+import sys
+import tempfile
+
+import pytest
+import torch
+import torch.distributed as dist
+import torch.multiprocessing as mp
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+pytestmark = pytest.mark.gpu
+
+
+def _worker(rank, world, init_file, mode, results):
+    sys.path.insert(0, ROOT)
+    sys.path.insert(0, os.path.join(ROOT, "tests"))
+    os.environ.setdefault("NCCL_NVLS_ENABLE", "0")
+    from dqmoe_b200 import ep, ops
+    from helpers import make_inputs
+    from oracle import moe_oracle as orc
+    torch.cuda.set_device(rank)
+    dev = torch.device("cuda", rank)
+    dist.init_process_group("nccl", init_method=f"file://{init_file}", rank=rank, world_size=world, device_id=dev)
+    try:
+        E, T, H, I, k = 8, 300, 512, 384, 2
+        _, b, b1, _, _ = make_inputs(100, T, H, I, E, k, 1.0, 0.05)       # the model, same on every rank
+        a, _, _, _, m_indices = make_inputs(200 + rank, T, H, I, E, k, 1.0, 0.05)
+        if rank == 1:
+            m_indices[3, 0] = -1
+        weights = torch.rand(T, k)
+        lo, hi = ep.expert_range(rank, world, E)
+        if mode == 0:
+            full = (b.to(dev), None, b1.to(dev), None)
+            aq, asc = a.to(dev), None
+        elif mode == 1024:
+            full = (*ops.per_block_cast_to_fp8(b.to(dev)), *ops.per_block_cast_to_fp8(b1.to(dev)))
+            aq, asc = ops.per_token_block_cast_to_fp8(a.to(dev))
+        else:
+            bq, bs = ops.per_channel_cast_to_fp8(b.to(dev))
+            b1q, b1s = ops.per_channel_cast_to_fp8(b1.to(dev))
+            full = (bq, bs.view(E, -1), b1q, b1s.view(E, -1))
+            aq, asc = ops.per_token_cast_to_fp8(a.to(dev))
+            asc = asc.view(-1)
+        # single-GPU reference on this rank: all experts local
+        ws = torch.empty(ops.moe_workspace_bytes(T, H, I, E, k, mode), dtype=torch.uint8, device=dev)
+        ref = torch.zeros(T, k, H, dtype=torch.bfloat16, device=dev)
+        idx = m_indices.to(dev)
+        ops.moe_forward(aq, asc, full[0], full[1], full[2], full[3], ref, idx, ws, mode)
+        shard = tuple(None if t is None else t[lo:hi].contiguous() for t in full)
+        layer = ep.ExpertParallelLayer(E, k, mode, shard, ep.CudaBackend(ops))
+        d = layer.forward(aq, asc, idx)
+        out = layer.forward(aq, asc, idx, weights.to(dev))
+        torch.cuda.synchronize()
+        status = ops.device_status()
+        same = bool(torch.equal(d, ref))  # same kernels, same per-row arithmetic: bit-identical
+        wref = ops.finalize_weighted(ref, weights.to(dev))
+        results[rank] = (status, same, orc.cosine(d.cpu(), ref.cpu()), bool(torch.equal(out, wref)))
+    finally:
+        dist.destroy_process_group()
+
+
+@pytest.mark.parametrize("mode", [0, 512, 1024])
+def test_expert_parallel_matches_single_gpu(mode):
+    if torch.cuda.device_count() < 2:
+        pytest.skip("needs two GPUs")
+    world = 2
+    with tempfile.TemporaryDirectory() as tmp:
+        results = mp.Manager().dict()
+        mp.spawn(_worker, args=(world, os.path.join(tmp, "init"), mode, results), nprocs=world, join=True)
+        for rank in range(world):
+            status, same, cos, wsame = results[rank]
+            assert status == 0
+            assert cos >= 0.9999, (rank, cos)
+            assert same and wsame, (rank, cos)
