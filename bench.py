@@ -42,6 +42,9 @@ WORKLOADS = {
     "c4": dict(T=16384, H=2048, I=768, E=128, k=8, mode=512, scoring="softmax",
                desc="Qwen-MoE-shape channel-wise layer, Zipf(1.1) expert bias"),
 }
+# dram__bytes_read.sum + dram__bytes_write.sum of one fc1 launch, from the ncu capture summarised in
+# profiles/c2_block_fp8_grouped_gemm.md (ncu cannot run inside a timed bench, so the figure is recorded here)
+NCU_FC1_DRAM_BYTES = {"c2": 974.494976e6 + 115.531008e6}
 MODE_NAME = {0: "bf16", 256: "fp8-tensor", 512: "fp8-channel", 1024: "fp8-block"}
 
 
@@ -326,7 +329,7 @@ def main():
         aq, as_ = layer.quantize_activations(x)
 
         def step():
-            layer.forward(aq, as_, idx, weights)
+            layer.forward(aq, as_, idx, None)  # d[T, k, H] like the single-GPU step
     torch.cuda.synchronize()
 
     def barrier():
@@ -430,10 +433,7 @@ def main():
                     "peak_note": ("2 x measured bf16 burst (no FP8 peak was measured); " if mode else "") +
                                  f"of {pk['source']}; nominal dense {'FP8 4500' if mode else 'BF16 2250'} TFLOP/s",
                     "ms_per_launch": fc1_ms, "traffic": None}
-        tr = os.path.join(ROOT, "profiles", "traffic.json")
-        if os.path.exists(tr):
-            with open(tr) as f:
-                roofline["traffic"] = json.load(f).get(args.workload + "_fc1_dram_bytes_per_launch")
+        roofline["traffic"] = NCU_FC1_DRAM_BYTES.get(args.workload)
 
     if rank != 0:
         if world > 1:

@@ -121,8 +121,8 @@ class ExpertParallelLayer:
         counts, offsets, d2s, _ = be.route_sort(m_indices, self.E)
         # 2. counts to the owners; split sizes must reach the host (one small synchronising copy)
         recv_counts = self.exchange_counts(counts)
-        in_splits = send_splits(counts.cpu(), W)
-        out_splits = recv_counts.sum(dim=1).tolist()
+        splits = torch.stack([counts.view(W, -1).sum(dim=1), recv_counts.sum(dim=1)]).cpu()  # the one host sync
+        in_splits, out_splits = splits[0].tolist(), splits[1].tolist()
         n_recv = int(sum(out_splits))
         kept = int(sum(in_splits))
         # 3. dispatch: gather the kept rows (expert-sorted = destination-sorted) and send them
