@@ -215,3 +215,16 @@ def test_grouped_gemm_ragged_groups(ops, mode, gated, counts, N, K):
     assert ops.device_status() == 0
     # one e4m3 step of the re-quantised output at the largest magnitude is 1/16 of it: the layer tolerance applies
     assert orc.cosine(got, want) >= 0.9999 and orc.max_rel_err(got, want) <= REL_MAX
+
+
+def test_profiler_sees_the_kernel_names_the_reference_script_filters_on(ops, workspace):
+    """test/torch_test.py:180-205 times the layer by summing profiler rows whose kernel name contains
+    "GemmUniversal" (bf16, block) or "GemmGrouped" (channel); test/bench.py:149-168 does the matching."""
+    a, b, b1, _, m_indices = make_inputs(3, 64, 256, 128, 4, 2, 1.0, 0.05)
+    with torch.profiler.profile(activities=[torch.profiler.ProfilerActivity.CUDA]) as prof:
+        run_layer(a, b, b1, m_indices, 0, workspace)
+        run_layer(a, b, b1, m_indices, 512, workspace)
+        torch.cuda.synchronize()
+    names = [e.key for e in prof.key_averages()]
+    gemm = [n for n in names if "GemmUniversal" in n and "GemmGrouped" in n]
+    assert gemm, names
