@@ -41,6 +41,14 @@ SIGNATURES = {
     "dqmoe_quant_fp8_tensor": (_c_int, [_ptr, _c_int, _c_i64, _ptr, _ptr, _ptr, _ptr]),
     "dqmoe_quant_fp8_tensor_static": (_c_int, [_ptr, _c_int, _c_i64, _ptr, _ptr, _ptr]),
     "dqmoe_grouped_gemm": (_c_int, [_ptr] * 6 + [_c_int] * 6 + [_ptr] * 5),
+    "dqmoe_grouped_gemm_rows": (_c_int, [_ptr] * 6 + [_c_int] * 5 + [_ptr, _ptr]),
+    "dqmoe_ep_publish_counts": (_c_int, [_ptr, _c_int, _c_int, _c_int, _ptr, _ptr, _c_int, _ptr]),
+    "dqmoe_ep_plan": (_c_int, [_ptr, _ptr, _c_int, _c_int, _c_int, _c_int, _ptr, _ptr, _ptr, _ptr]),
+    "dqmoe_ep_dispatch": (_c_int, [_ptr, _ptr, _c_size, _c_int, _c_int, _c_int, _ptr, _ptr, _ptr, _c_int, _c_int,
+                                   _c_int, _ptr, _ptr, _ptr, _ptr, _ptr, _c_int, _ptr]),
+    "dqmoe_ep_wait": (_c_int, [_ptr, _c_int, _c_int, _c_int, _ptr]),
+    "dqmoe_ep_signal": (_c_int, [_ptr, _c_int, _c_int, _c_int, _c_int, _ptr]),
+    "dqmoe_ep_row_ptrs": (_c_int, [_ptr, _ptr, _c_int, _ptr, _c_int, _c_size, _c_int, _ptr, _ptr]),
     "dqmoe_mtile_prefix": (_c_int, [_ptr, _c_int, _ptr, _ptr]),
     "dqmoe_requant_from_amax": (_c_int, [_ptr, _c_i64, _c_int, _ptr, _c_int, _ptr, _ptr, _ptr]),
 }

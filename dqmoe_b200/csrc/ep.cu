@@ -1,0 +1,303 @@
+// Expert-parallel exchange over peer memory (NVLink P2P loads/stores; no NCCL on the data
+// path, no multicast). Every rank maps the same set of buffers of every other rank
+// ("symmetric" buffers); a layer call is
+//   publish   my per-expert row counts -> every peer's count matrix, then a flag
+//   plan      wait for all count rows; compute where my rows go in each owner's receive
+//             buffer (already grouped by expert there) and my own receive offsets
+//   dispatch  gather my rows (+ scales, + their home slot) straight into the owners' buffers
+//   wait      until every source has signalled its rows
+//   row_ptrs  destination address of each received row's result in its home rank's output
+//   [grouped fc1 / fc2 run on the receive buffer; fc2's epilogue stores through row_ptrs]
+//   signal + wait   results have landed in every home rank
+// Flags carry a per-call epoch, so nothing is reset between calls. Every wait is bounded: a
+// wait that gives up writes the device status word and returns (no trap, no hang).
+// The reference has no multi-GPU path; this extends its layer (csrc/moe_kernels.h:770-892).
+#include "common.cuh"
+
+namespace dq {
+namespace ep {
+
+constexpr int kMaxRanks = 8;
+constexpr int kMaxExperts = 1024;
+constexpr long long kWaitLimit = 20000000000LL;  // cycles (~10 s): peers may be late on the host side
+
+struct Peers {
+    void* p[kMaxRanks];
+};
+
+__device__ __forceinline__ int ld_acquire_sys(const int* p) {
+    int v;
+    asm volatile("ld.acquire.sys.global.s32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+    return v;
+}
+__device__ __forceinline__ void st_release_sys(int* p, int v) {
+    asm volatile("st.release.sys.global.s32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
+}
+
+// bounded wait until flag == epoch; false (and status written) when it gives up
+__device__ bool wait_flag(const int* flag, int epoch, int* status, int code) {
+    const long long t0 = clock64();
+    unsigned spins = 0;
+    while (ld_acquire_sys(flag) != epoch) {
+        if (((++spins) & 0x3f) == 0) {
+            __nanosleep(200);
+            if (clock64() - t0 > kWaitLimit) {
+                if (status != nullptr) {
+                    *reinterpret_cast<volatile int*>(status) = code;
+                    __threadfence_system();
+                }
+                return false;
+            }
+        }
+    }
+    return true;
+}
+
+// flags: int[3][kMaxRanks] per rank: [phase][source rank]
+__global__ void __launch_bounds__(256) publish_counts_kernel(const int* __restrict__ counts, int E, int me, int W,
+                                                             Peers cnt, Peers flags, int epoch) {
+    for (int p = 0; p < W; ++p) {
+        int* dst = static_cast<int*>(cnt.p[p]) + size_t(me) * E;
+        for (int e = threadIdx.x; e < E; e += blockDim.x) dst[e] = counts[e];
+    }
+    __threadfence_system();
+    __syncthreads();
+    if (threadIdx.x < W) st_release_sys(static_cast<int*>(flags.p[threadIdx.x]) + 0 * kMaxRanks + me, epoch);
+}
+
+// One block. cnt: my copy of the count matrix [W][E]. Outputs (all local):
+//   send_base[E]      row in the owner's receive buffer where my rows of expert e start
+//   rx_offsets[El+1]  first received row of each of my experts (sum over sources), [El] = rows received
+//   rx_mtiles[El+1]   cumulative 128-row tiles of my experts
+__global__ void __launch_bounds__(256) plan_kernel(const int* __restrict__ cnt, const int* __restrict__ my_flags,
+                                                   int E, int me, int W, int epoch, int* __restrict__ send_base,
+                                                   int* __restrict__ rx_offsets, int* __restrict__ rx_mtiles,
+                                                   int* status) {
+    __shared__ int s_tot[kMaxExperts];
+    __shared__ int s_before[kMaxExperts];
+    __shared__ int s_ok;
+    if (threadIdx.x == 0) s_ok = 1;
+    __syncthreads();
+    if (threadIdx.x < W) {
+        if (!wait_flag(my_flags + 0 * kMaxRanks + threadIdx.x, epoch, status, 201)) s_ok = 0;
+    }
+    __syncthreads();
+    if (!s_ok) return;
+    const int El = E / W;
+    for (int e = threadIdx.x; e < E; e += blockDim.x) {
+        int tot = 0, before = 0;
+        for (int s = 0; s < W; ++s) {
+            const int c = cnt[size_t(s) * E + e];
+            if (s < me) before += c;
+            tot += c;
+        }
+        s_tot[e] = tot;
+        s_before[e] = before;
+    }
+    __syncthreads();
+    if (threadIdx.x < W) {  // one thread per owner rank: running base over its experts
+        const int d = threadIdx.x;
+        int run = 0, tiles = 0;
+        for (int el = 0; el < El; ++el) {
+            const int e = d * El + el;
+            send_base[e] = run + s_before[e];
+            if (d == me) {
+                rx_offsets[el] = run;
+                rx_mtiles[el] = tiles;
+            }
+            run += s_tot[e];
+            tiles += (s_tot[e] + 127) / 128;
+        }
+        if (d == me) {
+            rx_offsets[El] = run;
+            rx_mtiles[El] = tiles;
+        }
+    }
+}
+
+__device__ __forceinline__ void copy_vecs(const uint8_t* __restrict__ src, uint8_t* dst, int vecs, int lane) {
+    int i = lane;
+    for (; i + 96 < vecs; i += 128) {
+        const Vec16 a = ld_nc16(src + size_t(i) * 16), b = ld_nc16(src + size_t(i + 32) * 16);
+        const Vec16 c = ld_nc16(src + size_t(i + 64) * 16), d = ld_nc16(src + size_t(i + 96) * 16);
+        st16(dst + size_t(i) * 16, a);
+        st16(dst + size_t(i + 32) * 16, b);
+        st16(dst + size_t(i + 64) * 16, c);
+        st16(dst + size_t(i + 96) * 16, d);
+    }
+    for (; i < vecs; i += 32) st16(dst + size_t(i) * 16, ld_nc16(src + size_t(i) * 16));
+}
+
+// One warp per expert-sorted local row i: a[dest_to_src[i] / k] -> owner's receive buffer.
+__global__ void __launch_bounds__(256) dispatch_kernel(const uint8_t* __restrict__ a, const float* __restrict__ a_scale,
+                                                       int row_vecs, int scale_cols, int k,
+                                                       const int* __restrict__ offsets /*[E+1] local sort*/,
+                                                       const int* __restrict__ dest_to_src,
+                                                       const int* __restrict__ send_base, int E, int me, int W,
+                                                       Peers rx_rows, Peers rx_scale, Peers rx_home, Peers flags,
+                                                       int* done_counter, int epoch) {
+    __shared__ int s_off[kMaxExperts + 1];
+    for (int e = threadIdx.x; e <= E; e += blockDim.x) s_off[e] = offsets[e];
+    __syncthreads();
+    const int kept = s_off[E];
+    const int El = E / W;
+    const int lane = threadIdx.x & 31;
+    const int warps = gridDim.x * (blockDim.x >> 5);
+    for (int i = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5); i < kept; i += warps) {
+        int lo = 0, hi = E;  // expert of sorted row i: last e with s_off[e] <= i
+        while (hi - lo > 1) {
+            const int mid = (lo + hi) >> 1;
+            if (s_off[mid] <= i) lo = mid; else hi = mid;
+        }
+        const int e = lo;
+        const int owner = e / El;
+        const size_t dst_row = size_t(send_base[e] + (i - s_off[e]));
+        const int slot = dest_to_src[i];
+        const size_t src_row = size_t(slot / k);
+        copy_vecs(a + src_row * row_vecs * 16, static_cast<uint8_t*>(rx_rows.p[owner]) + dst_row * row_vecs * 16,
+                  row_vecs, lane);
+        if (scale_cols > 0) {
+            float* sd = static_cast<float*>(rx_scale.p[owner]) + dst_row * scale_cols;
+            for (int c = lane; c < scale_cols; c += 32) sd[c] = a_scale[src_row * scale_cols + c];
+        }
+        // home of the result: (source rank, slot t*k+j) packed as rank * 2^27 + slot (slot < 2^27)
+        if (lane == 0) static_cast<int*>(rx_home.p[owner])[dst_row] = (me << 27) | slot;
+    }
+    // all blocks done -> tell every owner that my rows have landed
+    __threadfence_system();
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        const int prev = atomicAdd(done_counter, 1);
+        if (prev == int(gridDim.x) - 1) {
+            *done_counter = 0;
+            __threadfence_system();
+            for (int p = 0; p < W; ++p) st_release_sys(static_cast<int*>(flags.p[p]) + 1 * kMaxRanks + me, epoch);
+        }
+    }
+}
+
+__global__ void wait_kernel(const int* __restrict__ my_flags, int phase, int W, int epoch, int* status) {
+    if (threadIdx.x < W) wait_flag(my_flags + phase * kMaxRanks + threadIdx.x, epoch, status, 210 + phase);
+}
+
+__global__ void signal_kernel(Peers flags, int phase, int me, int W, int epoch) {
+    __threadfence_system();
+    if (threadIdx.x < W) st_release_sys(static_cast<int*>(flags.p[threadIdx.x]) + phase * kMaxRanks + me, epoch);
+}
+
+// row_dst[r] = address of the home output row of received row r (0 beyond the received rows)
+__global__ void __launch_bounds__(256) row_ptrs_kernel(const int* __restrict__ rx_home, const int* __restrict__ rx_offsets,
+                                                       int El, Peers d_out, size_t out_row_bytes, int cap,
+                                                       unsigned long long* __restrict__ row_dst) {
+    const int n_recv = rx_offsets[El];
+    for (int r = blockIdx.x * blockDim.x + threadIdx.x; r < cap; r += gridDim.x * blockDim.x) {
+        unsigned long long ptr = 0;
+        if (r < n_recv) {
+            const int h = rx_home[r];
+            ptr = reinterpret_cast<unsigned long long>(static_cast<uint8_t*>(d_out.p[h >> 27]) +
+                                                       size_t(h & ((1 << 27) - 1)) * out_row_bytes);
+        }
+        row_dst[r] = ptr;
+    }
+}
+
+static int make_peers(Peers* out, const void* const* ptrs, int W) {
+    DQ_CHECK(W >= 1 && W <= kMaxRanks && ptrs != nullptr);
+    for (int i = 0; i < kMaxRanks; ++i) out->p[i] = i < W ? const_cast<void*>(ptrs[i]) : nullptr;
+    for (int i = 0; i < W; ++i) DQ_CHECK(out->p[i] != nullptr);
+    return DQMOE_OK;
+}
+
+}  // namespace ep
+}  // namespace dq
+
+using namespace dq;
+
+extern "C" {
+
+int dqmoe_ep_publish_counts(const int32_t* counts, int E, int me, int W, const void* const* cnt_ptrs,
+                            const void* const* flag_ptrs, int epoch, dqmoe_stream_t stream) {
+    DQ_CHECK(counts != nullptr && E > 0 && E <= ep::kMaxExperts && me >= 0 && me < W && E % W == 0);
+    ep::Peers cnt, flags;
+    int rc = ep::make_peers(&cnt, cnt_ptrs, W);
+    if (rc != DQMOE_OK) return rc;
+    rc = ep::make_peers(&flags, flag_ptrs, W);
+    if (rc != DQMOE_OK) return rc;
+    ep::publish_counts_kernel<<<1, 256, 0, static_cast<cudaStream_t>(stream)>>>(counts, E, me, W, cnt, flags, epoch);
+    DQ_LAUNCH_CHECK();
+    return DQMOE_OK;
+}
+
+int dqmoe_ep_plan(const int32_t* cnt, const int32_t* my_flags, int E, int me, int W, int epoch, int32_t* send_base,
+                  int32_t* rx_offsets, int32_t* rx_mtiles, dqmoe_stream_t stream) {
+    DQ_CHECK(cnt != nullptr && my_flags != nullptr && send_base != nullptr && rx_offsets != nullptr && rx_mtiles != nullptr);
+    DQ_CHECK(E > 0 && E <= ep::kMaxExperts && W >= 1 && W <= ep::kMaxRanks && me >= 0 && me < W && E % W == 0);
+    ep::plan_kernel<<<1, 256, 0, static_cast<cudaStream_t>(stream)>>>(cnt, my_flags, E, me, W, epoch, send_base,
+                                                                      rx_offsets, rx_mtiles, device_status_word());
+    DQ_LAUNCH_CHECK();
+    return DQMOE_OK;
+}
+
+int dqmoe_ep_dispatch(const void* a, const float* a_scale, size_t row_bytes, int scale_cols, int k, int n,
+                      const int32_t* offsets, const int32_t* dest_to_src, const int32_t* send_base, int E, int me,
+                      int W, const void* const* rx_rows, const void* const* rx_scale, const void* const* rx_home,
+                      const void* const* flag_ptrs, int32_t* done_counter, int epoch, dqmoe_stream_t stream) {
+    DQ_CHECK(a != nullptr && offsets != nullptr && dest_to_src != nullptr && send_base != nullptr && done_counter != nullptr);
+    DQ_CHECK(row_bytes % 16 == 0 && row_bytes > 0 && k > 0 && n >= 0 && scale_cols >= 0);
+    DQ_CHECK(E > 0 && E <= ep::kMaxExperts && me >= 0 && me < W && E % W == 0);
+    DQ_CHECK(int64_t(n) < (int64_t(1) << 27));
+    ep::Peers rows, scale, home, flags;
+    int rc = ep::make_peers(&rows, rx_rows, W);
+    if (rc == DQMOE_OK) rc = ep::make_peers(&home, rx_home, W);
+    if (rc == DQMOE_OK) rc = ep::make_peers(&flags, flag_ptrs, W);
+    if (rc != DQMOE_OK) return rc;
+    if (scale_cols > 0) {
+        DQ_CHECK(a_scale != nullptr);
+        rc = ep::make_peers(&scale, rx_scale, W);
+        if (rc != DQMOE_OK) return rc;
+    } else {
+        for (int i = 0; i < ep::kMaxRanks; ++i) scale.p[i] = nullptr;
+    }
+    const int want = (n + 7) / 8;
+    const int cap = sm_count() * 8;
+    const int grid = want < 1 ? 1 : (want < cap ? want : cap);
+    ep::dispatch_kernel<<<grid, 256, 0, static_cast<cudaStream_t>(stream)>>>(
+        static_cast<const uint8_t*>(a), a_scale, int(row_bytes / 16), scale_cols, k, offsets, dest_to_src, send_base, E,
+        me, W, rows, scale, home, flags, done_counter, epoch);
+    DQ_LAUNCH_CHECK();
+    return DQMOE_OK;
+}
+
+int dqmoe_ep_wait(const int32_t* my_flags, int phase, int W, int epoch, dqmoe_stream_t stream) {
+    DQ_CHECK(my_flags != nullptr && phase >= 0 && phase < 3 && W >= 1 && W <= ep::kMaxRanks);
+    ep::wait_kernel<<<1, 32, 0, static_cast<cudaStream_t>(stream)>>>(my_flags, phase, W, epoch, device_status_word());
+    DQ_LAUNCH_CHECK();
+    return DQMOE_OK;
+}
+
+int dqmoe_ep_signal(const void* const* flag_ptrs, int phase, int me, int W, int epoch, dqmoe_stream_t stream) {
+    DQ_CHECK(phase >= 0 && phase < 3 && me >= 0 && me < W);
+    ep::Peers flags;
+    const int rc = ep::make_peers(&flags, flag_ptrs, W);
+    if (rc != DQMOE_OK) return rc;
+    ep::signal_kernel<<<1, 32, 0, static_cast<cudaStream_t>(stream)>>>(flags, phase, me, W, epoch);
+    DQ_LAUNCH_CHECK();
+    return DQMOE_OK;
+}
+
+int dqmoe_ep_row_ptrs(const int32_t* rx_home, const int32_t* rx_offsets, int E_local, const void* const* d_out_ptrs,
+                      int W, size_t out_row_bytes, int cap, void* row_dst, dqmoe_stream_t stream) {
+    DQ_CHECK(rx_home != nullptr && rx_offsets != nullptr && row_dst != nullptr && E_local > 0 && cap >= 0);
+    if (cap == 0) return DQMOE_OK;
+    ep::Peers d_out;
+    const int rc = ep::make_peers(&d_out, d_out_ptrs, W);
+    if (rc != DQMOE_OK) return rc;
+    const int want = (cap + 255) / 256;
+    const int lim = sm_count() * 4;
+    ep::row_ptrs_kernel<<<want < lim ? want : lim, 256, 0, static_cast<cudaStream_t>(stream)>>>(
+        rx_home, rx_offsets, E_local, d_out, out_row_bytes, cap, static_cast<unsigned long long*>(row_dst));
+    DQ_LAUNCH_CHECK();
+    return DQMOE_OK;
+}
+
+}  // extern "C"

@@ -63,6 +63,7 @@ struct Params {
     float* out_scale;         // stage 1 block mode: [n, ceil(I/128)]
     float* amax;              // stage 1 channel: [n]; tensor: [1]
     const int* dest_to_src;   // stage 2 scatter map or nullptr
+    const unsigned long long* row_dst;  // stage 2: address of each row's output row (may be peer memory), or nullptr
     int* status;              // host-mapped status word
 #ifdef DQ_TRACE
     long long* trace;         // [3 roles][kTraceEvents][4] clock64 stamps of CTA 0 (diagnostic builds only)
@@ -499,6 +500,10 @@ moe_GemmGrouped_GemmUniversal_tcgen05(const __grid_constant__ CUtensorMap tma_a,
                     int orow_idx = grow;
                     if (row_ok && p.dest_to_src != nullptr) orow_idx = p.dest_to_src[grow];
                     __nv_bfloat16* orow = reinterpret_cast<__nv_bfloat16*>(p.out) + size_t(orow_idx) * I_or_H;
+                    if (p.row_dst != nullptr) {  // rows go to explicit addresses (expert parallel: the home rank's output)
+                        orow = row_ok ? reinterpret_cast<__nv_bfloat16*>(p.row_dst[grow]) : nullptr;
+                        orow_idx = orow != nullptr ? 0 : -1;
+                    }
 #pragma unroll 1
                     for (int c = 0; c < 2 * kChunks; ++c) {
                         uint32_t r[32];
@@ -650,8 +655,12 @@ moe_GemmGrouped_GemmUniversal_tcgen05(const __grid_constant__ CUtensorMap tma_a,
                 } else {
                     int orow_idx = grow;
                     if (row_ok && p.dest_to_src != nullptr) orow_idx = p.dest_to_src[grow];
+                    __nv_bfloat16* orow = reinterpret_cast<__nv_bfloat16*>(p.out) + size_t(orow_idx) * I_or_H;
+                    if (p.row_dst != nullptr) {
+                        orow = row_ok ? reinterpret_cast<__nv_bfloat16*>(p.row_dst[grow]) : nullptr;
+                        orow_idx = orow != nullptr ? 0 : -1;
+                    }
                     if (row_ok && orow_idx >= 0) {
-                        __nv_bfloat16* orow = reinterpret_cast<__nv_bfloat16*>(p.out) + size_t(orow_idx) * I_or_H;
 #pragma unroll
                         for (int c = 0; c < 4; ++c) {
                             const int col0 = tl.nt * kUmmaN + (c >> 1) * kBoxRows + h * 64 + (c & 1) * 32;
@@ -782,7 +791,7 @@ static bool use_pairs(int n, int E, int quant_mode) {
 
 int grouped_gemm(const void* a, const float* a_scale, const void* w, const float* w_scale, const int* offsets,
                  const int* mtile_prefix, int n, int N, int K, int E, int quant_mode, int gated, void* out,
-                 float* out_scale, float* amax, const int* dest_to_src, cudaStream_t stream) {
+                 float* out_scale, float* amax, const int* dest_to_src, const void* row_dst, cudaStream_t stream) {
     DQ_CHECK(quant_mode == DQMOE_QUANT_NONE || quant_mode == DQMOE_QUANT_FP8_TENSOR ||
              quant_mode == DQMOE_QUANT_FP8_CHANNEL || quant_mode == DQMOE_QUANT_FP8_BLOCK);
     DQ_CHECK(n >= 0 && N > 0 && K > 0 && E > 0 && E <= kMaxExperts);
@@ -791,8 +800,9 @@ int grouped_gemm(const void* a, const float* a_scale, const void* w, const float
     const int esz = fp8 ? 1 : 2;
     DQ_CHECK_FMT((size_t(K) * esz) % 16 == 0, "K=%d: rows must be a multiple of 16 bytes", K);
     DQ_CHECK_FMT(N % (gated && quant_mode == DQMOE_QUANT_FP8_BLOCK ? 16 : 8) == 0, "N=%d: output rows must be 16-byte vectors", N);
-    DQ_CHECK(is_aligned(a, 16) && is_aligned(w, 16) && is_aligned(out, 16));
-    DQ_CHECK(a != nullptr && w != nullptr && out != nullptr && offsets != nullptr && mtile_prefix != nullptr);
+    DQ_CHECK(is_aligned(a, 16) && is_aligned(w, 16) && is_aligned(out, 16) && is_aligned(row_dst, 8));
+    DQ_CHECK(a != nullptr && w != nullptr && (out != nullptr || row_dst != nullptr) && offsets != nullptr && mtile_prefix != nullptr);
+    DQ_CHECK(row_dst == nullptr || !gated);
     if (fp8) DQ_CHECK(a_scale != nullptr && w_scale != nullptr);
     if (gated && quant_mode == DQMOE_QUANT_FP8_BLOCK) DQ_CHECK(out_scale != nullptr);
     if (gated && (quant_mode == DQMOE_QUANT_FP8_TENSOR || quant_mode == DQMOE_QUANT_FP8_CHANNEL)) DQ_CHECK(amax != nullptr);
@@ -823,6 +833,7 @@ int grouped_gemm(const void* a, const float* a_scale, const void* w, const float
     p.out_scale = out_scale;
     p.amax = amax;
     p.dest_to_src = dest_to_src;
+    p.row_dst = static_cast<const unsigned long long*>(row_dst);
     p.status = device_status_word();
 #ifdef DQ_TRACE
     p.trace = g_trace;
@@ -862,5 +873,12 @@ extern "C" int dqmoe_grouped_gemm(const void* a, const float* a_scale, const voi
                                   int quant_mode, int gated, void* out, float* out_scale, float* amax,
                                   const int32_t* dest_to_src, dqmoe_stream_t stream) {
     return dq::gemm::grouped_gemm(a, a_scale, w, w_scale, offsets, mtile_prefix, n, N, K, E, quant_mode, gated, out,
-                                  out_scale, amax, dest_to_src, static_cast<cudaStream_t>(stream));
+                                  out_scale, amax, dest_to_src, nullptr, static_cast<cudaStream_t>(stream));
+}
+
+extern "C" int dqmoe_grouped_gemm_rows(const void* a, const float* a_scale, const void* w, const float* w_scale,
+                                       const int32_t* offsets, const int32_t* mtile_prefix, int n, int N, int K, int E,
+                                       int quant_mode, const void* row_dst, dqmoe_stream_t stream) {
+    return dq::gemm::grouped_gemm(a, a_scale, w, w_scale, offsets, mtile_prefix, n, N, K, E, quant_mode, 0, nullptr,
+                                  nullptr, nullptr, nullptr, row_dst, static_cast<cudaStream_t>(stream));
 }

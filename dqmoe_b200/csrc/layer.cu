@@ -17,7 +17,7 @@ int route_sort(const int* ids, int n, int E, int* counts, int* offsets, int* mti
 namespace gemm {
 int grouped_gemm(const void* a, const float* a_scale, const void* w, const float* w_scale, const int* offsets,
                  const int* mtile_prefix, int n, int N, int K, int E, int quant_mode, int gated, void* out,
-                 float* out_scale, float* amax, const int* dest_to_src, cudaStream_t stream);
+                 float* out_scale, float* amax, const int* dest_to_src, const void* row_dst, cudaStream_t stream);
 }  // namespace gemm
 
 namespace layer {
@@ -150,7 +150,7 @@ int dqmoe_moe_forward(const void* a, const float* a_scale, const void* b, const 
         DQ_CUDA(cudaMemsetAsync(amax, 0, amax_bytes, stream));
     }
     rc = gemm::grouped_gemm(perm_a, sa1, b, b_scale, offsets, mtile_prefix, n, I, H, E, quant_mode, 1,
-                            two_pass ? act_bf16 : act, act_scale, amax, nullptr, stream);
+                            two_pass ? act_bf16 : act, act_scale, amax, nullptr, nullptr, stream);
     if (rc != DQMOE_OK) return rc;
     if (two_pass) {
         rc = dqmoe_requant_from_amax(act_bf16, n, I, amax, quant_mode == DQMOE_QUANT_FP8_CHANNEL ? 1 : 0, act,
@@ -158,7 +158,7 @@ int dqmoe_moe_forward(const void* a, const float* a_scale, const void* b, const 
         if (rc != DQMOE_OK) return rc;
     }
     rc = gemm::grouped_gemm(act, act_scale, b1, b1_scale, offsets, mtile_prefix, n, H, I, E, quant_mode, 0, d, nullptr,
-                            nullptr, dest_to_src, stream);
+                            nullptr, dest_to_src, nullptr, stream);
     return rc;
 }
 

@@ -178,7 +178,14 @@ class ExpertParallelMoE:
         else:
             raise RuntimeError("[ASSERT FAILED] ep.py  Condition: mode in (0, 512, 1024)")
         del b, b1
-        self.layer = ExpertParallelLayer(E, wl["k"], mode, wq, CudaBackend(ops), group)
+        # exchange over peer memory where it is built (bf16, block FP8); DQMOE_EP_IMPL=nccl selects the collectives
+        import os
+        use_peer = mode in (0, 1024) and os.environ.get("DQMOE_EP_IMPL", "peer") == "peer" and world <= 8
+        if use_peer:
+            self.layer = PeerExpertParallelLayer(wl["T"], H, I, E, wl["k"], mode, wq, ops, group)
+        else:
+            self.layer = ExpertParallelLayer(E, wl["k"], mode, wq, CudaBackend(ops), group)
+        self.impl = "peer" if use_peer else "nccl"
 
     def quantize_activations(self, x):
         if self.mode == 1024:
@@ -190,3 +197,116 @@ class ExpertParallelMoE:
 
     def forward(self, aq, a_scale, idx, weights):
         return self.layer.forward(aq, a_scale, idx, weights)
+
+
+class PeerExpertParallelLayer:
+    """Expert-parallel layer whose exchange runs over peer-mapped memory instead of collectives.
+
+    Same partitioning as ExpertParallelLayer. Every rank allocates one symmetric buffer
+    (torch.distributed._symmetric_memory: the same allocation mapped into every rank of the node)
+    holding the count matrix, flags, the receive buffers and the output d[T, k, H]. A call then is
+    a fixed sequence of kernels on one stream with no host synchronisation and no collective:
+    sort -> publish counts -> plan -> dispatch (rows written straight into the owners' receive
+    buffers, already grouped by expert) -> wait -> grouped fc1 -> grouped fc2 whose epilogue stores
+    every result row directly into its home rank's d (NVLink stores) -> signal -> wait.
+    Block FP8 and bf16 modes (the per-row re-quantisation pass of channel mode needs the received
+    row count on the host; use ExpertParallelLayer for it). The returned tensor aliases the
+    symmetric output buffer and is overwritten by the next call.
+    """
+
+    def __init__(self, T: int, H: int, I: int, E: int, k: int, mode: int, weights_q, ops, group=None,
+                 capacity_rows: Optional[int] = None):
+        import ctypes
+        import os
+        os.environ.setdefault("TORCH_SYMM_MEM_DISABLE_MULTICAST", "1")  # plain peer loads/stores only
+        import torch.distributed._symmetric_memory as symm_mem
+        from . import _lib
+        if mode not in (0, 1024):
+            raise RuntimeError("[ASSERT FAILED] ep.py  Condition: mode in (0, 1024)  Info: peer exchange supports bf16 and block FP8")
+        self.ops, self.lib, self.check, self.ct = ops, _lib.load(), _lib.check, ctypes
+        self.group = group if group is not None else dist.group.WORLD
+        self.W, self.me = dist.get_world_size(self.group), dist.get_rank(self.group)
+        if self.W > 8:
+            raise RuntimeError("[ASSERT FAILED] ep.py  Condition: world <= 8")
+        self.T, self.H, self.I, self.E, self.k, self.mode = T, H, I, E, k, mode
+        self.lo, self.hi = expert_range(self.me, self.W, E)
+        self.El = self.hi - self.lo
+        self.weights_q = weights_q
+        self.esz = 1 if mode else 2
+        self.n = T * k
+        self.cap = capacity_rows if capacity_rows is not None else self.W * self.n  # worst case: every row comes here
+        self.scale_cols = (H + 127) // 128 if mode == 1024 else 0
+        dev = torch.device("cuda", torch.cuda.current_device())
+        self.dev = dev
+
+        def up(x):
+            return (x + 255) // 256 * 256
+        off, self.off = 0, {}
+        for name, nbytes in (("cnt", self.W * E * 4), ("flags", 3 * 8 * 4), ("rx_rows", self.cap * H * self.esz),
+                             ("rx_scale", self.cap * max(self.scale_cols, 1) * 4), ("rx_home", self.cap * 4),
+                             ("d_out", self.n * H * 2)):
+            self.off[name] = off
+            off += up(nbytes)
+        self.sym = symm_mem.empty(off, dtype=torch.uint8, device=dev)
+        self.sym.zero_()
+        self.handle = symm_mem.rendezvous(self.sym, self.group)
+        bases = [int(p) for p in self.handle.buffer_ptrs]
+        self._ptr_arrays = {}
+        for name in self.off:
+            arr = (ctypes.c_void_p * self.W)(*[b + self.off[name] for b in bases])
+            self._ptr_arrays[name] = arr
+        self.local = {name: self.sym.data_ptr() + o for name, o in self.off.items()}
+        self.send_base = torch.zeros(E, dtype=torch.int32, device=dev)
+        self.rx_offsets = torch.zeros(self.El + 1, dtype=torch.int32, device=dev)
+        self.rx_mtiles = torch.zeros(self.El + 1, dtype=torch.int32, device=dev)
+        self.done = torch.zeros(1, dtype=torch.int32, device=dev)
+        self.row_dst = torch.zeros(self.cap, dtype=torch.int64, device=dev)
+        self.act = torch.empty(self.cap * I * self.esz, dtype=torch.uint8, device=dev)
+        self.act_scale = torch.empty(self.cap * ((I + 127) // 128), dtype=torch.float32, device=dev)
+        self.d_out = self.sym[self.off["d_out"]:self.off["d_out"] + self.n * H * 2].view(torch.bfloat16).view(T, k, H)
+        self.epoch = 0
+        torch.cuda.synchronize()
+        dist.barrier(self.group)  # every rank's flags are zero before anyone publishes
+
+    def forward(self, a: torch.Tensor, a_scale: Optional[torch.Tensor], m_indices: torch.Tensor,
+                route_weights: Optional[torch.Tensor] = None, zero_dropped: bool = False) -> torch.Tensor:
+        ct, lib, ops = self.ct, self.lib, self.ops
+        W, me, E, El, H, I, k = self.W, self.me, self.E, self.El, self.H, self.I, self.k
+        if tuple(a.shape) != (self.T, H) or tuple(m_indices.shape) != (self.T, k):
+            raise RuntimeError("[ASSERT FAILED] ep.py  Condition: a is [T, H] and m_indices is [T, k] of the sizes given at construction")
+        self.epoch += 1
+        ep_ = self.epoch
+        stream = ct.c_void_p(torch.cuda.current_stream(self.dev).cuda_stream)
+        P = self._ptr_arrays
+        vp = ct.c_void_p
+        if zero_dropped:
+            self.d_out.zero_()
+        counts, offsets, d2s, _ = ops.route_sort(m_indices, E)
+        self.check(lib.dqmoe_ep_publish_counts(vp(counts.data_ptr()), E, me, W, P["cnt"], P["flags"], ep_, stream))
+        self.check(lib.dqmoe_ep_plan(vp(self.local["cnt"]), vp(self.local["flags"]), E, me, W, ep_,
+                                     vp(self.send_base.data_ptr()), vp(self.rx_offsets.data_ptr()),
+                                     vp(self.rx_mtiles.data_ptr()), stream))
+        sc_ptr = vp(a_scale.data_ptr()) if self.scale_cols else None
+        self.check(lib.dqmoe_ep_dispatch(vp(a.data_ptr()), sc_ptr, H * self.esz, self.scale_cols, k, self.n,
+                                         vp(offsets.data_ptr()), vp(d2s.data_ptr()), vp(self.send_base.data_ptr()),
+                                         E, me, W, P["rx_rows"], P["rx_scale"], P["rx_home"], P["flags"],
+                                         vp(self.done.data_ptr()), ep_, stream))
+        self.check(lib.dqmoe_ep_wait(vp(self.local["flags"]), 1, W, ep_, stream))
+        self.check(lib.dqmoe_ep_row_ptrs(vp(self.local["rx_home"]), vp(self.rx_offsets.data_ptr()), El, P["d_out"], W,
+                                         H * 2, self.cap, vp(self.row_dst.data_ptr()), stream))
+        b, bs, b1, b1s = self.weights_q
+        sp = lambda t: None if t is None else vp(t.data_ptr())
+        rx_scale = vp(self.local["rx_scale"]) if self.scale_cols else None
+        self.check(lib.dqmoe_grouped_gemm(vp(self.local["rx_rows"]), rx_scale, vp(b.data_ptr()), sp(bs),
+                                          vp(self.rx_offsets.data_ptr()), vp(self.rx_mtiles.data_ptr()), self.cap, I, H,
+                                          El, self.mode, 1, vp(self.act.data_ptr()), vp(self.act_scale.data_ptr()), None,
+                                          None, stream))
+        self.check(lib.dqmoe_grouped_gemm_rows(vp(self.act.data_ptr()), vp(self.act_scale.data_ptr()) if self.mode else None,
+                                               vp(b1.data_ptr()), sp(b1s), vp(self.rx_offsets.data_ptr()),
+                                               vp(self.rx_mtiles.data_ptr()), self.cap, H, I, El, self.mode,
+                                               vp(self.row_dst.data_ptr()), stream))
+        self.check(lib.dqmoe_ep_signal(P["flags"], 2, me, W, ep_, stream))
+        self.check(lib.dqmoe_ep_wait(vp(self.local["flags"]), 2, W, ep_, stream))
+        if route_weights is None:
+            return self.d_out
+        return ops.finalize_weighted(self.d_out, route_weights)

@@ -236,6 +236,16 @@ int dqmoe_grouped_gemm(const void* a, const float* a_scale, const void* w, const
                        int E, int quant_mode, int gated, void* out, float* out_scale, float* amax,
                        const int32_t* dest_to_src, dqmoe_stream_t stream);
 
+/*
+ * Stage-2 grouped GEMM whose epilogue stores row r to the address row_dst[r] (uint64 device
+ * addresses, 16-byte aligned rows of N bf16; 0 skips the row). The addresses may lie in another
+ * GPU's memory that this GPU can reach over NVLink: the expert-parallel layer uses this to write
+ * each result row directly into its home rank's output. Same GEMM as dqmoe_grouped_gemm.
+ */
+int dqmoe_grouped_gemm_rows(const void* a, const float* a_scale, const void* w, const float* w_scale,
+                            const int32_t* offsets, const int32_t* mtile_prefix, int n, int N, int K,
+                            int E, int quant_mode, const void* row_dst, dqmoe_stream_t stream);
+
 /* cumulative 128-row tile counts per expert from offsets[E+1] (device to device) */
 int dqmoe_mtile_prefix(const int32_t* offsets, int E, int32_t* mtile_prefix, dqmoe_stream_t stream);
 
@@ -247,6 +257,42 @@ int dqmoe_mtile_prefix(const int32_t* offsets, int E, int32_t* mtile_prefix, dqm
  */
 int dqmoe_requant_from_amax(const void* act_bf16, int64_t n, int I, const float* amax,
                             int per_row, void* q, float* scale, dqmoe_stream_t stream);
+
+/* ------------------------------------------------------------------ expert parallel over peer memory */
+
+/*
+ * Building blocks of the expert-parallel layer that exchanges rows through peer-mapped
+ * ("symmetric") buffers instead of a collective library. W <= 8 ranks of one node; rank `me`
+ * owns experts [me*E/W, (me+1)*E/W). The *_ptrs arguments are host arrays of W device addresses,
+ * entry r being rank r's copy of the same buffer (this rank's own copy included). Flags are
+ * int32[3][8] per rank and carry a per-call `epoch` (any value different from the previous
+ * call's), so nothing is cleared between calls. Waits are bounded (about 10 s) and report through
+ * dqmoe_device_status() instead of hanging. The reference has no multi-GPU path.
+ *
+ *   publish_counts  counts[E] of the local expert sort -> row `me` of every rank's cnt[W][E]; flag 0
+ *   plan            waits flag 0 of all ranks; send_base[E] = row in the owner's receive buffer where
+ *                   this rank's rows of expert e start (the receive buffer is grouped by expert, then
+ *                   by source rank); rx_offsets / rx_mtiles [E/W + 1] describe this rank's own
+ *                   receive buffer for dqmoe_grouped_gemm
+ *   dispatch        a[dest_to_src[i] / k] (+ scale row, + home slot) of every kept sorted row i ->
+ *                   the owner's rx_rows / rx_scale / rx_home; flag 1 when all rows are written
+ *   wait / signal   flag `phase` (1: rows landed, 2: results landed)
+ *   row_ptrs        row_dst[r] = address of received row r's result in its home rank's d_out
+ */
+int dqmoe_ep_publish_counts(const int32_t* counts, int E, int me, int W, const void* const* cnt_ptrs,
+                            const void* const* flag_ptrs, int epoch, dqmoe_stream_t stream);
+int dqmoe_ep_plan(const int32_t* cnt, const int32_t* my_flags, int E, int me, int W, int epoch,
+                  int32_t* send_base, int32_t* rx_offsets, int32_t* rx_mtiles, dqmoe_stream_t stream);
+int dqmoe_ep_dispatch(const void* a, const float* a_scale, size_t row_bytes, int scale_cols, int k, int n,
+                      const int32_t* offsets, const int32_t* dest_to_src, const int32_t* send_base,
+                      int E, int me, int W, const void* const* rx_rows, const void* const* rx_scale,
+                      const void* const* rx_home, const void* const* flag_ptrs, int32_t* done_counter,
+                      int epoch, dqmoe_stream_t stream);
+int dqmoe_ep_wait(const int32_t* my_flags, int phase, int W, int epoch, dqmoe_stream_t stream);
+int dqmoe_ep_signal(const void* const* flag_ptrs, int phase, int me, int W, int epoch, dqmoe_stream_t stream);
+int dqmoe_ep_row_ptrs(const int32_t* rx_home, const int32_t* rx_offsets, int E_local,
+                      const void* const* d_out_ptrs, int W, size_t out_row_bytes, int cap, void* row_dst,
+                      dqmoe_stream_t stream);
 
 #ifdef __cplusplus
 }

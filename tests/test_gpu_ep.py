@@ -13,7 +13,7 @@ ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
 pytestmark = pytest.mark.gpu
 
 
-def _worker(rank, world, init_file, mode, results):
+def _worker(rank, world, init_file, mode, impl, results):
     sys.path.insert(0, ROOT)
     sys.path.insert(0, os.path.join(ROOT, "tests"))
     os.environ.setdefault("NCCL_NVLS_ENABLE", "0")
@@ -49,9 +49,15 @@ def _worker(rank, world, init_file, mode, results):
         idx = m_indices.to(dev)
         ops.moe_forward(aq, asc, full[0], full[1], full[2], full[3], ref, idx, ws, mode)
         shard = tuple(None if t is None else t[lo:hi].contiguous() for t in full)
-        layer = ep.ExpertParallelLayer(E, k, mode, shard, ep.CudaBackend(ops))
-        d = layer.forward(aq, asc, idx)
-        out = layer.forward(aq, asc, idx, weights.to(dev))
+        if impl == "peer":  # exchange through peer-mapped memory, three calls in a row (flag epochs)
+            layer = ep.PeerExpertParallelLayer(T, H, I, E, k, mode, shard, ops)
+            layer.forward(aq, asc, idx, zero_dropped=True)
+            d = layer.forward(aq, asc, idx, zero_dropped=True).clone()
+            out = layer.forward(aq, asc, idx, weights.to(dev), zero_dropped=True)
+        else:
+            layer = ep.ExpertParallelLayer(E, k, mode, shard, ep.CudaBackend(ops))
+            d = layer.forward(aq, asc, idx)
+            out = layer.forward(aq, asc, idx, weights.to(dev))
         torch.cuda.synchronize()
         status = ops.device_status()
         same = bool(torch.equal(d, ref))  # same kernels, same per-row arithmetic: bit-identical
@@ -61,14 +67,14 @@ def _worker(rank, world, init_file, mode, results):
         dist.destroy_process_group()
 
 
-@pytest.mark.parametrize("mode", [0, 512, 1024])
-def test_expert_parallel_matches_single_gpu(mode):
+@pytest.mark.parametrize("mode,impl", [(0, "nccl"), (512, "nccl"), (1024, "nccl"), (0, "peer"), (1024, "peer")])
+def test_expert_parallel_matches_single_gpu(mode, impl):
     if torch.cuda.device_count() < 2:
         pytest.skip("needs two GPUs")
     world = 2
     with tempfile.TemporaryDirectory() as tmp:
         results = mp.Manager().dict()
-        mp.spawn(_worker, args=(world, os.path.join(tmp, "init"), mode, results), nprocs=world, join=True)
+        mp.spawn(_worker, args=(world, os.path.join(tmp, "init"), mode, impl, results), nprocs=world, join=True)
         for rank in range(world):
             status, same, cos, wsame = results[rank]
             assert status == 0
