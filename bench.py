@@ -326,6 +326,11 @@ def main():
             ops.moe_forward(aq, as_, bq, bs, b1q, b1s, d, idx, ws, mode)
     else:
         layer = ep.ExpertParallelMoE(wl, dev, seed=0, ops=ops)
+        # per rank and step: sort (1 or 3) + publish, plan, dispatch, wait, row_ptrs, fc1, fc2, signal, wait (peer exchange)
+        sort_l = 1 if n <= 2048 else 3
+        # collective exchange: sort, gather, segment ids, then the layer on the received rows, then scatter
+        ep_launches = (sort_l + 9) * world if layer.impl == "peer" else \
+            (sort_l + 2 + (3 + 3 + (1 if mode in (256, 512) else 0)) + 1) * world
         aq, as_ = layer.quantize_activations(x)
 
         def step():
@@ -365,37 +370,48 @@ def main():
     value = flops_step / (ms_step * 1e-3) / 1e12
 
     # ---- end to end through the drop-in call with host buffers (rank-local copies inside the timed region)
+    # every rank copies its own step inputs from pinned host memory and reads its result back
     e2e = None
+    h_aq = aq.cpu().pin_memory()
+    h_as = as_.cpu().pin_memory() if as_ is not None else None
+    h_idx = idx.cpu().pin_memory()
+    h_d = torch.empty((T, k, H), dtype=torch.bfloat16).pin_memory()
+    d_aq, d_as, d_idx = torch.empty_like(aq), (torch.empty_like(as_) if as_ is not None else None), torch.empty_like(idx)
+    dummy = torch.ones(1, device=dev)
     if world == 1:
-        h_aq = aq.cpu().pin_memory()
-        h_as = as_.cpu().pin_memory() if as_ is not None else None
-        h_idx = idx.cpu().pin_memory()
-        h_d = torch.empty(d.shape, dtype=d.dtype).pin_memory()
-        d_aq, d_as, d_idx = torch.empty_like(aq), (torch.empty_like(as_) if as_ is not None else None), torch.empty_like(idx)
         fn = moe_test.m_grouped_moe_nt_contiguous_fp8_bf16 if mode else moe_test.m_grouped_moe_nt_contiguous_bf16
-        dummy = torch.ones(1, device=dev)
 
-        def e2e_step():
-            d_aq.copy_(h_aq, non_blocking=True)
-            if h_as is not None:
-                d_as.copy_(h_as, non_blocking=True)
-            d_idx.copy_(h_idx, non_blocking=True)
+        def e2e_forward():
             fn((d_aq, d_as if mode else dummy), (bq, bs if mode else dummy), (b1q, b1s if mode else dummy), d, d_idx,
                ws, mode)
-            h_d.copy_(d, non_blocking=True)
+            return d
+    else:
+        def e2e_forward():
+            return layer.forward(d_aq, d_as, d_idx, None)
 
-        for _ in range(3):
-            e2e_step()
-        torch.cuda.synchronize()
-        ev0.record()
-        for _ in range(args.steps):
-            e2e_step()
-        ev1.record()
-        torch.cuda.synchronize()
-        e2e_ms = ev0.elapsed_time(ev1) / args.steps
-        h2d = h_aq.numel() * h_aq.element_size() + (h_as.numel() * 4 if h_as is not None else 0) + h_idx.numel() * 4
-        e2e = {"value": flops_step / (e2e_ms * 1e-3) / 1e12, "unit": "TFLOP/s", "ms_per_step": e2e_ms,
-               "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": h_d.numel() * h_d.element_size()}
+    def e2e_step():
+        d_aq.copy_(h_aq, non_blocking=True)
+        if h_as is not None:
+            d_as.copy_(h_as, non_blocking=True)
+        d_idx.copy_(h_idx, non_blocking=True)
+        h_d.copy_(e2e_forward(), non_blocking=True)
+
+    for _ in range(3):
+        e2e_step()
+    barrier()
+    ev0.record()
+    for _ in range(args.steps):
+        e2e_step()
+    ev1.record()
+    barrier()
+    e2e_ms = ev0.elapsed_time(ev1) / args.steps
+    if world > 1:
+        tmax = torch.tensor([e2e_ms], device=dev)
+        dist.all_reduce(tmax, op=dist.ReduceOp.MAX)
+        e2e_ms = float(tmax.item())
+    h2d = h_aq.numel() * h_aq.element_size() + (h_as.numel() * 4 if h_as is not None else 0) + h_idx.numel() * 4
+    e2e = {"value": flops_step / (e2e_ms * 1e-3) / 1e12, "unit": "TFLOP/s", "ms_per_step": e2e_ms,
+           "h2d_bytes_per_step": h2d * world, "d2h_bytes_per_step": h_d.numel() * h_d.element_size() * world}
 
     # ---- roofline of the dominant kernel: the fc1 grouped GEMM timed alone on this step's own operands
     roofline = None
@@ -446,8 +462,8 @@ def main():
         "ms_per_step": ms_step, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
         "dtype": "e4m3 x e4m3 -> f32" if mode else "bf16 x bf16 -> f32", "data": "synthetic",
         "tokens_per_s": T * world / (ms_step * 1e-3),
-        "config": config_of(args.workload, wl, world),
-        "gpu_launches": launches_per_step(n, mode) * args.steps if world == 1 else None,
+        "config": dict(config_of(args.workload, wl, world), **({"exchange": layer.impl} if world > 1 else {})),
+        "gpu_launches": (launches_per_step(n, mode) if world == 1 else ep_launches) * args.steps,
         "clocks": clocks, "e2e": e2e, "roofline": roofline, "cpu_baseline": base,
     }
     print(json.dumps(out))
