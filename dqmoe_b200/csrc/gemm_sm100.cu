@@ -91,9 +91,10 @@ struct SharedTail {
     uint64_t sc_empty[kScaleSlots];
     uint32_t tmem_base;
     int abort_flag;
-    float amax[2][2][kBM];
+    alignas(16) float amax[2][2][kBM];
     float sc_a[kScaleSlots][kBM];   // activation scale of each tile row for one K block
     float sc_b[kScaleSlots][4];     // weight scales: first group, second group (low / high block row)
+    uint4 stage[kEpiWarps][32 * 4]; // per epilogue warp: 32 rows x 64 bytes, for row-coalesced stores
     int mprefix[kMaxExperts + 1];
     int offsets[kMaxExperts + 1];
 };
@@ -151,6 +152,34 @@ __device__ __forceinline__ ScaleRows scale_rows(bool gated, int nt, int N, int N
 __device__ __forceinline__ float silu_bf16(float g) {
     // the torch oracle evaluates silu on bf16 and rounds the result to bf16 (test/util.py:141-142)
     return bf_round(__fdividef(g, 1.0f + __expf(-g)));
+}
+
+// Store 32 rows x 32 bf16 columns held one row per lane (packed[16]) so that each store
+// instruction writes 64 contiguous bytes of each of 8 rows instead of 16 bytes of each of 32 rows: the rows go
+// through a 2 KiB per-warp shared-memory buffer (16-byte pieces XOR-swizzled against bank
+// conflicts). row_ptr is this lane's destination (already at the chunk's first column) or null;
+// pieces_ok = number of 8-column pieces of the chunk that lie inside the matrix. Used for rows
+// that live in another GPU's memory, where 16-byte scattered stores waste NVLink packets.
+__device__ __forceinline__ void store_rows_staged(uint4* stage, const uint32_t (&packed)[16], uint8_t* row_ptr,
+                                                  int pieces_ok, int lane) {
+    __syncwarp();  // the previous use of the buffer has been read out
+#pragma unroll
+    for (int pc = 0; pc < 4; ++pc)
+        stage[lane * 4 + (pc ^ ((lane >> 1) & 3))] =
+            make_uint4(packed[pc * 4], packed[pc * 4 + 1], packed[pc * 4 + 2], packed[pc * 4 + 3]);
+    __syncwarp();
+    const unsigned long long my_ptr = reinterpret_cast<unsigned long long>(row_ptr);
+    const int piece = lane & 3;
+#pragma unroll
+    for (int it = 0; it < 4; ++it) {  // 4 lanes per 64-byte row: 8 rows per instruction
+        const int r = it * 8 + (lane >> 2);
+        const unsigned long long dst = __shfl_sync(0xffffffffu, my_ptr, r);
+        const uint4 v = stage[r * 4 + (piece ^ ((r >> 1) & 3))];
+        if (dst != 0 && piece < pieces_ok) {
+            Vec16 vv{v.x, v.y, v.z, v.w};
+            st16(reinterpret_cast<uint8_t*>(dst) + piece * 16, vv);
+        }
+    }
 }
 
 // two fp32 FMAs in one instruction (packed fp32 of sm_100): a += x * s
@@ -521,15 +550,9 @@ moe_GemmGrouped_GemmUniversal_tcgen05(const __grid_constant__ CUtensorMap tma_a,
                             }
                             packed[i >> 1] = pack_bf16x2(__uint_as_float(r[i]) * s0, __uint_as_float(r[i + 1]) * s1);
                         }
-                        if (row_ok && orow_idx >= 0) {
-#pragma unroll
-                            for (int g8 = 0; g8 < 4; ++g8) {
-                                if (col0 + g8 * 8 < I_or_H) {
-                                    Vec16 vv{packed[g8 * 4], packed[g8 * 4 + 1], packed[g8 * 4 + 2], packed[g8 * 4 + 3]};
-                                    st16(orow + col0 + g8 * 8, vv);
-                                }
-                            }
-                        }
+                        store_rows_staged(st.stage[warp - 4], packed,
+                                          row_ok && orow_idx >= 0 ? reinterpret_cast<uint8_t*>(orow + col0) : nullptr,
+                                          min(4, max(0, (I_or_H - col0 + 7) / 8)), lane);
                     }
                 }
                 ptx::tc_fence_before();
@@ -660,20 +683,15 @@ moe_GemmGrouped_GemmUniversal_tcgen05(const __grid_constant__ CUtensorMap tma_a,
                         orow = row_ok ? reinterpret_cast<__nv_bfloat16*>(p.row_dst[grow]) : nullptr;
                         orow_idx = orow != nullptr ? 0 : -1;
                     }
-                    if (row_ok && orow_idx >= 0) {
 #pragma unroll
-                        for (int c = 0; c < 4; ++c) {
-                            const int col0 = tl.nt * kUmmaN + (c >> 1) * kBoxRows + h * 64 + (c & 1) * 32;
+                    for (int c = 0; c < 4; ++c) {
+                        const int col0 = tl.nt * kUmmaN + (c >> 1) * kBoxRows + h * 64 + (c & 1) * 32;
+                        uint32_t packed[16];
 #pragma unroll
-                            for (int g8 = 0; g8 < 4; ++g8) {
-                                if (col0 + g8 * 8 < I_or_H) {
-                                    const float* a = acc + c * 32 + g8 * 8;
-                                    Vec16 vv{pack_bf16x2(a[0], a[1]), pack_bf16x2(a[2], a[3]), pack_bf16x2(a[4], a[5]),
-                                             pack_bf16x2(a[6], a[7])};
-                                    st16(orow + col0 + g8 * 8, vv);
-                                }
-                            }
-                        }
+                        for (int i = 0; i < 32; i += 2) packed[i >> 1] = pack_bf16x2(acc[c * 32 + i], acc[c * 32 + i + 1]);
+                        store_rows_staged(st.stage[warp - 4], packed,
+                                          row_ok && orow_idx >= 0 ? reinterpret_cast<uint8_t*>(orow + col0) : nullptr,
+                                          min(4, max(0, (I_or_H - col0 + 7) / 8)), lane);
                     }
                 }
             }

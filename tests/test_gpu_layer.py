@@ -228,3 +228,41 @@ def test_profiler_sees_the_kernel_names_the_reference_script_filters_on(ops, wor
     names = [e.key for e in prof.key_averages()]
     gemm = [n for n in names if "GemmUniversal" in n and "GemmGrouped" in n]
     assert gemm, names
+
+
+@pytest.mark.parametrize("counts,N,K", [(RAGGED, 384, 640), (LARGE, 384, 640), (MANY, 1280, 256)],
+                         ids=["ragged-narrow", "pairs", "many-wide"])
+@pytest.mark.parametrize("mode", [0, 512, 1024])
+def test_grouped_gemm_row_addresses_equal_scatter_map(ops, mode, counts, N, K):
+    """dqmoe_grouped_gemm_rows (stage 2 storing each row to an explicit address, the path the
+    expert-parallel layer uses to write into peer memory) against the same GEMM with a scatter map."""
+    import ctypes
+    from dqmoe_b200 import _lib
+    E, n = len(counts), sum(counts)
+    g = torch.Generator().manual_seed(mode + N)
+    a = torch.randn(n, K, generator=g).to(torch.bfloat16)
+    w = (torch.randn(E, N, K, generator=g) * 0.05).to(torch.bfloat16)
+    offsets = torch.tensor(np.concatenate([[0], np.cumsum(counts)]), dtype=torch.int32).to(DEV)
+    mt = ops.mtile_prefix(offsets)
+    if mode == 0:
+        aq, asc, wq, wsc = a, None, w, None
+    elif mode == 1024:
+        aq, asc = orc.quant_block_1x128(a)
+        wq, wsc = orc.quant_block_128x128(w)
+    else:
+        aq, asc = orc.quant_rowwise(a)
+        wq, wsc = orc.quant_rowwise(w)
+    dev = lambda t: None if t is None else t.to(DEV).contiguous()
+    aq, asc, wq, wsc = dev(aq), dev(asc), dev(wq), dev(wsc)
+    perm = torch.randperm(n, generator=g).to(torch.int32).to(DEV)
+    perm[5] = -1  # a row without a destination
+    want = torch.zeros(n, N, dtype=torch.bfloat16, device=DEV)
+    ops.grouped_gemm(aq, asc, wq, wsc, offsets, mt, N, mode, False, want, dest_to_src=perm)
+    got = torch.zeros(n, N, dtype=torch.bfloat16, device=DEV)
+    row_dst = torch.where(perm >= 0, got.data_ptr() + perm.to(torch.int64) * (N * 2), torch.zeros((), dtype=torch.int64, device=DEV))
+    p = lambda t: None if t is None else ctypes.c_void_p(t.data_ptr())
+    lib = _lib.load()
+    _lib.check(lib.dqmoe_grouped_gemm_rows(p(aq), p(asc), p(wq), p(wsc), p(offsets), p(mt), n, N, K, E, mode,
+                                           p(row_dst), ctypes.c_void_p(torch.cuda.current_stream().cuda_stream)))
+    assert ops.device_status() == 0
+    assert torch.equal(got, want)
