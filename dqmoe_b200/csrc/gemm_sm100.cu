@@ -502,16 +502,11 @@ moe_GemmGrouped_GemmUniversal_tcgen05(const __grid_constant__ CUtensorMap tma_a,
                             }
                             packed[i >> 1] = pack_bf16x2(a2[0], a2[1]);
                         }
-                        if (row_ok) {
-                            __nv_bfloat16* orow = reinterpret_cast<__nv_bfloat16*>(p.out) + size_t(grow) * I_or_H;
-#pragma unroll
-                            for (int g8 = 0; g8 < 4; ++g8) {
-                                if (col0 + g8 * 8 < I_or_H) {
-                                    Vec16 vv{packed[g8 * 4], packed[g8 * 4 + 1], packed[g8 * 4 + 2], packed[g8 * 4 + 3]};
-                                    st16(orow + col0 + g8 * 8, vv);
-                                }
-                            }
-                        }
+                        store_rows_staged(st.stage[warp - 4], packed,
+                                          row_ok ? reinterpret_cast<uint8_t*>(reinterpret_cast<__nv_bfloat16*>(p.out) +
+                                                                              size_t(grow) * I_or_H + col0)
+                                                 : nullptr,
+                                          min(4, max(0, (I_or_H - col0 + 7) / 8)), lane);
                     }
                     if constexpr (kMode == kChannel) {
                         if (row_ok) atomic_max_nonneg(p.amax + grow, amax_local);
@@ -659,21 +654,17 @@ moe_GemmGrouped_GemmUniversal_tcgen05(const __grid_constant__ CUtensorMap tma_a,
                     const float amax = fmaxf(amax_local, st.amax[tile_it & 1u][h ^ 1][r_in_tile]);
                     const float sf = scale_from_amax(amax);
                     const float inv = inv_scale(sf);
-                    if (row_ok) {
-                        uint8_t* orow = reinterpret_cast<uint8_t*>(p.out) + size_t(grow) * I_or_H;
+                    {
+                        uint32_t packed[16];  // 64 e4m3 bytes of this row
 #pragma unroll
-                        for (int g16 = 0; g16 < 4; ++g16) {
-                            if (col0 + g16 * 16 < I_or_H) {
-                                Vec16 vv;
-                                const float* a = acc + g16 * 16;
-                                vv.x = f2e4m3x4(a[0] * inv, a[1] * inv, a[2] * inv, a[3] * inv);
-                                vv.y = f2e4m3x4(a[4] * inv, a[5] * inv, a[6] * inv, a[7] * inv);
-                                vv.z = f2e4m3x4(a[8] * inv, a[9] * inv, a[10] * inv, a[11] * inv);
-                                vv.w = f2e4m3x4(a[12] * inv, a[13] * inv, a[14] * inv, a[15] * inv);
-                                st16(orow + col0 + g16 * 16, vv);
-                            }
+                        for (int g4 = 0; g4 < 16; ++g4) {
+                            const float* a = acc + g4 * 4;
+                            packed[g4] = f2e4m3x4(a[0] * inv, a[1] * inv, a[2] * inv, a[3] * inv);
                         }
-                        if (h == 0) p.out_scale[size_t(grow) * ((I_or_H + 127) / 128) + tl.nt] = sf;
+                        store_rows_staged(st.stage[warp - 4], packed,
+                                          row_ok ? reinterpret_cast<uint8_t*>(p.out) + size_t(grow) * I_or_H + col0 : nullptr,
+                                          min(4, max(0, (I_or_H - col0 + 15) / 16)), lane);
+                        if (row_ok && h == 0) p.out_scale[size_t(grow) * ((I_or_H + 127) / 128) + tl.nt] = sf;
                     }
                 } else {
                     int orow_idx = grow;
