@@ -27,6 +27,8 @@ SIGNATURES = {
     "dqmoe_moe_workspace_bytes": (_c_size, [_c_int] * 6),
     "dqmoe_moe_forward": (_c_int, [_ptr] * 9 + [_c_size] + [_c_int] * 7 + [_ptr]),
     "dqmoe_moe_workspace_ptr": (_ptr, [_ptr] + [_c_int] * 7),
+    "dqmoe_moe_block_workspace_bytes": (_c_size, [_c_int] * 6),
+    "dqmoe_moe_block": (_c_int, [_ptr] * 8 + [_c_size] + [_c_int] * 7 + [_ptr]),
     "dqmoe_route_topk": (_c_int, [_ptr, _c_int, _c_int, _c_int, _c_int, _ptr, _ptr, _ptr]),
     "dqmoe_route_sort_workspace_bytes": (_c_size, [_c_int, _c_int]),
     "dqmoe_route_sort": (_c_int, [_ptr, _c_int, _c_int, _ptr, _ptr, _ptr, _ptr, _ptr, _c_size, _ptr]),

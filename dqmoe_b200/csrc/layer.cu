@@ -162,4 +162,87 @@ int dqmoe_moe_forward(const void* a, const float* a_scale, const void* b, const 
     return rc;
 }
 
+// ---------------------------------------------------------------------------------------------
+// Whole MoE block from bf16 activations: router -> expert sort -> gather fused with the dynamic
+// activation quantisation -> grouped fc1/fc2 -> weighted combine over the k slots.
+// Workspace = [indices T*k | weights T*k | d T*k*H bf16 | layer workspace].
+struct BlockLayout {
+    size_t indices, weights, d, layer, total;
+};
+static BlockLayout block_layout(int T, int H, int I, int E, int k, int quant_mode) {
+    BlockLayout B{};
+    size_t off = 0;
+    auto add = [&](size_t bytes) {
+        const size_t at = off;
+        off += align_up(bytes, layer::kAlign);
+        return at;
+    };
+    B.indices = add(size_t(T) * k * sizeof(int));
+    B.weights = add(size_t(T) * k * sizeof(float));
+    B.d = add(size_t(T) * k * H * 2);
+    B.layer = add(layer::make_layout(T, H, I, E, k, quant_mode).total);
+    B.total = off;
+    return B;
+}
+
+size_t dqmoe_moe_block_workspace_bytes(int T, int H, int I, int E, int k, int quant_mode) {
+    if (T < 0 || H <= 0 || I <= 0 || E <= 0 || k <= 0) return 0;
+    if (quant_mode != DQMOE_QUANT_NONE && quant_mode != DQMOE_QUANT_FP8_BLOCK) return 0;
+    return block_layout(T, H, I, E, k, quant_mode).total;
+}
+
+int dqmoe_moe_block(const void* x_bf16, const float* logits, const void* b, const float* b_scale, const void* b1,
+                    const float* b1_scale, void* out_bf16, void* workspace, size_t workspace_bytes, int T, int H,
+                    int I, int E, int k, int scoring, int quant_mode, dqmoe_stream_t stream_) {
+    cudaStream_t stream = static_cast<cudaStream_t>(stream_);
+    DQ_CHECK(T >= 0 && H > 0 && I > 0 && E > 0 && k > 0);
+    DQ_CHECK_FMT(quant_mode == DQMOE_QUANT_NONE || quant_mode == DQMOE_QUANT_FP8_BLOCK,
+                 "quant_mode=%d: the fused block supports bf16 (0) and block FP8 (1024)", quant_mode);
+    if (T == 0) return DQMOE_OK;
+    DQ_CHECK(x_bf16 != nullptr && logits != nullptr && b != nullptr && b1 != nullptr && out_bf16 != nullptr);
+    DQ_CHECK_FMT(workspace != nullptr && is_aligned(workspace, layer::kAlign), "workspace pointer %p is not aligned!",
+                 workspace);
+    const bool fp8 = quant_mode != DQMOE_QUANT_NONE;
+    if (fp8) DQ_CHECK(b_scale != nullptr && b1_scale != nullptr);
+    DQ_CHECK_FMT(H % 16 == 0 && I % 16 == 0, "hidden_size=%d and inter_size=%d must be multiples of 16", H, I);
+    DQ_CHECK(int64_t(T) * k < (int64_t(1) << 31));
+    const int n = T * k;
+    const BlockLayout B = block_layout(T, H, I, E, k, quant_mode);
+    if (workspace_bytes != 0 && workspace_bytes < B.total)
+        return fail(DQMOE_ERR_WORKSPACE, __FILE__, __LINE__, "workspace_bytes >= dqmoe_moe_block_workspace_bytes(...)",
+                    "workspace has %zu bytes, the block needs %zu", workspace_bytes, B.total);
+    char* ws = static_cast<char*>(workspace);
+    int* indices = reinterpret_cast<int*>(ws + B.indices);
+    float* weights = reinterpret_cast<float*>(ws + B.weights);
+    void* d = ws + B.d;
+    char* lws = ws + B.layer;
+    const layer::Layout L = layer::make_layout(T, H, I, E, k, quant_mode);
+    int* offsets = reinterpret_cast<int*>(lws + L.offsets);
+    int* counts = reinterpret_cast<int*>(lws + L.counts);
+    int* mtile_prefix = reinterpret_cast<int*>(lws + L.mtile_prefix);
+    int* dest_to_src = reinterpret_cast<int*>(lws + L.dest_to_src);
+    void* perm_a = lws + L.perm_a;
+    float* perm_a_scale = reinterpret_cast<float*>(lws + L.perm_a_scale);
+    void* act = lws + L.act;
+    float* act_scale = reinterpret_cast<float*>(lws + L.act_scale);
+
+    int rc = dqmoe_route_topk(logits, T, E, k, scoring, indices, weights, stream);
+    if (rc != DQMOE_OK) return rc;
+    rc = route::route_sort(indices, n, E, counts, offsets, mtile_prefix, dest_to_src, nullptr, lws + L.sort_ws,
+                           L.sort_ws_bytes, stream);
+    if (rc != DQMOE_OK) return rc;
+    if (fp8)  // quantise while gathering: each expanded row is read as bf16 and written as e4m3 + 1x128 scales
+        rc = dqmoe_permute_quant_block_1x128(x_bf16, H, k, dest_to_src, n, perm_a, perm_a_scale, stream);
+    else
+        rc = dqmoe_permute_rows(x_bf16, size_t(H) * 2, k, dest_to_src, n, perm_a, nullptr, 0, nullptr, stream);
+    if (rc != DQMOE_OK) return rc;
+    rc = gemm::grouped_gemm(perm_a, perm_a_scale, b, b_scale, offsets, mtile_prefix, n, I, H, E, quant_mode, 1, act,
+                            act_scale, nullptr, nullptr, nullptr, stream);
+    if (rc != DQMOE_OK) return rc;
+    rc = gemm::grouped_gemm(act, act_scale, b1, b1_scale, offsets, mtile_prefix, n, H, I, E, quant_mode, 0, d, nullptr,
+                            nullptr, dest_to_src, nullptr, stream);
+    if (rc != DQMOE_OK) return rc;
+    return dqmoe_finalize_weighted(d, weights, out_bf16, T, k, H, stream);
+}
+
 }  // extern "C"

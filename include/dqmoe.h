@@ -109,6 +109,22 @@ int dqmoe_moe_forward(const void* a, const float* a_scale, const void* b, const 
 void* dqmoe_moe_workspace_ptr(void* workspace, int which, int T, int H, int I, int E, int k,
                               int quant_mode);
 
+/*
+ * The whole MoE block from bf16 activations x [T, H] and fp32 router logits [T, E] to
+ * out [T, H] bf16: top-k router, expert sort, gather fused with the dynamic 1x128 FP8
+ * quantisation of the activations (block mode) or plain gather (bf16 mode), grouped fc1 +
+ * SwiGLU (+ re-quantisation), grouped fc2, weighted combine of the k slots. quant_mode is
+ * DQMOE_QUANT_NONE (bf16 weights) or DQMOE_QUANT_FP8_BLOCK (e4m3 weights with 128x128
+ * scales). The natural caller of the reference's layer (its tests do routing and input
+ * quantisation in torch, test/torch_test.py:60-80, test/util.py:162-184); no single
+ * counterpart in the reference.
+ */
+size_t dqmoe_moe_block_workspace_bytes(int T, int H, int I, int E, int k, int quant_mode);
+int dqmoe_moe_block(const void* x_bf16, const float* logits, const void* b, const float* b_scale,
+                    const void* b1, const float* b1_scale, void* out_bf16, void* workspace,
+                    size_t workspace_bytes, int T, int H, int I, int E, int k, int scoring,
+                    int quant_mode, dqmoe_stream_t stream);
+
 /* ------------------------------------------------------------------ routing */
 
 /*

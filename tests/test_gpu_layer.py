@@ -266,3 +266,59 @@ def test_grouped_gemm_row_addresses_equal_scatter_map(ops, mode, counts, N, K):
                                            p(row_dst), ctypes.c_void_p(torch.cuda.current_stream().cuda_stream)))
     assert ops.device_status() == 0
     assert torch.equal(got, want)
+
+
+@pytest.mark.parametrize("mode,scoring", [(0, "softmax"), (1024, "softmax"), (1024, "sigmoid")])
+def test_moe_block_router_to_weighted_output(ops, mode, scoring):
+    """dqmoe_moe_block (router, fused gather+quantise, layer, weighted combine) against the oracle's moe_block."""
+    E, T, H, I, k = 16, 200, 512, 256, 4
+    a, b, b1, _, _ = make_inputs(31, T, H, I, E, k, 1.0, 0.05)
+    logits = torch.randn(T, E, generator=torch.Generator().manual_seed(5))
+    if mode == 0:
+        ref = orc.moe_block(a, logits, b, b1, k, scoring, 0)
+        out = ops.moe_block(a.to(DEV), logits.to(DEV), b.to(DEV), None, b1.to(DEV), None, k, scoring, 0)
+    else:
+        qs = orc.quantize_inputs(a, b, b1, 1024)
+        ref = orc.moe_block(a, logits, b, b1, k, scoring, 1024, quantized=qs)
+        out = ops.moe_block(a.to(DEV), logits.to(DEV), qs[2].to(DEV), qs[3].to(DEV).contiguous(), qs[4].to(DEV),
+                            qs[5].to(DEV).contiguous(), k, scoring, 1024)
+    assert ops.device_status() == 0
+    assert_close(out, ref)
+
+
+@pytest.mark.parametrize("mode", [0, 256, 1024])
+def test_layer_replays_from_a_cuda_graph(ops, workspace, mode):
+    """The layer enqueues kernels only (no host synchronisation, no allocation), so after one warm-up
+    call it can be captured into a CUDA graph and replayed on new inputs (decode loops do this)."""
+    E, T, H, I, k = 8, 16, 512, 256, 2
+    a, b, b1, _, m_indices = make_inputs(9, T, H, I, E, k, 1.0, 0.05)
+    a2, _, _, _, m2 = make_inputs(10, T, H, I, E, k, 1.0, 0.05)
+    if mode == 0:
+        q = [a.to(DEV), None, b.to(DEV), None, b1.to(DEV), None]
+        q2 = [a2.to(DEV), None]
+        ref2 = orc.moe_layer_bf16(a2, b, b1, m2, E)
+    else:
+        qs = orc.quantize_inputs(a, b, b1, mode)
+        q = [t.to(DEV).contiguous() for t in qs]
+        qs2 = orc.quantize_inputs(a2, b, b1, mode)
+        q2 = [qs2[0].to(DEV), qs2[1].to(DEV).contiguous()]
+        ref2 = orc.moe_layer_fp8(*qs2, m2, E, mode)
+    idx = m_indices.to(DEV)
+    d = torch.zeros(T, k, H, dtype=torch.bfloat16, device=DEV)
+    stream = torch.cuda.Stream()
+    with torch.cuda.stream(stream):
+        ops.moe_forward(*q, d, idx, workspace, mode)  # warm-up: one-time host set-up happens here
+        stream.synchronize()
+        graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(graph, stream=stream):
+            ops.moe_forward(*q, d, idx, workspace, mode)
+    # new inputs written into the captured buffers, then replay
+    q[0].copy_(q2[0])
+    if q2[1] is not None:
+        q[1].copy_(q2[1])
+    idx.copy_(m2.to(DEV))
+    d.zero_()
+    graph.replay()
+    torch.cuda.synchronize()
+    assert ops.device_status() == 0
+    assert_close(d, ref2)
