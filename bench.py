@@ -252,9 +252,30 @@ def run_decode(args, rank):
                 if i >= max(args.warmup, 3):
                     times.append(e0.elapsed_time(e1))
             p50 = statistics.median(times)
+            # the same call replayed from a CUDA graph (what a decode loop does): launch gaps removed
+            side = torch.cuda.Stream()
+            with torch.cuda.stream(side):
+                ops.moe_forward(*call, d, idx, ws, mode)
+                side.synchronize()
+                graph = torch.cuda.CUDAGraph()
+                with torch.cuda.graph(graph, stream=side):
+                    ops.moe_forward(*call, d, idx, ws, mode)
+            gtimes = []
+            for i in range(args.steps + 3):
+                flush.zero_()
+                e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                e0.record()
+                graph.replay()
+                e1.record()
+                torch.cuda.synchronize()
+                if i >= 3:
+                    gtimes.append(e0.elapsed_time(e1))
+            p50g = statistics.median(gtimes)
+            del graph
             # algorithmic bytes: weights of the experts hit + activations in and out
             nbytes = active * 3 * H * I * (1 if mode else 2) + T * H * (1 if mode else 2) + T * k * H * 2
             rows.append({"quant": MODE_NAME[mode], "T": T, "active_experts": active, "p50_us": p50 * 1e3,
+                         "p50_us_cuda_graph": p50g * 1e3, "gbs_cuda_graph": nbytes / (p50g * 1e-3) / 1e9,
                          "bytes": nbytes, "gbs": nbytes / (p50 * 1e-3) / 1e9,
                          "frac_of_measured_hbm": nbytes / (p50 * 1e-3) / 1e9 / pk["hbm_gbs"]})
     clocks = sampler.stop()

@@ -816,12 +816,23 @@ int grouped_gemm(const void* a, const float* a_scale, const void* w, const float
     if (gated && quant_mode == DQMOE_QUANT_FP8_BLOCK) DQ_CHECK(out_scale != nullptr);
     if (gated && (quant_mode == DQMOE_QUANT_FP8_TENSOR || quant_mode == DQMOE_QUANT_FP8_CHANNEL)) DQ_CHECK(amax != nullptr);
 
-    // Tile width: 256 accumulator columns, or 128 when the launch would leave SMs without a tile.
+    // Tile width: 256 accumulator columns, or 128 when the launch would leave many SMs without a tile.
     // The row-tile count is known only on the device; ceil(n/128) + min(E, n) - 1 bounds it.
     const bool pair = use_pairs(n, E, quant_mode);
     const int mtiles_max = ceil_div(n, kBM) + (E < n ? E : n) - 1;
     const int wide_tiles = mtiles_max * (gated ? ceil_div(N, kBoxRows) : ceil_div(N, kUmmaN));
-    const bool narrow = quant_mode != DQMOE_QUANT_FP8_BLOCK && !pair && wide_tiles < 2 * sm_count();
+    // (DQMOE_GEMM_BOX=64/128 overrides the choice for measurements.)
+    static int forced_box = -1;
+    if (forced_box == -1) {
+        const char* env = getenv("DQMOE_GEMM_BOX");
+        forced_box = env == nullptr ? 0 : atoi(env);
+    }
+    // measured on decode shapes: 128-column tiles win when 256-column tiles would fill at most half of
+    // the SMs, or when there are at most two row tiles (one or two tokens); otherwise 256 columns win
+    bool narrow = quant_mode != DQMOE_QUANT_FP8_BLOCK && !pair &&
+                  (2 * wide_tiles <= sm_count() || (mtiles_max <= 2 && wide_tiles < 2 * sm_count()));
+    if (forced_box == 64 && quant_mode != DQMOE_QUANT_FP8_BLOCK && !pair) narrow = true;
+    if (forced_box == 128) narrow = false;
     const int box = narrow ? 64 : kBoxRows;
 
     Params p;
