@@ -20,9 +20,16 @@ int grouped_gemm(const void* a, const float* a_scale, const void* w, const float
                  float* out_scale, float* amax, const int* dest_to_src, const void* row_dst, cudaStream_t stream);
 }  // namespace gemm
 
+namespace decode {
+int forward(const void* a, const float* a_scale, const void* b, const float* b_scale, const void* b1,
+            const float* b1_scale, void* d, const int* m_indices, void* act_bf16, float* amax, int T, int H, int I,
+            int E, int k, bool fp8, cudaStream_t stream);
+}  // namespace decode
+
 namespace layer {
 
-constexpr size_t kAlign = 256;  // CUDA_MEM_ALIGN of the reference (csrc/util.h:54-59)
+constexpr size_t kAlign = 256;
+constexpr int kDecodeRows = 8;  // up to this many expanded rows the GEMV path of decode.cu is used (bf16, per-tensor FP8)  // CUDA_MEM_ALIGN of the reference (csrc/util.h:54-59)
 
 struct Layout {
     size_t offsets, counts, mtile_prefix, sort_ws, dest_to_src, perm_a, perm_a_scale, act, act_scale, act_bf16, amax;
@@ -134,6 +141,11 @@ int dqmoe_moe_forward(const void* a, const float* a_scale, const void* b, const 
     float* act_scale = reinterpret_cast<float*>(ws + L.act_scale);
     void* act_bf16 = ws + L.act_bf16;
     float* amax = reinterpret_cast<float*>(ws + L.amax);
+
+    if (n <= layer::kDecodeRows && (quant_mode == DQMOE_QUANT_NONE || quant_mode == DQMOE_QUANT_FP8_TENSOR) &&
+        size_t(H > I ? H : I) * sizeof(float) <= 200 * 1024)
+        return decode::forward(a, a_scale, b, b_scale, b1, b1_scale, d, m_indices, fp8 ? act_bf16 : act, amax, T, H, I,
+                               E, k, fp8, stream);
 
     int rc = route::route_sort(m_indices, n, E, counts, offsets, mtile_prefix, dest_to_src, nullptr, ws + L.sort_ws,
                                L.sort_ws_bytes, stream);

@@ -27,7 +27,7 @@ def _worker(rank, world, init_file, mode, impl, results):
         E, T, H, I, k = 8, 300, 512, 384, 2
         _, b, b1, _, _ = make_inputs(100, T, H, I, E, k, 1.0, 0.05)       # the model, same on every rank
         a, _, _, _, m_indices = make_inputs(200 + rank, T, H, I, E, k, 1.0, 0.05)
-        if rank == 1:
+        if rank == world - 1:
             m_indices[3, 0] = -1
         weights = torch.rand(T, k)
         lo, hi = ep.expert_range(rank, world, E)
@@ -67,11 +67,13 @@ def _worker(rank, world, init_file, mode, impl, results):
         dist.destroy_process_group()
 
 
+@pytest.mark.parametrize("world", [1, 2])
 @pytest.mark.parametrize("mode,impl", [(0, "nccl"), (512, "nccl"), (1024, "nccl"), (0, "peer"), (1024, "peer")])
-def test_expert_parallel_matches_single_gpu(mode, impl):
-    if torch.cuda.device_count() < 2:
+def test_expert_parallel_matches_single_gpu(mode, impl, world):
+    """world = 1 runs the whole exchange (count matrix, plan, dispatch, row-address epilogue, flags) on one
+    GPU, so the kernels of csrc/ep.cu are exercised where only one device is available."""
+    if torch.cuda.device_count() < world:
         pytest.skip("needs two GPUs")
-    world = 2
     with tempfile.TemporaryDirectory() as tmp:
         results = mp.Manager().dict()
         mp.spawn(_worker, args=(world, os.path.join(tmp, "init"), mode, impl, results), nprocs=world, join=True)
