@@ -391,38 +391,57 @@ def main():
     value = flops_step / (ms_step * 1e-3) / 1e12
 
     # ---- end to end through the drop-in call with host buffers (rank-local copies inside the timed region)
-    # every rank copies its own step inputs from pinned host memory and reads its result back
-    e2e = None
+    # End to end through the public call with host buffers: every step copies its own inputs from pinned
+    # host memory and reads its result back. Steps are double-buffered over three streams (copy-in,
+    # compute, copy-out) as a serving loop would do, so a step's PCIe copies overlap other steps' compute.
     h_aq = aq.cpu().pin_memory()
     h_as = as_.cpu().pin_memory() if as_ is not None else None
     h_idx = idx.cpu().pin_memory()
-    h_d = torch.empty((T, k, H), dtype=torch.bfloat16).pin_memory()
-    d_aq, d_as, d_idx = torch.empty_like(aq), (torch.empty_like(as_) if as_ is not None else None), torch.empty_like(idx)
     dummy = torch.ones(1, device=dev)
+    comp, s_in, s_out = torch.cuda.current_stream(), torch.cuda.Stream(), torch.cuda.Stream()
+    bufs = []
+    for _ in range(2):
+        bufs.append(dict(aq=torch.empty_like(aq), as_=torch.empty_like(as_) if as_ is not None else None,
+                         idx=torch.empty_like(idx), d=torch.empty((T, k, H), dtype=torch.bfloat16, device=dev),
+                         h_d=torch.empty((T, k, H), dtype=torch.bfloat16).pin_memory(),
+                         ev_in=torch.cuda.Event(), ev_comp=torch.cuda.Event(), ev_out=torch.cuda.Event()))
     if world == 1:
         fn = moe_test.m_grouped_moe_nt_contiguous_fp8_bf16 if mode else moe_test.m_grouped_moe_nt_contiguous_bf16
 
-        def e2e_forward():
-            fn((d_aq, d_as if mode else dummy), (bq, bs if mode else dummy), (b1q, b1s if mode else dummy), d, d_idx,
-               ws, mode)
-            return d
+        def e2e_forward(bf):
+            fn((bf["aq"], bf["as_"] if mode else dummy), (bq, bs if mode else dummy), (b1q, b1s if mode else dummy),
+               bf["d"], bf["idx"], ws, mode)
     else:
-        def e2e_forward():
-            return layer.forward(d_aq, d_as, d_idx, None)
+        def e2e_forward(bf):
+            bf["d"].copy_(layer.forward(bf["aq"], bf["as_"], bf["idx"], None))  # out of the exchange buffer
 
-    def e2e_step():
-        d_aq.copy_(h_aq, non_blocking=True)
-        if h_as is not None:
-            d_as.copy_(h_as, non_blocking=True)
-        d_idx.copy_(h_idx, non_blocking=True)
-        h_d.copy_(e2e_forward(), non_blocking=True)
+    def e2e_step(i):
+        bf = bufs[i % 2]
+        with torch.cuda.stream(s_in):
+            s_in.wait_event(bf["ev_comp"])  # the step that last read these input buffers is done
+            bf["aq"].copy_(h_aq, non_blocking=True)
+            if h_as is not None:
+                bf["as_"].copy_(h_as, non_blocking=True)
+            bf["idx"].copy_(h_idx, non_blocking=True)
+            bf["ev_in"].record(s_in)
+        comp.wait_event(bf["ev_in"])
+        comp.wait_event(bf["ev_out"])       # the previous result in this output buffer has been read back
+        e2e_forward(bf)
+        bf["ev_comp"].record(comp)
+        with torch.cuda.stream(s_out):
+            s_out.wait_event(bf["ev_comp"])
+            bf["h_d"].copy_(bf["d"], non_blocking=True)
+            bf["ev_out"].record(s_out)
 
-    for _ in range(3):
-        e2e_step()
+    for i in range(4):
+        e2e_step(i)
+    comp.wait_stream(s_out)
     barrier()
     ev0.record()
-    for _ in range(args.steps):
-        e2e_step()
+    s_in.wait_event(ev0)
+    for i in range(args.steps):
+        e2e_step(i)
+    comp.wait_stream(s_out)
     ev1.record()
     barrier()
     e2e_ms = ev0.elapsed_time(ev1) / args.steps
@@ -432,7 +451,8 @@ def main():
         e2e_ms = float(tmax.item())
     h2d = h_aq.numel() * h_aq.element_size() + (h_as.numel() * 4 if h_as is not None else 0) + h_idx.numel() * 4
     e2e = {"value": flops_step / (e2e_ms * 1e-3) / 1e12, "unit": "TFLOP/s", "ms_per_step": e2e_ms,
-           "h2d_bytes_per_step": h2d * world, "d2h_bytes_per_step": h_d.numel() * h_d.element_size() * world}
+           "h2d_bytes_per_step": h2d * world, "d2h_bytes_per_step": T * k * H * 2 * world,
+           "pipelining": "double-buffered: copy-in, compute and copy-out streams"}
 
     # ---- roofline of the dominant kernel: the fc1 grouped GEMM timed alone on this step's own operands
     roofline = None
