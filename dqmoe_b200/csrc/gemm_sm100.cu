@@ -793,8 +793,9 @@ static bool use_pairs(int n, int E, int quant_mode) {
         forced = env == nullptr ? -1 : (env[0] == '0' ? 0 : 1);
     }
     if (forced >= 0) return forced == 1;
-    // Block mode hands a TMEM buffer back every K block; the cross-CTA hops of a pair lengthen that
-    // round trip (measured: 0.5x), the other modes gain a few percent.
+    // Block mode hands a TMEM buffer back every K block and is bound by that round trip, not by the
+    // shared-memory traffic a pair saves (measured: +1 % with pairs, while ragged experts waste more
+    // rows in 256-row tiles), so it stays on single CTAs.
     return quant_mode != DQMOE_QUANT_FP8_BLOCK && n / E >= 512;
 }
 

@@ -204,8 +204,12 @@ __device__ __forceinline__ uint32_t map_to_cta(const void* smem_ptr, uint32_t ra
     asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(out) : "r"(smem_u32(smem_ptr)), "r"(rank));
     return out;
 }
+// Arrive on an mbarrier of any CTA of the cluster. CTA-scope release only: a cluster-scope release
+// costs a round trip through L2 (about a thousand cycles per arrival, measured), and the waiters
+// here need no memory ordering from the arriving thread, only the arrival itself (TMEM reads are
+// ordered by tcgen05.wait::ld and the tcgen05 fences).
 __device__ __forceinline__ void mbar_arrive_cluster(uint32_t cluster_addr) {
-    asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];" ::"r"(cluster_addr) : "memory");
+    asm volatile("mbarrier.arrive.shared::cluster.b64 _, [%0];" ::"r"(cluster_addr) : "memory");
 }
 // 2-D tiled load into this CTA's shared memory whose completion bytes are credited to an
 // mbarrier that may live in the other CTA of the pair (given as a shared::cluster address).
