@@ -491,12 +491,43 @@ def main():
                                  f"of {pk['source']}; nominal dense {'FP8 4500' if mode else 'BF16 2250'} TFLOP/s",
                     "ms_per_launch": fc1_ms, "traffic": None}
         roofline["traffic"] = NCU_FC1_DRAM_BYTES.get(args.workload)
+    elif mode in (0, 1024):
+        # Expert parallel: the same kernel timed alone on rank 0's expert shard, with this rank's rows repeated k
+        # times and split evenly over its experts (the received rows of a step have this size on average).
+        e_loc = layer.wq[0].shape[0]
+        rows = aq.repeat_interleave(k, dim=0)
+        rows_s = as_.repeat_interleave(k, dim=0) if as_ is not None else None
+        cuts = [(n * i) // e_loc for i in range(e_loc + 1)]
+        offs = torch.tensor(cuts, dtype=torch.int32, device=dev)
+        mt = ops.mtile_prefix(offs)
+        out1 = torch.empty((n, I), dtype=torch.uint8 if mode else torch.bfloat16, device=dev)
+        out1_s = torch.empty((n, (I + 127) // 128), dtype=torch.float32, device=dev)
+
+        def fc1():
+            ops.grouped_gemm(rows, rows_s, layer.wq[0], layer.wq[1], offs, mt, I, mode, True, out1, out_scale=out1_s)
+        for _ in range(3):
+            fc1()
+        torch.cuda.synchronize()
+        ev0.record()
+        for _ in range(args.steps):
+            fc1()
+        ev1.record()
+        torch.cuda.synchronize()
+        fc1_ms = ev0.elapsed_time(ev1) / args.steps
+        achieved = 2.0 * n * (2 * I) * H / (fc1_ms * 1e-3) / 1e12
+        peak = pk["bf16"] * (2.0 if mode else 1.0)
+        roofline = {"bound": "tensor", "kernel": "moe_GemmGrouped_GemmUniversal_tcgen05 (fc1, gated), rank 0's shard",
+                    "achieved": achieved, "peak": peak, "unit": "TFLOP/s", "frac": achieved / peak,
+                    "peak_note": ("2 x measured bf16 burst (no FP8 peak was measured); " if mode else "") +
+                                 f"of {pk['source']}; nominal dense {'FP8 4500' if mode else 'BF16 2250'} TFLOP/s",
+                    "ms_per_launch": fc1_ms, "traffic": None}
 
     if rank != 0:
         if world > 1:
             dist.destroy_process_group()
         return
-    base = None if args.no_cpu_baseline else cpu_baseline(wl, 2048)
+    # the CPU baseline is timed at N=1 only (torchrun also pins the host threads to one per rank)
+    base = None if args.no_cpu_baseline or world > 1 else cpu_baseline(wl, 2048)
     out = {
         "metric": "moe_layer_fp8_tflops" if mode else "moe_layer_bf16_tflops",
         "value": value, "unit": "TFLOP/s", "n_gpus": world, "steps": args.steps, "warmup": max(args.warmup, 3),

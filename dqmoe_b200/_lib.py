@@ -29,6 +29,7 @@ SIGNATURES = {
     "dqmoe_moe_workspace_ptr": (_ptr, [_ptr] + [_c_int] * 7),
     "dqmoe_moe_block_workspace_bytes": (_c_size, [_c_int] * 6),
     "dqmoe_moe_block": (_c_int, [_ptr] * 8 + [_c_size] + [_c_int] * 7 + [_ptr]),
+    "dqmoe_moe_block_shared": (_c_int, [_ptr] * 8 + [_c_size] + [_c_int] * 8 + [_ptr]),
     "dqmoe_route_topk": (_c_int, [_ptr, _c_int, _c_int, _c_int, _c_int, _ptr, _ptr, _ptr]),
     "dqmoe_route_sort_workspace_bytes": (_c_size, [_c_int, _c_int]),
     "dqmoe_route_sort": (_c_int, [_ptr, _c_int, _c_int, _ptr, _ptr, _ptr, _ptr, _ptr, _c_size, _ptr]),
@@ -53,6 +54,14 @@ SIGNATURES = {
     "dqmoe_ep_row_ptrs": (_c_int, [_ptr, _ptr, _c_int, _ptr, _c_int, _c_size, _c_int, _ptr, _ptr]),
     "dqmoe_mtile_prefix": (_c_int, [_ptr, _c_int, _ptr, _ptr]),
     "dqmoe_requant_from_amax": (_c_int, [_ptr, _c_i64, _c_int, _ptr, _c_int, _ptr, _ptr, _ptr]),
+    "dqmoe_plugin_create": (_c_int, [_ptr, ctypes.POINTER(_ptr)]),
+    "dqmoe_plugin_destroy": (None, [_ptr]),
+    "dqmoe_plugin_get_fields": (_c_int, [_ptr, _ptr]),
+    "dqmoe_plugin_workspace_size": (_c_size, [_ptr, _c_int]),
+    "dqmoe_plugin_enqueue": (_c_int, [_ptr, _c_int, _ptr, _ptr, _ptr, _ptr]),
+    "dqmoe_plugin_serialization_size": (_c_size, []),
+    "dqmoe_plugin_serialize": (_c_int, [_ptr, _ptr, _c_size]),
+    "dqmoe_plugin_deserialize": (_c_int, [_ptr, _c_size, ctypes.POINTER(_ptr)]),
 }
 
 _lib = None

@@ -13,6 +13,8 @@ namespace route {
 size_t sort_workspace_bytes(int n, int E);
 int route_sort(const int* ids, int n, int E, int* counts, int* offsets, int* mtile_prefix, int* dest_to_src,
                int* src_to_dest, void* ws, size_t ws_bytes, cudaStream_t stream);
+int route_topk(const float* logits, int T, int E, int k, int n_shared, int scoring, int* indices, float* weights,
+               cudaStream_t stream);
 }  // namespace route
 namespace gemm {
 int grouped_gemm(const void* a, const float* a_scale, const void* w, const float* w_scale, const int* offsets,
@@ -203,11 +205,16 @@ size_t dqmoe_moe_block_workspace_bytes(int T, int H, int I, int E, int k, int qu
     return block_layout(T, H, I, E, k, quant_mode).total;
 }
 
-int dqmoe_moe_block(const void* x_bf16, const float* logits, const void* b, const float* b_scale, const void* b1,
-                    const float* b1_scale, void* out_bf16, void* workspace, size_t workspace_bytes, int T, int H,
-                    int I, int E, int k, int scoring, int quant_mode, dqmoe_stream_t stream_) {
-    cudaStream_t stream = static_cast<cudaStream_t>(stream_);
-    DQ_CHECK(T >= 0 && H > 0 && I > 0 && E > 0 && k > 0);
+// The block with `n_shared` shared experts: the weight tensors hold E routed experts followed by the shared ones,
+// and every token gets n_shared extra slots (expert E + j, weight 1) that run through the same sort, gather,
+// grouped GEMMs and weighted sum as the routed slots.
+static int moe_block_impl(const void* x_bf16, const float* logits, const void* b, const float* b_scale, const void* b1,
+                          const float* b1_scale, void* out_bf16, void* workspace, size_t workspace_bytes, int T, int H,
+                          int I, int E_routed, int k_routed, int n_shared, int scoring, int quant_mode,
+                          cudaStream_t stream) {
+    DQ_CHECK(T >= 0 && H > 0 && I > 0 && E_routed > 0 && k_routed > 0 && n_shared >= 0);
+    const int E = E_routed + n_shared;
+    const int k = k_routed + n_shared;
     DQ_CHECK_FMT(quant_mode == DQMOE_QUANT_NONE || quant_mode == DQMOE_QUANT_FP8_BLOCK,
                  "quant_mode=%d: the fused block supports bf16 (0) and block FP8 (1024)", quant_mode);
     if (T == 0) return DQMOE_OK;
@@ -238,7 +245,7 @@ int dqmoe_moe_block(const void* x_bf16, const float* logits, const void* b, cons
     void* act = lws + L.act;
     float* act_scale = reinterpret_cast<float*>(lws + L.act_scale);
 
-    int rc = dqmoe_route_topk(logits, T, E, k, scoring, indices, weights, stream);
+    int rc = route::route_topk(logits, T, E_routed, k_routed, n_shared, scoring, indices, weights, stream);
     if (rc != DQMOE_OK) return rc;
     rc = route::route_sort(indices, n, E, counts, offsets, mtile_prefix, dest_to_src, nullptr, lws + L.sort_ws,
                            L.sort_ws_bytes, stream);
@@ -255,6 +262,22 @@ int dqmoe_moe_block(const void* x_bf16, const float* logits, const void* b, cons
                             nullptr, dest_to_src, nullptr, stream);
     if (rc != DQMOE_OK) return rc;
     return dqmoe_finalize_weighted(d, weights, out_bf16, T, k, H, stream);
+}
+
+
+int dqmoe_moe_block(const void* x_bf16, const float* logits, const void* b, const float* b_scale, const void* b1,
+                    const float* b1_scale, void* out_bf16, void* workspace, size_t workspace_bytes, int T, int H,
+                    int I, int E, int k, int scoring, int quant_mode, dqmoe_stream_t stream) {
+    return moe_block_impl(x_bf16, logits, b, b_scale, b1, b1_scale, out_bf16, workspace, workspace_bytes, T, H, I, E,
+                              k, 0, scoring, quant_mode, static_cast<cudaStream_t>(stream));
+}
+
+int dqmoe_moe_block_shared(const void* x_bf16, const float* logits, const void* b, const float* b_scale,
+                           const void* b1, const float* b1_scale, void* out_bf16, void* workspace,
+                           size_t workspace_bytes, int T, int H, int I, int E, int k, int n_shared, int scoring,
+                           int quant_mode, dqmoe_stream_t stream) {
+    return moe_block_impl(x_bf16, logits, b, b_scale, b1, b1_scale, out_bf16, workspace, workspace_bytes, T, H, I, E,
+                              k, n_shared, scoring, quant_mode, static_cast<cudaStream_t>(stream));
 }
 
 }  // extern "C"

@@ -272,10 +272,11 @@ int route_sort(const int* ids, int n, int E, int* counts, int* offsets, int* mti
 // ---------------------------------------------------------------- top-k router
 // One warp per token. Ranking is by logit (both scoring functions are monotonic),
 // value descending then expert id ascending; weights are the selected scores
-// normalised to sum 1.
+// normalised to sum 1. Output rows have `slots` >= k entries: entries k.. name the shared
+// experts E, E+1, ... (every token, weight 1), which the layer then treats like routed ones.
 template <int kPerLane>
 __global__ void __launch_bounds__(256) route_topk_kernel(const float* __restrict__ logits, int T, int E, int k,
-                                                         int scoring, int* __restrict__ indices,
+                                                         int slots, int scoring, int* __restrict__ indices,
                                                          float* __restrict__ weights) {
     const int warp = (blockIdx.x * blockDim.x + threadIdx.x) >> 5;
     const int lane = threadIdx.x & 31;
@@ -325,24 +326,29 @@ __global__ void __launch_bounds__(256) route_topk_kernel(const float* __restrict
         }
     }
     if (lane < k) {
-        indices[size_t(warp) * k + lane] = sel_idx;
-        weights[size_t(warp) * k + lane] = sel_score / denom;
+        indices[size_t(warp) * slots + lane] = sel_idx;
+        weights[size_t(warp) * slots + lane] = sel_score / denom;
+    } else if (lane < slots) {
+        indices[size_t(warp) * slots + lane] = E + (lane - k);
+        weights[size_t(warp) * slots + lane] = 1.0f;
     }
 }
 
-int route_topk(const float* logits, int T, int E, int k, int scoring, int* indices, float* weights,
+int route_topk(const float* logits, int T, int E, int k, int n_shared, int scoring, int* indices, float* weights,
                cudaStream_t stream) {
     DQ_CHECK(T >= 0 && E > 0 && E <= kMaxExperts && k > 0 && k <= 32 && k <= E);
+    DQ_CHECK_FMT(n_shared >= 0 && k + n_shared <= 32 && E + n_shared <= kMaxExperts, "n_shared=%d", n_shared);
+    const int slots = k + n_shared;
     DQ_CHECK(scoring == DQMOE_SCORE_SOFTMAX || scoring == DQMOE_SCORE_SIGMOID);
     if (T == 0) return DQMOE_OK;
     DQ_CHECK(logits != nullptr && indices != nullptr && weights != nullptr);
     const int blocks = ceil_div(T, 8);
-    if (E <= 32) route_topk_kernel<1><<<blocks, 256, 0, stream>>>(logits, T, E, k, scoring, indices, weights);
-    else if (E <= 64) route_topk_kernel<2><<<blocks, 256, 0, stream>>>(logits, T, E, k, scoring, indices, weights);
-    else if (E <= 128) route_topk_kernel<4><<<blocks, 256, 0, stream>>>(logits, T, E, k, scoring, indices, weights);
-    else if (E <= 256) route_topk_kernel<8><<<blocks, 256, 0, stream>>>(logits, T, E, k, scoring, indices, weights);
-    else if (E <= 512) route_topk_kernel<16><<<blocks, 256, 0, stream>>>(logits, T, E, k, scoring, indices, weights);
-    else route_topk_kernel<32><<<blocks, 256, 0, stream>>>(logits, T, E, k, scoring, indices, weights);
+    if (E <= 32) route_topk_kernel<1><<<blocks, 256, 0, stream>>>(logits, T, E, k, slots, scoring, indices, weights);
+    else if (E <= 64) route_topk_kernel<2><<<blocks, 256, 0, stream>>>(logits, T, E, k, slots, scoring, indices, weights);
+    else if (E <= 128) route_topk_kernel<4><<<blocks, 256, 0, stream>>>(logits, T, E, k, slots, scoring, indices, weights);
+    else if (E <= 256) route_topk_kernel<8><<<blocks, 256, 0, stream>>>(logits, T, E, k, slots, scoring, indices, weights);
+    else if (E <= 512) route_topk_kernel<16><<<blocks, 256, 0, stream>>>(logits, T, E, k, slots, scoring, indices, weights);
+    else route_topk_kernel<32><<<blocks, 256, 0, stream>>>(logits, T, E, k, slots, scoring, indices, weights);
     DQ_LAUNCH_CHECK();
     return DQMOE_OK;
 }
@@ -381,7 +387,7 @@ int dqmoe_segment_ids(const int32_t* counts, const int32_t* values, int S, int32
 
 int dqmoe_route_topk(const float* logits, int T, int E, int k, int scoring, int32_t* indices, float* weights,
                      dqmoe_stream_t stream) {
-    return dq::route::route_topk(logits, T, E, k, scoring, indices, weights, static_cast<cudaStream_t>(stream));
+    return dq::route::route_topk(logits, T, E, k, 0, scoring, indices, weights, static_cast<cudaStream_t>(stream));
 }
 
 }  // extern "C"

@@ -178,6 +178,7 @@ class ExpertParallelMoE:
         else:
             raise RuntimeError("[ASSERT FAILED] ep.py  Condition: mode in (0, 512, 1024)")
         del b, b1
+        self.wq = wq  # (fc1 weights, scales, fc2 weights, scales) of this rank's experts
         # exchange over peer memory where it is built (bf16, block FP8); DQMOE_EP_IMPL=nccl selects the collectives
         import os
         use_peer = mode in (0, 1024) and os.environ.get("DQMOE_EP_IMPL", "peer") == "peer" and world <= 8

@@ -72,22 +72,29 @@ def moe_forward(a, a_scale, b, b_scale, b1, b1_scale, d, m_indices, workspace, q
 
 
 def moe_block(x: torch.Tensor, logits: torch.Tensor, b, b_scale, b1, b1_scale, k: int, scoring: str = "softmax",
-              quant_mode: int = QUANT_FP8_BLOCK, workspace: Optional[torch.Tensor] = None) -> torch.Tensor:
-    """Router -> layer -> weighted combine from bf16 activations x [T, H]; see dqmoe_moe_block."""
+              quant_mode: int = QUANT_FP8_BLOCK, workspace: Optional[torch.Tensor] = None,
+              n_shared: int = 0) -> torch.Tensor:
+    """Router -> layer -> weighted combine from bf16 activations x [T, H]; see dqmoe_moe_block.
+
+    With n_shared > 0 the last n_shared experts of b / b1 are shared experts that every token
+    passes through with weight 1 (dqmoe_moe_block_shared); logits are [T, E - n_shared]."""
     lib = _lib.load()
     for name, t in (("x", x), ("logits", logits), ("b", b), ("b1", b1)):
         _cuda(t, name)
     T, H = x.shape
-    E, I = b.shape[0], b1.shape[2]
-    need = int(lib.dqmoe_moe_block_workspace_bytes(T, H, I, E, k, int(quant_mode)))
+    E_all, I = b.shape[0], b1.shape[2]
+    E = E_all - n_shared
+    if n_shared < 0 or E <= 0 or logits.shape[1] != E:
+        raise RuntimeError("[ASSERT FAILED] ops.py  Condition: logits is [T, num_experts - n_shared]")
+    need = int(lib.dqmoe_moe_block_workspace_bytes(T, H, I, E_all, k + n_shared, int(quant_mode)))
     if workspace is None:
         workspace = torch.empty(max(need, 256), dtype=torch.uint8, device=x.device)
     out = torch.empty((T, H), dtype=torch.bfloat16, device=x.device)
     mode = {"softmax": SCORE_SOFTMAX, "sigmoid": SCORE_SIGMOID}[scoring]
     with torch.cuda.device(x.device):
-        _lib.check(lib.dqmoe_moe_block(_p(x), _p(logits), _p(b), _p(b_scale), _p(b1), _p(b1_scale), _p(out),
-                                       _p(workspace), workspace.numel(), T, H, I, E, k, mode, int(quant_mode),
-                                       _stream(x.device)))
+        _lib.check(lib.dqmoe_moe_block_shared(_p(x), _p(logits), _p(b), _p(b_scale), _p(b1), _p(b1_scale), _p(out),
+                                              _p(workspace), workspace.numel(), T, H, I, E, k, n_shared, mode,
+                                              int(quant_mode), _stream(x.device)))
     return out
 
 

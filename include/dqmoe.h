@@ -125,6 +125,71 @@ int dqmoe_moe_block(const void* x_bf16, const float* logits, const void* b, cons
                     size_t workspace_bytes, int T, int H, int I, int E, int k, int scoring,
                     int quant_mode, dqmoe_stream_t stream);
 
+/*
+ * The same block with n_shared shared experts (DeepSeek-style: every token also runs
+ * through them, weight 1). b / b1 and their scales hold E routed experts followed by the
+ * n_shared shared ones (E + n_shared in all, same H and I); logits stay [T, E]. The
+ * shared experts occupy k..k+n_shared-1 of each token's slots and go through the same
+ * sort, gather, grouped GEMMs and weighted sum. Size the workspace with
+ * dqmoe_moe_block_workspace_bytes(T, H, I, E + n_shared, k + n_shared, quant_mode).
+ * No counterpart in the reference.
+ */
+int dqmoe_moe_block_shared(const void* x_bf16, const float* logits, const void* b, const float* b_scale,
+                           const void* b1, const float* b1_scale, void* out_bf16, void* workspace,
+                           size_t workspace_bytes, int T, int H, int I, int E, int k, int n_shared,
+                           int scoring, int quant_mode, dqmoe_stream_t stream);
+
+/* ------------------------------------------------------------------ plugin-shaped front end */
+
+/*
+ * The layer behind the interface of the reference's "mixture_of_experts" TensorRT plugin
+ * as its test drives it (test/trt_test.py): the nine creation fields (:97-135), the input
+ * list in the plugin's order (:140-150) and one output [num_tokens, top_k, hidden]. A
+ * TensorRT build wraps these calls in IPluginV2DynamicExt (create -> the creator's
+ * createPlugin, workspace_size -> getWorkspaceSize, enqueue -> enqueue, serialize /
+ * deserialize -> serialize / deserializePlugin). The plugin's own source is not part of the
+ * reference; its kernels are the ones dqmoe_moe_forward replaces.
+ *
+ * type / output_type use the nvinfer1::DataType codes below. Built: FP8 operands with
+ * quant_mode 256 / 512 / 1024 and BF16 operands with quant_mode 0; outputs BF16 (written
+ * directly), HALF or FLOAT (converted from the layer's bf16 result through workspace).
+ * type FLOAT / HALF (the reference's unquantised FP32 / FP16 instantiations) and
+ * use_bias != 0 return DQMOE_ERR_INVALID.
+ * enqueue inputs: 0 input [T,H], 1 weight1 [E,2I,H], 2 weight2 [E,H,I], 3 index [T,k] int32,
+ * 4 bias1, 5 bias2 (never read), 6 actscale, 7 scale_a (fc1 weight scales), 8 scale_b (fc2
+ * weight scales); entries 6-8 are read only for FP8 operands. Scale shapes per mode as
+ * listed at the top of this file.
+ */
+#define DQMOE_DT_FLOAT 0
+#define DQMOE_DT_HALF 1
+#define DQMOE_DT_FP8 6
+#define DQMOE_DT_BF16 7
+
+typedef struct dqmoe_plugin_fields {
+    int32_t number_of_experts;
+    int32_t top_k;
+    int32_t expert_hidden_size;
+    int32_t expert_inter_size;
+    int32_t max_num_tokens;
+    int32_t use_bias;
+    int32_t type;
+    int32_t output_type;
+    int32_t quant_mode;
+} dqmoe_plugin_fields;
+
+typedef struct dqmoe_plugin dqmoe_plugin; /* opaque, host memory only */
+
+int dqmoe_plugin_create(const dqmoe_plugin_fields* fields, dqmoe_plugin** out);
+void dqmoe_plugin_destroy(dqmoe_plugin* plugin);
+int dqmoe_plugin_get_fields(const dqmoe_plugin* plugin, dqmoe_plugin_fields* out);
+/* 0 for a null plugin or num_tokens outside [0, max_num_tokens] */
+size_t dqmoe_plugin_workspace_size(const dqmoe_plugin* plugin, int num_tokens);
+int dqmoe_plugin_enqueue(const dqmoe_plugin* plugin, int num_tokens, const void* const* inputs,
+                         void* const* outputs, void* workspace, dqmoe_stream_t stream);
+size_t dqmoe_plugin_serialization_size(void);
+int dqmoe_plugin_serialize(const dqmoe_plugin* plugin, void* buffer, size_t bytes);
+int dqmoe_plugin_deserialize(const void* buffer, size_t bytes, dqmoe_plugin** out);
+
 /* ------------------------------------------------------------------ routing */
 
 /*

@@ -242,10 +242,18 @@ def moe_layer_fp8(a_q, a_s, b_q, b_s, b1_q, b1_s, m_indices, E: int, quant_mode:
     return d
 
 
-def moe_block(x, logits, b, b1, k: int, scoring: str, quant_mode: int, quantized=None) -> torch.Tensor:
-    """Router -> layer -> weighted combine, [T, H] -> [T, H] (parity unpinned as a whole)."""
+def moe_block(x, logits, b, b1, k: int, scoring: str, quant_mode: int, quantized=None, n_shared: int = 0) -> torch.Tensor:
+    """Router -> layer -> weighted combine, [T, H] -> [T, H] (parity unpinned as a whole).
+
+    With n_shared > 0 the last n_shared experts of b / b1 are shared experts: every token runs
+    through them with weight 1, as extra slots after its k routed ones."""
     E = b.shape[0]
     idx, w = route_topk(logits, k, scoring)
+    if n_shared:
+        T = idx.shape[0]
+        extra = torch.arange(E - n_shared, E, dtype=idx.dtype).expand(T, n_shared)
+        idx = torch.cat([idx, extra], dim=1)
+        w = torch.cat([w, torch.ones(T, n_shared, dtype=w.dtype)], dim=1)
     if quant_mode == QUANT_NONE:
         d = moe_layer_bf16(x, b, b1, idx, E)
     else:

@@ -49,3 +49,30 @@ def test_argument_errors_have_reference_format():
     one = ctypes.c_void_p(addr)
     rc = lib.dqmoe_moe_forward(one, None, one, None, one, None, one, one, mis, 0, 4, 64, 64, 2, 1, 0, 1, None)
     assert rc == 1 and "is not aligned!" in lib.dqmoe_last_error().decode()
+
+
+def test_plugin_descriptor_host_calls():
+    """The plugin-shaped front end: creation checks, workspace arithmetic and serialisation need no GPU."""
+    from dqmoe_b200 import plugin
+    p = plugin.MoePlugin(8, 2, 1024, 2048, 64, quant_mode=1024, output_type=plugin.DT_HALF)
+    f = p.fields
+    assert f["number_of_experts"] == 8 and f["quant_mode"] == 1024 and f["output_type"] == plugin.DT_HALF
+    lib = _lib.load()
+    layer = lib.dqmoe_moe_workspace_bytes(64, 1024, 2048, 8, 2, 1024)
+    # HALF output stages the bf16 result [T, k, H] behind the layer's workspace
+    assert p.workspace_size(64) == layer + 64 * 2 * 1024 * 2
+    assert p.workspace_size(65) == 0 and p.workspace_size(-1) == 0
+    direct = plugin.MoePlugin(8, 2, 1024, 2048, 64, quant_mode=1024, output_type=plugin.DT_BF16)
+    assert direct.workspace_size(64) == layer
+    blob = p.serialize()
+    assert len(blob) == 36
+    assert plugin.MoePlugin.deserialize(blob).fields == f
+    with pytest.raises(RuntimeError, match="expected 36"):
+        plugin.MoePlugin.deserialize(blob[:-4])
+    for bad in (dict(use_bias=1), dict(type=plugin.DT_FLOAT, quant_mode=0), dict(type=plugin.DT_HALF, quant_mode=0),
+                dict(type=plugin.DT_BF16, quant_mode=512), dict(type=plugin.DT_FP8, quant_mode=0),
+                dict(output_type=3)):
+        with pytest.raises(RuntimeError, match=r"\[ASSERT FAILED\] plugin.cu"):
+            plugin.MoePlugin(8, 2, 1024, 2048, 64, **bad)
+    with pytest.raises(RuntimeError, match="expert_hidden_size=1000"):
+        plugin.MoePlugin(8, 2, 1000, 2048, 64)

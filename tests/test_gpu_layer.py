@@ -286,6 +286,29 @@ def test_moe_block_router_to_weighted_output(ops, mode, scoring):
     assert_close(out, ref)
 
 
+@pytest.mark.parametrize("mode,n_shared", [(0, 1), (1024, 1), (1024, 2)])
+def test_moe_block_with_shared_experts(ops, mode, n_shared):
+    """dqmoe_moe_block_shared: the last n_shared experts of the weight tensors see every token with weight 1
+    (DeepSeek-style shared experts); checked against the oracle's moe_block with the same slots appended."""
+    E, T, H, I, k = 16, 150, 512, 256, 4
+    a, b, b1, _, _ = make_inputs(41, T, H, I, E + n_shared, k, 1.0, 0.05)
+    logits = torch.randn(T, E, generator=torch.Generator().manual_seed(6))
+    if mode == 0:
+        ref = orc.moe_block(a, logits, b, b1, k, "sigmoid", 0, n_shared=n_shared)
+        out = ops.moe_block(a.to(DEV), logits.to(DEV), b.to(DEV), None, b1.to(DEV), None, k, "sigmoid", 0,
+                            n_shared=n_shared)
+    else:
+        qs = orc.quantize_inputs(a, b, b1, 1024)
+        ref = orc.moe_block(a, logits, b, b1, k, "sigmoid", 1024, quantized=qs, n_shared=n_shared)
+        out = ops.moe_block(a.to(DEV), logits.to(DEV), qs[2].to(DEV), qs[3].to(DEV).contiguous(), qs[4].to(DEV),
+                            qs[5].to(DEV).contiguous(), k, "sigmoid", 1024, n_shared=n_shared)
+    assert ops.device_status() == 0
+    assert_close(out, ref)
+    # without the shared slots the result differs: the shared experts really contributed
+    plain = orc.moe_block(a, logits, b[:E], b1[:E], k, "sigmoid", 0)
+    assert (ref.float() - plain.float()).abs().max() > 0
+
+
 @pytest.mark.parametrize("mode", [0, 256, 1024])
 def test_layer_replays_from_a_cuda_graph(ops, workspace, mode):
     """The layer enqueues kernels only (no host synchronisation, no allocation), so after one warm-up
