@@ -151,7 +151,7 @@ __device__ __forceinline__ ScaleRows scale_rows(bool gated, int nt, int N, int N
 
 __device__ __forceinline__ float silu_bf16(float g) {
     // the torch oracle evaluates silu on bf16 and rounds the result to bf16 (test/util.py:141-142)
-    return bf_round(__fdividef(g, 1.0f + __expf(-g)));
+    return bf_round_cvt(__fdividef(g, 1.0f + __expf(-g)));
 }
 
 // Store 32 rows x 32 bf16 columns held one row per lane (packed[16]) so that each store
@@ -494,13 +494,13 @@ moe_GemmGrouped_GemmUniversal_tcgen05(const __grid_constant__ CUtensorMap tma_a,
                                     sg *= p.sb[size_t(tl.e) * p.w_rows + c];
                                     sv *= p.sb[size_t(tl.e) * p.w_rows + I_or_H + c];
                                 }
-                                const float gate = bf_round(__uint_as_float(g[i + u]) * sg);
-                                const float val = bf_round(__uint_as_float(v[i + u]) * sv);
-                                const float act = bf_round(silu_bf16(gate) * val);
+                                const float gate = bf_round_cvt(__uint_as_float(g[i + u]) * sg);
+                                const float val = bf_round_cvt(__uint_as_float(v[i + u]) * sv);
+                                const float act = bf_round_cvt(silu_bf16(gate) * val);
                                 a2[u] = act;
                                 if (col0 + i + u < I_or_H) amax_local = fmaxf(amax_local, fabsf(act));
                             }
-                            packed[i >> 1] = pack_bf16x2(a2[0], a2[1]);
+                            packed[i >> 1] = pack_bf16x2_exact(a2[0], a2[1]);  // act is already rounded to bf16
                         }
                         store_rows_staged(st.stage[warp - 4], packed,
                                           row_ok ? reinterpret_cast<uint8_t*>(reinterpret_cast<__nv_bfloat16*>(p.out) +
@@ -633,15 +633,28 @@ moe_GemmGrouped_GemmUniversal_tcgen05(const __grid_constant__ CUtensorMap tma_a,
                     // act columns nt*128 + h*64 + [0, 64): gate = acc[0..63], value = acc[64..127]
                     const int col0 = tl.nt * kBoxRows + h * 64;
                     float amax_local = 0.0f;
+                    // The tensor pipe idles during this part (the same warps drain its buffers), so it is
+                    // written for throughput: bf16 roundings on the fp32 pipe (bf_round), eight elements
+                    // per step and stage by stage so that the exp / reciprocal latencies overlap.
 #pragma unroll
-                    for (int i = 0; i < 64; ++i) {
-                        const float gate = bf_round(acc[i]);
-                        const float val = bf_round(acc[64 + i]);
-                        float act = bf_round(silu_bf16(gate) * val);
-                        if (col0 + i >= I_or_H) act = 0.0f;
-                        acc[i] = act;
-                        amax_local = fmaxf(amax_local, fabsf(act));
+                    for (int i0 = 0; i0 < 64; i0 += 8) {
+                        float g8[8], e8[8];
+#pragma unroll
+                        for (int j = 0; j < 8; ++j) {
+                            g8[j] = bf_round(acc[i0 + j]);
+                            e8[j] = __expf(-g8[j]);
+                        }
+#pragma unroll
+                        for (int j = 0; j < 8; ++j) e8[j] = bf_round(__fdividef(g8[j], 1.0f + e8[j]));
+#pragma unroll
+                        for (int j = 0; j < 8; ++j) {
+                            float act = bf_round(e8[j] * bf_round(acc[64 + i0 + j]));
+                            if (col0 + i0 + j >= I_or_H) act = 0.0f;
+                            acc[i0 + j] = act;
+                            amax_local = fmaxf(amax_local, fabsf(act));
+                        }
                     }
+                    if (lane == 0) DQ_STAMP(warp - 2, acc_it - 1, 5);
                     // the 1x128 group spans both halves: exchange the partial amax through shared memory
                     st.amax[tile_it & 1u][h][r_in_tile] = amax_local;
                     __syncwarp();
@@ -651,6 +664,7 @@ moe_GemmGrouped_GemmUniversal_tcgen05(const __grid_constant__ CUtensorMap tma_a,
                         break;
                     }
                     epi_phase ^= 1u;
+                    if (lane == 0) DQ_STAMP(warp - 2, acc_it - 1, 6);
                     const float amax = fmaxf(amax_local, st.amax[tile_it & 1u][h ^ 1][r_in_tile]);
                     const float sf = scale_from_amax(amax);
                     const float inv = inv_scale(sf);
@@ -665,6 +679,7 @@ moe_GemmGrouped_GemmUniversal_tcgen05(const __grid_constant__ CUtensorMap tma_a,
                                           row_ok ? reinterpret_cast<uint8_t*>(p.out) + size_t(grow) * I_or_H + col0 : nullptr,
                                           min(4, max(0, (I_or_H - col0 + 15) / 16)), lane);
                         if (row_ok && h == 0) p.out_scale[size_t(grow) * ((I_or_H + 127) / 128) + tl.nt] = sf;
+                        if (lane == 0) DQ_STAMP(warp - 2, acc_it - 1, 7);
                     }
                 } else {
                     int orow_idx = grow;
