@@ -479,28 +479,43 @@ moe_GemmGrouped_GemmUniversal_tcgen05(const __grid_constant__ CUtensorMap tma_a,
                         const int c0 = h * kHalf + j * 32;  // column inside the kBox-wide act tile
                         ptx::tmem_ld32(t_buf + c0, g);
                         ptx::tmem_ld32(t_buf + kBox + c0, v);
+                        const int col0 = tl.nt * kBox + c0;
+                        if constexpr (kMode == kChannel) {
+                            // this chunk's 32 gate and 32 value column scales, staged once per warp and read back
+                            // as broadcast 16-byte loads (the buffer is free until the staged store below)
+                            float* csw = reinterpret_cast<float*>(st.stage[warp - 4]);
+                            __syncwarp();
+                            const int c = min(col0 + lane, I_or_H - 1);
+                            csw[lane] = p.sb[size_t(tl.e) * p.w_rows + c];
+                            csw[32 + lane] = p.sb[size_t(tl.e) * p.w_rows + I_or_H + c];
+                            __syncwarp();
+                        }
                         ptx::tmem_wait_ld(g);
                         ptx::tmem_wait_ld(v);
-                        const int col0 = tl.nt * kBox + c0;
                         uint32_t packed[16];
+                        // This epilogue runs beside the next tile's MMAs; its roundings use the conversion
+                        // instruction (one issue slot each), which measured faster here than bf_round.
+                        [[maybe_unused]] const float4* cs4 = reinterpret_cast<const float4*>(st.stage[warp - 4]);
 #pragma unroll
-                        for (int i = 0; i < 32; i += 2) {
-                            float a2[2];
+                        for (int i = 0; i < 32; i += 4) {
+                            float sg[4] = {row_scale, row_scale, row_scale, row_scale};
+                            float sv[4] = {row_scale, row_scale, row_scale, row_scale};
+                            if constexpr (kMode == kChannel) {
+                                const float4 a = cs4[i >> 2], b = cs4[8 + (i >> 2)];
+                                sg[0] *= a.x, sg[1] *= a.y, sg[2] *= a.z, sg[3] *= a.w;
+                                sv[0] *= b.x, sv[1] *= b.y, sv[2] *= b.z, sv[3] *= b.w;
+                            }
+                            float a4[4];
 #pragma unroll
-                            for (int u = 0; u < 2; ++u) {
-                                float sg = row_scale, sv = row_scale;
-                                if constexpr (kMode == kChannel) {
-                                    const int c = min(col0 + i + u, I_or_H - 1);
-                                    sg *= p.sb[size_t(tl.e) * p.w_rows + c];
-                                    sv *= p.sb[size_t(tl.e) * p.w_rows + I_or_H + c];
-                                }
-                                const float gate = bf_round_cvt(__uint_as_float(g[i + u]) * sg);
-                                const float val = bf_round_cvt(__uint_as_float(v[i + u]) * sv);
+                            for (int u = 0; u < 4; ++u) {
+                                const float gate = bf_round_cvt(__uint_as_float(g[i + u]) * sg[u]);
+                                const float val = bf_round_cvt(__uint_as_float(v[i + u]) * sv[u]);
                                 const float act = bf_round_cvt(silu_bf16(gate) * val);
-                                a2[u] = act;
+                                a4[u] = act;
                                 if (col0 + i + u < I_or_H) amax_local = fmaxf(amax_local, fabsf(act));
                             }
-                            packed[i >> 1] = pack_bf16x2_exact(a2[0], a2[1]);  // act is already rounded to bf16
+                            packed[i >> 1] = pack_bf16x2_exact(a4[0], a4[1]);  // act is already rounded to bf16
+                            packed[(i >> 1) + 1] = pack_bf16x2_exact(a4[2], a4[3]);
                         }
                         store_rows_staged(st.stage[warp - 4], packed,
                                           row_ok ? reinterpret_cast<uint8_t*>(reinterpret_cast<__nv_bfloat16*>(p.out) +
@@ -533,17 +548,26 @@ moe_GemmGrouped_GemmUniversal_tcgen05(const __grid_constant__ CUtensorMap tma_a,
                         uint32_t r[32];
                         const int tc = (c / kChunks) * kBox + h * kHalf + (c % kChunks) * 32;
                         ptx::tmem_ld32(t_buf + tc, r);
-                        ptx::tmem_wait_ld(r);
                         const int col0 = tl.nt * kN + tc;
+                        if constexpr (kMode == kChannel) {  // column scales of the chunk, as in stage 1
+                            float* csw = reinterpret_cast<float*>(st.stage[warp - 4]);
+                            __syncwarp();
+                            csw[lane] = p.sb[size_t(tl.e) * p.w_rows + min(col0 + lane, I_or_H - 1)];
+                            __syncwarp();
+                        }
+                        ptx::tmem_wait_ld(r);
                         uint32_t packed[16];
+                        [[maybe_unused]] const float4* cs4 = reinterpret_cast<const float4*>(st.stage[warp - 4]);
 #pragma unroll
-                        for (int i = 0; i < 32; i += 2) {
-                            float s0 = row_scale, s1 = row_scale;
+                        for (int i = 0; i < 32; i += 4) {
+                            float sc[4] = {row_scale, row_scale, row_scale, row_scale};
                             if constexpr (kMode == kChannel) {
-                                s0 *= p.sb[size_t(tl.e) * p.w_rows + min(col0 + i, I_or_H - 1)];
-                                s1 *= p.sb[size_t(tl.e) * p.w_rows + min(col0 + i + 1, I_or_H - 1)];
+                                const float4 a = cs4[i >> 2];
+                                sc[0] *= a.x, sc[1] *= a.y, sc[2] *= a.z, sc[3] *= a.w;
                             }
-                            packed[i >> 1] = pack_bf16x2(__uint_as_float(r[i]) * s0, __uint_as_float(r[i + 1]) * s1);
+                            packed[i >> 1] = pack_bf16x2(__uint_as_float(r[i]) * sc[0], __uint_as_float(r[i + 1]) * sc[1]);
+                            packed[(i >> 1) + 1] =
+                                pack_bf16x2(__uint_as_float(r[i + 2]) * sc[2], __uint_as_float(r[i + 3]) * sc[3]);
                         }
                         store_rows_staged(st.stage[warp - 4], packed,
                                           row_ok && orow_idx >= 0 ? reinterpret_cast<uint8_t*>(orow + col0) : nullptr,
