@@ -42,35 +42,59 @@ __device__ __forceinline__ float block_max(float v, float* s_red) {
 }
 
 // One block per row (grid-stride): amax pass, then quantise pass (second read hits L1/L2).
-// kHaveAmax: the per-row (or single) amax was produced elsewhere.
-template <bool kHaveAmax>
 __global__ void __launch_bounds__(kThreads) rowwise_kernel(const uint8_t* __restrict__ x, int64_t rows, int cols,
-                                                           uint8_t* __restrict__ q, float* __restrict__ scale,
-                                                           const float* __restrict__ amax_in, int amax_per_row) {
+                                                           uint8_t* __restrict__ q, float* __restrict__ scale) {
     __shared__ float s_red[kThreads / 32];
     const int vecs = cols / 8;
     for (int64_t r = blockIdx.x; r < rows; r += gridDim.x) {
         const uint8_t* xr = x + size_t(r) * cols * 2;
-        float amax;
-        if constexpr (kHaveAmax) {
-            amax = amax_in[amax_per_row ? r : 0];
-        } else {
-            float m = 0.0f;
-            for (int i = threadIdx.x; i < vecs; i += kThreads) {
-                float v[8];
-                unpack8(ld_nc16(xr + size_t(i) * 16), v);
-                m = amax8(v, m);
-            }
-            amax = block_max(m, s_red);
+        float m = 0.0f;
+        for (int i = threadIdx.x; i < vecs; i += kThreads) {
+            float v[8];
+            unpack8(ld_nc16(xr + size_t(i) * 16), v);
+            m = amax8(v, m);
         }
+        const float amax = block_max(m, s_red);
         const float sf = scale_from_amax(amax);
         const float inv = inv_scale(sf);
-        if (threadIdx.x == 0 && (amax_per_row || r == 0)) scale[amax_per_row ? r : 0] = sf;
+        if (threadIdx.x == 0) scale[r] = sf;
         uint8_t* qr = q + size_t(r) * cols;
         for (int i = threadIdx.x; i < vecs; i += kThreads) {
             float v[8];
             unpack8(ld_nc16(xr + size_t(i) * 16), v);
             *reinterpret_cast<uint2*>(qr + size_t(i) * 8) = quant8(v, inv);
+        }
+    }
+}
+
+// Second pass over the bf16 intermediate when stage 1 already produced the amax: one warp per row
+// (grid-stride), four 16-byte vectors per lane in flight, the scale arithmetic once per row.
+__global__ void __launch_bounds__(kThreads) requant_rows_kernel(const uint8_t* __restrict__ x, int64_t rows, int cols,
+                                                                uint8_t* __restrict__ q, float* __restrict__ scale,
+                                                                const float* __restrict__ amax_in, int amax_per_row) {
+    const int lane = threadIdx.x & 31;
+    const int64_t warp = (int64_t(blockIdx.x) * kThreads + threadIdx.x) >> 5;
+    const int64_t nwarps = int64_t(gridDim.x) * (kThreads / 32);
+    const int vecs = cols / 8;
+    for (int64_t r = warp; r < rows; r += nwarps) {
+        const float sf = scale_from_amax(amax_in[amax_per_row ? r : 0]);
+        const float inv = inv_scale(sf);
+        if (lane == 0 && (amax_per_row || r == 0)) scale[amax_per_row ? r : 0] = sf;
+        const uint8_t* xr = x + size_t(r) * cols * 2;
+        uint8_t* qr = q + size_t(r) * cols;
+        for (int i0 = lane; i0 < vecs; i0 += 128) {
+            Vec16 raw[4];
+#pragma unroll
+            for (int j = 0; j < 4; ++j)
+                if (i0 + 32 * j < vecs) raw[j] = ld_nc16(xr + size_t(i0 + 32 * j) * 16);
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+                if (i0 + 32 * j < vecs) {
+                    float v[8];
+                    unpack8(raw[j], v);
+                    *reinterpret_cast<uint2*>(qr + size_t(i0 + 32 * j) * 8) = quant8(v, inv);
+                }
+            }
         }
     }
 }
@@ -191,8 +215,8 @@ int dqmoe_quant_fp8_rowwise(const void* x_bf16, int64_t rows, int cols, void* q,
     DQ_CHECK(x_bf16 != nullptr && q != nullptr && scale != nullptr);
     DQ_CHECK_FMT(cols % 8 == 0, "cols=%d must be a multiple of 8", cols);
     DQ_CHECK(is_aligned(x_bf16, 16) && is_aligned(q, 8));
-    quant::rowwise_kernel<false><<<quant::grid_cap(rows, 16), quant::kThreads, 0, static_cast<cudaStream_t>(stream)>>>(
-        static_cast<const uint8_t*>(x_bf16), rows, cols, static_cast<uint8_t*>(q), scale, nullptr, 1);
+    quant::rowwise_kernel<<<quant::grid_cap(rows, 16), quant::kThreads, 0, static_cast<cudaStream_t>(stream)>>>(
+        static_cast<const uint8_t*>(x_bf16), rows, cols, static_cast<uint8_t*>(q), scale);
     DQ_LAUNCH_CHECK();
     return DQMOE_OK;
 }
@@ -204,7 +228,7 @@ int dqmoe_requant_from_amax(const void* act_bf16, int64_t n, int I, const float*
     DQ_CHECK(act_bf16 != nullptr && q != nullptr && scale != nullptr && amax != nullptr);
     DQ_CHECK_FMT(I % 8 == 0, "I=%d must be a multiple of 8", I);
     DQ_CHECK(is_aligned(act_bf16, 16) && is_aligned(q, 8));
-    quant::rowwise_kernel<true><<<quant::grid_cap(n, 16), quant::kThreads, 0, static_cast<cudaStream_t>(stream)>>>(
+    quant::requant_rows_kernel<<<quant::grid_cap((n + 7) / 8, 8), quant::kThreads, 0, static_cast<cudaStream_t>(stream)>>>(
         static_cast<const uint8_t*>(act_bf16), n, I, static_cast<uint8_t*>(q), scale, amax, per_row ? 1 : 0);
     DQ_LAUNCH_CHECK();
     return DQMOE_OK;

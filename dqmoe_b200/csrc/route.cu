@@ -86,16 +86,27 @@ __global__ void __launch_bounds__(1024) sort_scan_kernel(int* __restrict__ chunk
     __shared__ int s_tot[kMaxExperts + 2];
     __shared__ int s_tiles[kMaxExperts + 2];
     __shared__ int s_warp_tot[33];
-    for (int b = threadIdx.x; b <= E; b += blockDim.x) {
+    // one warp per bucket, lanes over chunks: the chunk counters of a bucket are scanned 32 at a time
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, nwarps = blockDim.x >> 5;
+    for (int b = warp; b <= E; b += nwarps) {
         int run = 0;
-        for (int c = 0; c < chunks; ++c) {
-            const int v = chunk_hist[size_t(c) * (E + 1) + b];
-            chunk_hist[size_t(c) * (E + 1) + b] = run;
-            run += v;
+        for (int c0 = 0; c0 < chunks; c0 += 32) {
+            const int c = c0 + lane;
+            const int v = c < chunks ? chunk_hist[size_t(c) * (E + 1) + b] : 0;
+            int incl = v;
+#pragma unroll
+            for (int o = 1; o < 32; o <<= 1) {
+                const int up = __shfl_up_sync(0xffffffffu, incl, o);
+                if (lane >= o) incl += up;
+            }
+            if (c < chunks) chunk_hist[size_t(c) * (E + 1) + b] = run + incl - v;
+            run += __shfl_sync(0xffffffffu, incl, 31);
         }
-        s_tot[b] = run;
-        s_tiles[b] = b < E ? (run + 127) / 128 : 0;
-        if (b < E && counts != nullptr) counts[b] = run;
+        if (lane == 0) {
+            s_tot[b] = run;
+            s_tiles[b] = b < E ? (run + 127) / 128 : 0;
+            if (b < E && counts != nullptr) counts[b] = run;
+        }
     }
     __syncthreads();
     block_exclusive_scan(s_tot, E + 1, s_warp_tot);
@@ -103,8 +114,8 @@ __global__ void __launch_bounds__(1024) sort_scan_kernel(int* __restrict__ chunk
     for (int b = threadIdx.x; b <= E; b += blockDim.x) {
         offsets[b] = s_tot[b];  // offsets[E] = number of kept rows
         if (mtile_prefix != nullptr) mtile_prefix[b] = s_tiles[b];
-        for (int c = 0; c < chunks; ++c) chunk_hist[size_t(c) * (E + 1) + b] += s_tot[b];
     }
+    for (int i = threadIdx.x; i < chunks * (E + 1); i += blockDim.x) chunk_hist[i] += s_tot[i % (E + 1)];
 }
 
 // ---------------------------------------------------------------- pass 3: scatter
