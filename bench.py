@@ -44,7 +44,7 @@ WORKLOADS = {
 }
 # dram__bytes_read.sum + dram__bytes_write.sum of one fc1 launch, from the ncu capture summarised in
 # profiles/c2_block_fp8_grouped_gemm.md (ncu cannot run inside a timed bench, so the figure is recorded here)
-NCU_FC1_DRAM_BYTES = {"c2": 974.494976e6 + 115.531008e6}
+NCU_FC1_DRAM_BYTES = {"c2": 974.503936e6 + 115.165696e6}
 MODE_NAME = {0: "bf16", 256: "fp8-tensor", 512: "fp8-channel", 1024: "fp8-block"}
 
 
@@ -59,17 +59,56 @@ def peaks():
 
 
 class ClockSampler:
-    """Samples SM clocks and throttle reasons with nvidia-smi while the timed region runs."""
+    """Samples SM clocks and clock-event reasons while the timed region runs.
+
+    Reads only (NVML queries every 2 ms from a thread; the nvidia-smi command line every 100 ms as a
+    fallback): nothing here changes a GPU setting. The timed regions last tens of milliseconds, far
+    shorter than nvidia-smi's start-up, which is why NVML is polled in-process."""
 
     FIELDS = ("clocks.sm,clocks.max.sm,clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
               "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+    NAMES = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
 
     def __init__(self, index: int):
         self.index = index
         self.proc = None
         self.lines = []
+        self.samples = []       # (sm MHz, reasons bit mask) from NVML
+        self.max_mhz = None
+        self._stop = threading.Event()
+        self._thread = None
+        self._nvml = None
+
+    def _physical_index(self):
+        vis = os.environ.get("CUDA_VISIBLE_DEVICES")
+        if vis:
+            ids = [v.strip() for v in vis.split(",") if v.strip()]
+            if self.index < len(ids) and ids[self.index].isdigit():
+                return int(ids[self.index])
+        return self.index
 
     def start(self):
+        try:
+            import pynvml
+            pynvml.nvmlInit()
+            h = pynvml.nvmlDeviceGetHandleByIndex(self._physical_index())
+            self.max_mhz = float(pynvml.nvmlDeviceGetMaxClockInfo(h, pynvml.NVML_CLOCK_SM))
+            self._nvml = pynvml
+
+            def poll():
+                while not self._stop.is_set():
+                    try:
+                        mhz = float(pynvml.nvmlDeviceGetClockInfo(h, pynvml.NVML_CLOCK_SM))
+                        mask = int(pynvml.nvmlDeviceGetCurrentClocksEventReasons(h))
+                        self.samples.append((mhz, mask))
+                    except pynvml.NVMLError:
+                        pass
+                    time.sleep(0.002)
+            self._thread = threading.Thread(target=poll, daemon=True)
+            self._thread.start()
+            return
+        except Exception:  # no NVML binding or no permission: fall back to the command line
+            self._nvml = None
         try:
             self.proc = subprocess.Popen(
                 ["nvidia-smi", "-i", str(self.index), f"--query-gpu={self.FIELDS}", "--format=csv,noheader,nounits",
@@ -83,6 +122,22 @@ class ClockSampler:
             self.lines.append(line.strip())
 
     def stop(self):
+        if self._nvml is not None:
+            self._stop.set()
+            self._thread.join(timeout=2)
+            nv = self._nvml
+            bits = {"hw_slowdown": nv.nvmlClocksEventReasonHwSlowdown,
+                    "hw_thermal_slowdown": nv.nvmlClocksEventReasonHwThermalSlowdown,
+                    "sw_thermal_slowdown": nv.nvmlClocksEventReasonSwThermalSlowdown,
+                    "sw_power_cap": nv.nvmlClocksEventReasonSwPowerCap}
+            mhz = [m for m, _ in self.samples]
+            reasons = sorted(n for n, b in bits.items() if any(mask & b for _, mask in self.samples))
+            try:
+                nv.nvmlShutdown()
+            except Exception:
+                pass
+            return {"sm_mhz": statistics.median(mhz) if mhz else None, "sm_min_mhz": min(mhz) if mhz else None,
+                    "sm_max_mhz": self.max_mhz, "samples": len(mhz), "source": "nvml, 2 ms", "reasons": reasons}
         if self.proc is None:
             return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
         time.sleep(0.15)
@@ -92,7 +147,6 @@ class ClockSampler:
         except subprocess.TimeoutExpired:
             self.proc.kill()
         mhz, mx, reasons = [], [], set()
-        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
         for ln in self.lines:
             parts = [x.strip() for x in ln.split(",")]
             if len(parts) < 6:
@@ -102,11 +156,11 @@ class ClockSampler:
                 mx.append(float(parts[1]))
             except ValueError:
                 continue
-            for nm, val in zip(names, parts[2:6]):
+            for nm, val in zip(self.NAMES, parts[2:6]):
                 if val.lower().startswith("active"):
                     reasons.add(nm)
         return {"sm_mhz": statistics.median(mhz) if mhz else None, "sm_max_mhz": max(mx) if mx else None,
-                "samples": len(mhz), "reasons": sorted(reasons)}
+                "samples": len(mhz), "source": "nvidia-smi, 100 ms", "reasons": sorted(reasons)}
 
 
 def synth_inputs(wl, seed, device, T=None):
