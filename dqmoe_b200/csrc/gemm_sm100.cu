@@ -86,7 +86,7 @@ struct SharedTail {
     uint64_t empty[kMaxStages];
     uint64_t tmem_full[2];
     uint64_t tmem_empty[2];
-    uint64_t epi_sync;
+    uint64_t epi_sync[4];    // per TMEM lane quarter: the two warps that share a row's 1x128 group
     uint64_t sc_full[kScaleSlots];
     uint64_t sc_empty[kScaleSlots];
     uint32_t tmem_base;
@@ -224,7 +224,7 @@ moe_GemmGrouped_GemmUniversal_tcgen05(const __grid_constant__ CUtensorMap tma_a,
             ptx::mbar_init(&st.tmem_full[b], 1);
             ptx::mbar_init(&st.tmem_empty[b], kPair ? 2 * kEpiWarps : kEpiWarps);  // both CTAs' epilogue warps
         }
-        ptx::mbar_init(&st.epi_sync, kEpiWarps);
+        for (int i = 0; i < 4; ++i) ptx::mbar_init(&st.epi_sync[i], 2);
         for (int i = 0; i < kScaleSlots; ++i) {
             ptx::mbar_init(&st.sc_full[i], 32);         // every lane of the scale-loader warp
             ptx::mbar_init(&st.sc_empty[i], kEpiWarps);
@@ -682,8 +682,8 @@ moe_GemmGrouped_GemmUniversal_tcgen05(const __grid_constant__ CUtensorMap tma_a,
                     // the 1x128 group spans both halves: exchange the partial amax through shared memory
                     st.amax[tile_it & 1u][h][r_in_tile] = amax_local;
                     __syncwarp();
-                    if (lane == 0) ptx::mbar_arrive(&st.epi_sync);
-                    if (!ptx::mbar_wait(&st.epi_sync, epi_phase, abort_flag, kWaitLimit)) {
+                    if (lane == 0) ptx::mbar_arrive(&st.epi_sync[q]);
+                    if (!ptx::mbar_wait(&st.epi_sync[q], epi_phase, abort_flag, kWaitLimit)) {
                         ok = false;
                         break;
                     }

@@ -91,3 +91,20 @@ def test_fp8_layers_track_the_bf16_layer():
     for mode in (orc.QUANT_TENSOR, orc.QUANT_CHANNEL, orc.QUANT_BLOCK):
         d = orc.moe_layer_fp8(*orc.quantize_inputs(a, b, b1, mode), m_indices, 4, mode)
         assert orc.cosine(d, ref) > 0.99, mode
+
+
+def test_block_with_shared_experts_is_routed_block_plus_dense_expert():
+    """moe_block(n_shared=1): the appended expert sees every token with weight 1, i.e. the result is the routed
+    block's fp32 sum plus that expert applied densely (one rounding to bf16 at the end)."""
+    E, T, H, I, k = 4, 12, 128, 128, 2
+    a, b, b1, _, _ = make_inputs(3, T, H, I, E + 1, k, 1.0, 0.05)
+    logits = torch.randn(T, E, generator=torch.Generator().manual_seed(1))
+    idx, w = orc.route_topk(logits, k, "softmax")
+    d_routed = orc.moe_layer_bf16(a, b[:E], b1[:E], idx, E)                       # [T, k, H]
+    everyone = torch.zeros(T, 1, dtype=torch.int32)
+    d_shared = orc.moe_layer_bf16(a, b[E:], b1[E:], everyone, 1)                  # [T, 1, H]
+    want = orc.finalize_weighted(torch.cat([d_routed, d_shared], dim=1),
+                                 torch.cat([w, torch.ones(T, 1)], dim=1))
+    got = orc.moe_block(a, logits, b, b1, k, "softmax", 0, n_shared=1)
+    assert torch.equal(got, want)
+    assert not torch.equal(got, orc.moe_block(a, logits, b[:E], b1[:E], k, "softmax", 0))
