@@ -137,3 +137,22 @@ def test_finalize_weighted(ops):
     # fp32 accumulation in the same slot order: results agree to one bf16 rounding
     torch.testing.assert_close(out.cpu().float(), ref.float(), rtol=1e-2, atol=1e-3)
     assert (out.cpu() != ref).float().mean().item() < 0.01
+
+
+@pytest.mark.parametrize("rows,cols", [(1, 8), (37, 24), (300, 768), (64, 2880), (1025, 1000)])
+def test_requant_from_amax_bit_exact(ops, rows, cols):
+    """The second pass of the tensor / channel modes (dqmoe_requant_from_amax): with the amax that stage 1
+    collects, its bytes and scales equal the oracle's row-wise and per-tensor quantisers."""
+    x = (torch.randn(rows, cols, generator=torch.Generator().manual_seed(rows + cols)) * 3).to(torch.bfloat16)
+    x[0, 0] = 0.0
+    if rows > 2:
+        x[2] = 0.0  # an all-zero row: scale 1e-4 / 448
+    xd = x.to(DEV)
+    q, s = ops.requant_from_amax(xd, xd.abs().float().amax(dim=1).contiguous(), per_row=True)
+    rq, rs = orc.quant_rowwise(x)
+    assert np.array_equal(bits(q), bits(rq))
+    assert torch.equal(s.cpu(), rs.reshape(-1))
+    q, s = ops.requant_from_amax(xd, xd.abs().float().amax().reshape(1), per_row=False)
+    rq, rs = orc.quant_tensor(x)
+    assert np.array_equal(bits(q), bits(rq))
+    assert torch.equal(s.cpu(), rs.reshape(-1))
