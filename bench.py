@@ -336,13 +336,61 @@ def run_decode(args, rank):
     if ops.device_status() != 0:
         raise SystemExit("device status non-zero: a kernel's bounded wait gave up; no number reported")
     head = next(r for r in rows if r["quant"] == "fp8-tensor" and r["T"] == 64)
+
+    # the headline point end to end: quantised activations, scale and expert ids come from pinned host memory,
+    # the [T, k, H] result goes back to pinned host memory, every call
+    T = 64
+    g = torch.Generator(device=dev).manual_seed(T)
+    x = torch.randn(T, H, generator=g, device=dev).to(torch.bfloat16)
+    idx, _ = ops.route_topk(torch.randn(T, E, generator=g, device=dev), k, "softmax")
+    aq, as_ = ops.per_tensor_cast_to_fp8(x)
+    h_aq, h_as, h_idx = aq.cpu().pin_memory(), as_.cpu().pin_memory(), idx.cpu().pin_memory()
+    d_aq, d_as, d_idx = torch.empty_like(aq), torch.empty_like(as_), torch.empty_like(idx)
+    d = torch.empty(T, k, H, dtype=torch.bfloat16, device=dev)
+    h_d = torch.empty(T, k, H, dtype=torch.bfloat16).pin_memory()
+    ws = torch.empty(ops.moe_workspace_bytes(T, H, I, E, k, 256), dtype=torch.uint8, device=dev)
+    etimes = []
+    for i in range(args.steps + 3):
+        flush.zero_()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        d_aq.copy_(h_aq, non_blocking=True)
+        d_as.copy_(h_as, non_blocking=True)
+        d_idx.copy_(h_idx, non_blocking=True)
+        ops.moe_forward(d_aq, d_as, bq, bs, b1q, b1s, d, d_idx, ws, 256)
+        h_d.copy_(d, non_blocking=True)
+        e1.record()
+        torch.cuda.synchronize()
+        if i >= 3:
+            etimes.append(e0.elapsed_time(e1))
+    e2e = {"value": statistics.median(etimes) * 1e3, "unit": "us",
+           "h2d_bytes_per_step": h_aq.numel() + 4 * h_as.numel() + 4 * h_idx.numel(),
+           "d2h_bytes_per_step": h_d.numel() * 2}
+
+    base = None
+    if not args.no_cpu_baseline:
+        # the oracle on the host cores for the smallest point of the sweep: one token, its two experts, bf16
+        from oracle import moe_oracle as orc
+        gc = torch.Generator().manual_seed(0)
+        xb = torch.randn(1, H, generator=gc).to(torch.bfloat16)
+        bb = (torch.randn(2, 2 * I, H, generator=gc) * 0.02).to(torch.bfloat16)
+        bb1 = (torch.randn(2, H, I, generator=gc) * 0.02).to(torch.bfloat16)
+        ids = torch.tensor([[0, 1]], dtype=torch.int32)
+        ct = []
+        for _ in range(3):
+            t0 = time.perf_counter()
+            orc.moe_layer_bf16(xb, bb, bb1, ids, 2)
+            ct.append(time.perf_counter() - t0)
+        base = {"value": statistics.median(ct) * 1e6, "unit": "us", "cores": torch.get_num_threads(), "kind": "port",
+                "sample": "bf16 layer, T=1, its 2 active experts (the sweep's smallest point), median of 3 calls"}
     print(json.dumps({
         "metric": "moe_layer_decode_p50_latency_us", "value": head["p50_us"], "unit": "us", "n_gpus": 1,
         "steps": args.steps, "warmup": max(args.warmup, 3), "ms_per_step": head["p50_us"] / 1e3,
         "higher_is_better": False, "scaling": "weak", "vs_baseline": None, "dtype": "e4m3 x e4m3 -> f32", "data": "synthetic",
         "config": {"workload": "c5: decode-shape sweep, Mixtral shape, T in {1,16,64,256}; headline = fp8-tensor T=64",
                    "H": H, "I": I, "E": E, "k": k, "l2": "256 MB flush write before every timed call"},
-        "clocks": clocks, "sweep": rows,
+        "clocks": clocks, "sweep": rows, "e2e": e2e, "cpu_baseline": base,
+        "gpu_launches": launches_per_step(64 * k, 256) * args.steps,
         "roofline": {"bound": "hbm", "achieved": head["gbs"], "peak": pk["hbm_gbs"], "unit": "GB/s",
                      "frac": head["gbs"] / pk["hbm_gbs"], "traffic": None,
                      "peak_note": f"of {pk['source']} copy bandwidth; nominal 8000 GB/s"}}))
