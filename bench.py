@@ -449,10 +449,10 @@ def main():
             ops.moe_forward(aq, as_, bq, bs, b1q, b1s, d, idx, ws, mode)
     else:
         layer = ep.ExpertParallelMoE(wl, dev, seed=0, ops=ops)
-        # per rank and step: sort (1 or 3) + publish, plan, dispatch, wait, row_ptrs, fc1, fc2, signal, wait (peer exchange)
+        # per rank and step: sort (1 or 3) + publish, plan, dispatch, wait, row_ptrs, fc1, [requant], fc2, signal, wait (peer exchange)
         sort_l = 1 if n <= 2048 else 3
         # collective exchange: sort, gather, segment ids, then the layer on the received rows, then scatter
-        ep_launches = (sort_l + 9) * world if layer.impl == "peer" else \
+        ep_launches = (sort_l + 9 + (1 if mode == 512 else 0)) * world if layer.impl == "peer" else \
             (sort_l + 2 + (3 + 3 + (1 if mode in (256, 512) else 0)) + 1) * world
         aq, as_ = layer.quantize_activations(x)
 
@@ -593,7 +593,7 @@ def main():
                                  f"of {pk['source']}; nominal dense {'FP8 4500' if mode else 'BF16 2250'} TFLOP/s",
                     "ms_per_launch": fc1_ms, "traffic": None}
         roofline["traffic"] = NCU_FC1_DRAM_BYTES.get(args.workload)
-    elif mode in (0, 1024):
+    elif mode in (0, 1024) and layer.impl == "peer":
         # Expert parallel: the same kernel timed alone on rank 0's expert shard, with this rank's rows repeated k
         # times and split evenly over its experts (the received rows of a step have this size on average).
         e_loc = layer.wq[0].shape[0]

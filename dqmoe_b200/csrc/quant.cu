@@ -71,7 +71,9 @@ __global__ void __launch_bounds__(kThreads) rowwise_kernel(const uint8_t* __rest
 // (grid-stride), four 16-byte vectors per lane in flight, the scale arithmetic once per row.
 __global__ void __launch_bounds__(kThreads) requant_rows_kernel(const uint8_t* __restrict__ x, int64_t rows, int cols,
                                                                 uint8_t* __restrict__ q, float* __restrict__ scale,
-                                                                const float* __restrict__ amax_in, int amax_per_row) {
+                                                                const float* __restrict__ amax_in, int amax_per_row,
+                                                                const int* __restrict__ rows_dev) {
+    if (rows_dev != nullptr) rows = rows < *rows_dev ? rows : *rows_dev;  // row count known only on the device
     const int lane = threadIdx.x & 31;
     const int64_t warp = (int64_t(blockIdx.x) * kThreads + threadIdx.x) >> 5;
     const int64_t nwarps = int64_t(gridDim.x) * (kThreads / 32);
@@ -221,17 +223,23 @@ int dqmoe_quant_fp8_rowwise(const void* x_bf16, int64_t rows, int cols, void* q,
     return DQMOE_OK;
 }
 
-int dqmoe_requant_from_amax(const void* act_bf16, int64_t n, int I, const float* amax, int per_row, void* q,
-                            float* scale, dqmoe_stream_t stream) {
-    DQ_CHECK(n >= 0 && I > 0);
-    if (n == 0) return DQMOE_OK;
+int dqmoe_requant_from_amax_dev(const void* act_bf16, int64_t n_max, int I, const float* amax, int per_row, void* q,
+                                float* scale, const int32_t* n_rows_device, dqmoe_stream_t stream) {
+    DQ_CHECK(n_max >= 0 && I > 0);
+    if (n_max == 0) return DQMOE_OK;
     DQ_CHECK(act_bf16 != nullptr && q != nullptr && scale != nullptr && amax != nullptr);
     DQ_CHECK_FMT(I % 8 == 0, "I=%d must be a multiple of 8", I);
     DQ_CHECK(is_aligned(act_bf16, 16) && is_aligned(q, 8));
-    quant::requant_rows_kernel<<<quant::grid_cap((n + 7) / 8, 8), quant::kThreads, 0, static_cast<cudaStream_t>(stream)>>>(
-        static_cast<const uint8_t*>(act_bf16), n, I, static_cast<uint8_t*>(q), scale, amax, per_row ? 1 : 0);
+    quant::requant_rows_kernel<<<quant::grid_cap((n_max + 7) / 8, 8), quant::kThreads, 0, static_cast<cudaStream_t>(stream)>>>(
+        static_cast<const uint8_t*>(act_bf16), n_max, I, static_cast<uint8_t*>(q), scale, amax, per_row ? 1 : 0,
+        n_rows_device);
     DQ_LAUNCH_CHECK();
     return DQMOE_OK;
+}
+
+int dqmoe_requant_from_amax(const void* act_bf16, int64_t n, int I, const float* amax, int per_row, void* q,
+                            float* scale, dqmoe_stream_t stream) {
+    return dqmoe_requant_from_amax_dev(act_bf16, n, I, amax, per_row, q, scale, nullptr, stream);
 }
 
 int dqmoe_quant_fp8_block_128x128(const void* w_bf16, int e, int rows, int cols, void* q, float* scale,

@@ -179,9 +179,9 @@ class ExpertParallelMoE:
             raise RuntimeError("[ASSERT FAILED] ep.py  Condition: mode in (0, 512, 1024)")
         del b, b1
         self.wq = wq  # (fc1 weights, scales, fc2 weights, scales) of this rank's experts
-        # exchange over peer memory where it is built (bf16, block FP8); DQMOE_EP_IMPL=nccl selects the collectives
+        # exchange over peer memory; DQMOE_EP_IMPL=nccl selects the collectives
         import os
-        use_peer = mode in (0, 1024) and os.environ.get("DQMOE_EP_IMPL", "peer") == "peer" and world <= 8
+        use_peer = os.environ.get("DQMOE_EP_IMPL", "peer") == "peer" and world <= 8
         if use_peer:
             self.layer = PeerExpertParallelLayer(wl["T"], H, I, E, wl["k"], mode, wq, ops, group)
         else:
@@ -210,9 +210,9 @@ class PeerExpertParallelLayer:
     sort -> publish counts -> plan -> dispatch (rows written straight into the owners' receive
     buffers, already grouped by expert) -> wait -> grouped fc1 -> grouped fc2 whose epilogue stores
     every result row directly into its home rank's d (NVLink stores) -> signal -> wait.
-    Block FP8 and bf16 modes (the per-row re-quantisation pass of channel mode needs the received
-    row count on the host; use ExpertParallelLayer for it). The returned tensor aliases the
-    symmetric output buffer and is overwritten by the next call.
+    bf16, block FP8 and channel FP8 modes (channel mode adds the per-row re-quantisation pass between
+    the GEMMs, bounded by the received row count read on the device). The returned tensor aliases
+    the symmetric output buffer and is overwritten by the next call.
     """
 
     def __init__(self, T: int, H: int, I: int, E: int, k: int, mode: int, weights_q, ops, group=None,
@@ -222,8 +222,8 @@ class PeerExpertParallelLayer:
         os.environ.setdefault("TORCH_SYMM_MEM_DISABLE_MULTICAST", "1")  # plain peer loads/stores only
         import torch.distributed._symmetric_memory as symm_mem
         from . import _lib
-        if mode not in (0, 1024):
-            raise RuntimeError("[ASSERT FAILED] ep.py  Condition: mode in (0, 1024)  Info: peer exchange supports bf16 and block FP8")
+        if mode not in (0, 512, 1024):
+            raise RuntimeError("[ASSERT FAILED] ep.py  Condition: mode in (0, 512, 1024)  Info: peer exchange supports bf16, channel and block FP8")
         self.ops, self.lib, self.check, self.ct = ops, _lib.load(), _lib.check, ctypes
         self.group = group if group is not None else dist.group.WORLD
         self.W, self.me = dist.get_world_size(self.group), dist.get_rank(self.group)
@@ -236,7 +236,7 @@ class PeerExpertParallelLayer:
         self.esz = 1 if mode else 2
         self.n = T * k
         self.cap = capacity_rows if capacity_rows is not None else self.W * self.n  # worst case: every row comes here
-        self.scale_cols = (H + 127) // 128 if mode == 1024 else 0
+        self.scale_cols = (H + 127) // 128 if mode == 1024 else (1 if mode == 512 else 0)
         dev = torch.device("cuda", torch.cuda.current_device())
         self.dev = dev
 
@@ -264,6 +264,9 @@ class PeerExpertParallelLayer:
         self.row_dst = torch.zeros(self.cap, dtype=torch.int64, device=dev)
         self.act = torch.empty(self.cap * I * self.esz, dtype=torch.uint8, device=dev)
         self.act_scale = torch.empty(self.cap * ((I + 127) // 128), dtype=torch.float32, device=dev)
+        if mode == 512:  # stage 1 writes bf16 and collects the row amax; a second pass quantises
+            self.act_bf16 = torch.empty(self.cap * I, dtype=torch.bfloat16, device=dev)
+            self.amax = torch.zeros(self.cap, dtype=torch.float32, device=dev)
         self.d_out = self.sym[self.off["d_out"]:self.off["d_out"] + self.n * H * 2].view(torch.bfloat16).view(T, k, H)
         self.epoch = 0
         torch.cuda.synchronize()
@@ -298,10 +301,21 @@ class PeerExpertParallelLayer:
         b, bs, b1, b1s = self.weights_q
         sp = lambda t: None if t is None else vp(t.data_ptr())
         rx_scale = vp(self.local["rx_scale"]) if self.scale_cols else None
-        self.check(lib.dqmoe_grouped_gemm(vp(self.local["rx_rows"]), rx_scale, vp(b.data_ptr()), sp(bs),
-                                          vp(self.rx_offsets.data_ptr()), vp(self.rx_mtiles.data_ptr()), self.cap, I, H,
-                                          El, self.mode, 1, vp(self.act.data_ptr()), vp(self.act_scale.data_ptr()), None,
-                                          None, stream))
+        if self.mode == 512:
+            self.amax.zero_()
+            self.check(lib.dqmoe_grouped_gemm(vp(self.local["rx_rows"]), rx_scale, vp(b.data_ptr()), sp(bs),
+                                              vp(self.rx_offsets.data_ptr()), vp(self.rx_mtiles.data_ptr()), self.cap, I,
+                                              H, El, self.mode, 1, vp(self.act_bf16.data_ptr()), None,
+                                              vp(self.amax.data_ptr()), None, stream))
+            n_rx = vp(self.rx_offsets.data_ptr() + 4 * El)  # rows received, on the device
+            self.check(lib.dqmoe_requant_from_amax_dev(vp(self.act_bf16.data_ptr()), self.cap, I, vp(self.amax.data_ptr()),
+                                                       1, vp(self.act.data_ptr()), vp(self.act_scale.data_ptr()), n_rx,
+                                                       stream))
+        else:
+            self.check(lib.dqmoe_grouped_gemm(vp(self.local["rx_rows"]), rx_scale, vp(b.data_ptr()), sp(bs),
+                                              vp(self.rx_offsets.data_ptr()), vp(self.rx_mtiles.data_ptr()), self.cap, I,
+                                              H, El, self.mode, 1, vp(self.act.data_ptr()), vp(self.act_scale.data_ptr()),
+                                              None, None, stream))
         self.check(lib.dqmoe_grouped_gemm_rows(vp(self.act.data_ptr()), vp(self.act_scale.data_ptr()) if self.mode else None,
                                                vp(b1.data_ptr()), sp(b1s), vp(self.rx_offsets.data_ptr()),
                                                vp(self.rx_mtiles.data_ptr()), self.cap, H, I, El, self.mode,

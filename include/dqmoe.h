@@ -338,6 +338,11 @@ int dqmoe_mtile_prefix(const int32_t* offsets, int E, int32_t* mtile_prefix, dqm
  */
 int dqmoe_requant_from_amax(const void* act_bf16, int64_t n, int I, const float* amax,
                             int per_row, void* q, float* scale, dqmoe_stream_t stream);
+/* The same over at most n_max rows when the row count exists only on the device
+ * (*n_rows_device, e.g. the rows an expert-parallel rank received); NULL means n_max rows. */
+int dqmoe_requant_from_amax_dev(const void* act_bf16, int64_t n_max, int I, const float* amax,
+                                int per_row, void* q, float* scale, const int32_t* n_rows_device,
+                                dqmoe_stream_t stream);
 
 /* ------------------------------------------------------------------ expert parallel over peer memory */
 

@@ -68,7 +68,7 @@ def _worker(rank, world, init_file, mode, impl, results):
 
 
 @pytest.mark.parametrize("world", [1, 2])
-@pytest.mark.parametrize("mode,impl", [(0, "nccl"), (512, "nccl"), (1024, "nccl"), (0, "peer"), (1024, "peer")])
+@pytest.mark.parametrize("mode,impl", [(0, "nccl"), (512, "nccl"), (1024, "nccl"), (0, "peer"), (512, "peer"), (1024, "peer")])
 def test_expert_parallel_matches_single_gpu(mode, impl, world):
     """world = 1 runs the whole exchange (count matrix, plan, dispatch, row-address epilogue, flags) on one
     GPU, so the kernels of csrc/ep.cu are exercised where only one device is available."""
