@@ -181,7 +181,7 @@ int dqmoe_moe_forward(const void* a, const float* a_scale, const void* b, const 
 // activation quantisation -> grouped fc1/fc2 -> weighted combine over the k slots.
 // Workspace = [indices T*k | weights T*k | d T*k*H bf16 | layer workspace].
 struct BlockLayout {
-    size_t indices, weights, d, layer, total;
+    size_t indices, weights, d, xq, xs, xamax, layer, total;
 };
 static BlockLayout block_layout(int T, int H, int I, int E, int k, int quant_mode) {
     BlockLayout B{};
@@ -194,6 +194,11 @@ static BlockLayout block_layout(int T, int H, int I, int E, int k, int quant_mod
     B.indices = add(size_t(T) * k * sizeof(int));
     B.weights = add(size_t(T) * k * sizeof(float));
     B.d = add(size_t(T) * k * H * 2);
+    // tensor / channel modes quantise x [T, H] before the gather (block mode quantises while gathering)
+    const bool pre_quant = quant_mode == DQMOE_QUANT_FP8_TENSOR || quant_mode == DQMOE_QUANT_FP8_CHANNEL;
+    B.xq = add(pre_quant ? size_t(T) * H : 0);
+    B.xs = add(pre_quant ? size_t(T) * sizeof(float) : 0);
+    B.xamax = add(pre_quant ? sizeof(float) : 0);
     B.layer = add(layer::make_layout(T, H, I, E, k, quant_mode).total);
     B.total = off;
     return B;
@@ -201,7 +206,9 @@ static BlockLayout block_layout(int T, int H, int I, int E, int k, int quant_mod
 
 size_t dqmoe_moe_block_workspace_bytes(int T, int H, int I, int E, int k, int quant_mode) {
     if (T < 0 || H <= 0 || I <= 0 || E <= 0 || k <= 0) return 0;
-    if (quant_mode != DQMOE_QUANT_NONE && quant_mode != DQMOE_QUANT_FP8_BLOCK) return 0;
+    if (quant_mode != DQMOE_QUANT_NONE && quant_mode != DQMOE_QUANT_FP8_BLOCK &&
+        quant_mode != DQMOE_QUANT_FP8_TENSOR && quant_mode != DQMOE_QUANT_FP8_CHANNEL)
+        return 0;
     return block_layout(T, H, I, E, k, quant_mode).total;
 }
 
@@ -215,8 +222,9 @@ static int moe_block_impl(const void* x_bf16, const float* logits, const void* b
     DQ_CHECK(T >= 0 && H > 0 && I > 0 && E_routed > 0 && k_routed > 0 && n_shared >= 0);
     const int E = E_routed + n_shared;
     const int k = k_routed + n_shared;
-    DQ_CHECK_FMT(quant_mode == DQMOE_QUANT_NONE || quant_mode == DQMOE_QUANT_FP8_BLOCK,
-                 "quant_mode=%d: the fused block supports bf16 (0) and block FP8 (1024)", quant_mode);
+    DQ_CHECK_FMT(quant_mode == DQMOE_QUANT_NONE || quant_mode == DQMOE_QUANT_FP8_BLOCK ||
+                     quant_mode == DQMOE_QUANT_FP8_TENSOR || quant_mode == DQMOE_QUANT_FP8_CHANNEL,
+                 "quant_mode=%d: unknown quantisation mode", quant_mode);
     if (T == 0) return DQMOE_OK;
     DQ_CHECK(x_bf16 != nullptr && logits != nullptr && b != nullptr && b1 != nullptr && out_bf16 != nullptr);
     DQ_CHECK_FMT(workspace != nullptr && is_aligned(workspace, layer::kAlign), "workspace pointer %p is not aligned!",
@@ -247,6 +255,19 @@ static int moe_block_impl(const void* x_bf16, const float* logits, const void* b
 
     int rc = route::route_topk(logits, T, E_routed, k_routed, n_shared, scoring, indices, weights, stream);
     if (rc != DQMOE_OK) return rc;
+    if (quant_mode == DQMOE_QUANT_FP8_TENSOR || quant_mode == DQMOE_QUANT_FP8_CHANNEL) {
+        // dynamic quantisation of the activations (per tensor or per token), then the layer as the drop-in call runs it
+        void* xq = ws + B.xq;
+        float* xs = reinterpret_cast<float*>(ws + B.xs);
+        rc = quant_mode == DQMOE_QUANT_FP8_CHANNEL
+                 ? dqmoe_quant_fp8_rowwise(x_bf16, T, H, xq, xs, stream)
+                 : dqmoe_quant_fp8_tensor(x_bf16, 1, int64_t(T) * H, xq, xs, reinterpret_cast<float*>(ws + B.xamax), stream);
+        if (rc != DQMOE_OK) return rc;
+        rc = dqmoe_moe_forward(xq, xs, b, b_scale, b1, b1_scale, d, indices, lws, L.total, T, H, I, E, k, quant_mode, 1,
+                               stream);
+        if (rc != DQMOE_OK) return rc;
+        return dqmoe_finalize_weighted(d, weights, out_bf16, T, k, H, stream);
+    }
     rc = route::route_sort(indices, n, E, counts, offsets, mtile_prefix, dest_to_src, nullptr, lws + L.sort_ws,
                            L.sort_ws_bytes, stream);
     if (rc != DQMOE_OK) return rc;

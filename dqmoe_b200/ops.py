@@ -75,6 +75,7 @@ def moe_block(x: torch.Tensor, logits: torch.Tensor, b, b_scale, b1, b1_scale, k
               quant_mode: int = QUANT_FP8_BLOCK, workspace: Optional[torch.Tensor] = None,
               n_shared: int = 0) -> torch.Tensor:
     """Router -> layer -> weighted combine from bf16 activations x [T, H]; see dqmoe_moe_block.
+    quant_mode 0 (bf16 weights) or 256 / 512 / 1024 (e4m3 weights with that mode's scales).
 
     With n_shared > 0 the last n_shared experts of b / b1 are shared experts that every token
     passes through with weight 1 (dqmoe_moe_block_shared); logits are [T, E - n_shared]."""

@@ -114,7 +114,9 @@ void* dqmoe_moe_workspace_ptr(void* workspace, int which, int T, int H, int I, i
  * out [T, H] bf16: top-k router, expert sort, gather fused with the dynamic 1x128 FP8
  * quantisation of the activations (block mode) or plain gather (bf16 mode), grouped fc1 +
  * SwiGLU (+ re-quantisation), grouped fc2, weighted combine of the k slots. quant_mode is
- * DQMOE_QUANT_NONE (bf16 weights) or DQMOE_QUANT_FP8_BLOCK (e4m3 weights with 128x128
+ * DQMOE_QUANT_NONE (bf16 weights), DQMOE_QUANT_FP8_BLOCK (e4m3 weights with 128x128
+ * scales), or DQMOE_QUANT_FP8_TENSOR / _CHANNEL (x is quantised per tensor / per token
+ * into the workspace first, then the layer runs as dqmoe_moe_forward does; weight
  * scales). The natural caller of the reference's layer (its tests do routing and input
  * quantisation in torch, test/torch_test.py:60-80, test/util.py:162-184); no single
  * counterpart in the reference.

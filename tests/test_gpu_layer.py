@@ -268,9 +268,10 @@ def test_grouped_gemm_row_addresses_equal_scatter_map(ops, mode, counts, N, K):
     assert torch.equal(got, want)
 
 
-@pytest.mark.parametrize("mode,scoring", [(0, "softmax"), (1024, "softmax"), (1024, "sigmoid")])
+@pytest.mark.parametrize("mode,scoring", [(0, "softmax"), (1024, "softmax"), (1024, "sigmoid"), (512, "softmax"),
+                                          (256, "sigmoid")])
 def test_moe_block_router_to_weighted_output(ops, mode, scoring):
-    """dqmoe_moe_block (router, fused gather+quantise, layer, weighted combine) against the oracle's moe_block."""
+    """dqmoe_moe_block (router, activation quantisation, layer, weighted combine) against the oracle's moe_block."""
     E, T, H, I, k = 16, 200, 512, 256, 4
     a, b, b1, _, _ = make_inputs(31, T, H, I, E, k, 1.0, 0.05)
     logits = torch.randn(T, E, generator=torch.Generator().manual_seed(5))
@@ -278,10 +279,12 @@ def test_moe_block_router_to_weighted_output(ops, mode, scoring):
         ref = orc.moe_block(a, logits, b, b1, k, scoring, 0)
         out = ops.moe_block(a.to(DEV), logits.to(DEV), b.to(DEV), None, b1.to(DEV), None, k, scoring, 0)
     else:
-        qs = orc.quantize_inputs(a, b, b1, 1024)
-        ref = orc.moe_block(a, logits, b, b1, k, scoring, 1024, quantized=qs)
-        out = ops.moe_block(a.to(DEV), logits.to(DEV), qs[2].to(DEV), qs[3].to(DEV).contiguous(), qs[4].to(DEV),
-                            qs[5].to(DEV).contiguous(), k, scoring, 1024)
+        qs = orc.quantize_inputs(a, b, b1, mode)
+        ref = orc.moe_block(a, logits, b, b1, k, scoring, mode, quantized=qs)
+        out = ops.moe_block(a.to(DEV), logits.to(DEV), qs[2].to(DEV), qs[3].to(DEV).contiguous().view(E, -1)
+                            if mode == 512 else qs[3].to(DEV).contiguous(), qs[4].to(DEV),
+                            qs[5].to(DEV).contiguous().view(E, -1) if mode == 512 else qs[5].to(DEV).contiguous(),
+                            k, scoring, mode)
     assert ops.device_status() == 0
     assert_close(out, ref)
 
