@@ -27,6 +27,7 @@ SIGNATURES = {
     "dqmoe_moe_workspace_bytes": (_c_size, [_c_int] * 6),
     "dqmoe_moe_forward": (_c_int, [_ptr] * 9 + [_c_size] + [_c_int] * 7 + [_ptr]),
     "dqmoe_moe_workspace_ptr": (_ptr, [_ptr] + [_c_int] * 7),
+    "dqmoe_moe_forward_f16": (_c_int, [_ptr] * 6 + [_c_size] + [_c_int] * 5 + [_ptr]),
     "dqmoe_moe_block_workspace_bytes": (_c_size, [_c_int] * 6),
     "dqmoe_moe_block": (_c_int, [_ptr] * 8 + [_c_size] + [_c_int] * 7 + [_ptr]),
     "dqmoe_moe_block_shared": (_c_int, [_ptr] * 8 + [_c_size] + [_c_int] * 8 + [_ptr]),

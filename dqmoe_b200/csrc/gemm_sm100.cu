@@ -13,6 +13,8 @@
 // per-expert "configure" kernels (csrc/moe_gemm_template.h:72-1039) together
 // with doGatedActivationKernel, scale_1x128_kernel and finalizeScatterKernel
 // (csrc/moe_kernels.h:301-444, 581-620).
+#include <cuda_fp16.h>
+
 #include <cstdlib>
 
 #include "common.cuh"
@@ -182,6 +184,25 @@ __device__ __forceinline__ void store_rows_staged(uint4* stage, const uint32_t (
     }
 }
 
+// Rounding / packing to the 16-bit output type of the unquantised path: bf16, or IEEE half (kF16) for the
+// FP16 instantiation of the reference's template (csrc/pybind11_register.h:104-151 with T = half).
+template <bool kF16>
+__device__ __forceinline__ float round16(float x) {
+    if constexpr (kF16)
+        return __half2float(__float2half_rn(x));
+    else
+        return bf_round_cvt(x);
+}
+template <bool kF16>
+__device__ __forceinline__ uint32_t pack16x2(float lo, float hi) {
+    if constexpr (kF16) {
+        const __half2 h = __floats2half2_rn(lo, hi);
+        return *reinterpret_cast<const uint32_t*>(&h);
+    } else {
+        return pack_bf16x2(lo, hi);
+    }
+}
+
 // two fp32 FMAs in one instruction (packed fp32 of sm_100): a += x * s
 __device__ __forceinline__ void ffma2(float& a0, float& a1, uint32_t x0, uint32_t x1, float s0, float s1) {
     const float2 r = __ffma2_rn(make_float2(__uint_as_float(x0), __uint_as_float(x1)), make_float2(s0, s1),
@@ -192,7 +213,7 @@ __device__ __forceinline__ void ffma2(float& a0, float& a1, uint32_t x0, uint32_
 
 // kBox = weight rows per TMA box (two boxes per stage, 2*kBox accumulator columns): 128 for
 // throughput, 64 when a launch would otherwise have fewer tiles than SMs (decode shapes).
-template <bool kFp8, int kMode, bool kGated, bool kPair, int kBox>
+template <bool kFp8, int kMode, bool kGated, bool kPair, int kBox, bool kF16 = false>
 __global__ void __launch_bounds__(kThreads, 1)
 moe_GemmGrouped_GemmUniversal_tcgen05(const __grid_constant__ CUtensorMap tma_a,
                                       const __grid_constant__ CUtensorMap tma_b, const Params p) {
@@ -204,6 +225,7 @@ moe_GemmGrouped_GemmUniversal_tcgen05(const __grid_constant__ CUtensorMap tma_a,
     const int lane = threadIdx.x & 31;
     constexpr int kBKElems = kFp8 ? kBKBytes : kBKBytes / 2;
     static_assert(kBox == 128 || (kBox == 64 && !kPair && kMode != kBlock), "narrow tiles: single CTA, non-block modes");
+    static_assert(!kF16 || (!kFp8 && kMode == kNone), "fp16 operands: the unquantised path only");
     constexpr int kN = 2 * kBox;                      // accumulator columns of a tile
     constexpr int kStageSz = kPair ? kStageBytesPair : kABytes + kN * kBKBytes;
     constexpr int kNumStages = (kStages * kStageBytes) / kStageSz;   // 4 (wide), 6 (pairs, narrow)
@@ -318,7 +340,8 @@ moe_GemmGrouped_GemmUniversal_tcgen05(const __grid_constant__ CUtensorMap tma_a,
       } else if (warp == 1) {
         // ------------------------------------------------------------ MMA issuer
         if (lane == 0 && leader) {
-            constexpr uint32_t idesc = ptx::make_idesc(kFp8 ? 0u : 1u, kPair ? 2 * kBM : kBM, kN);
+            // operand format code: e4m3 = 0 (kind::f8f6f4); f16 = 0, bf16 = 1 (kind::f16)
+            constexpr uint32_t idesc = ptx::make_idesc(kFp8 || kF16 ? 0u : 1u, kPair ? 2 * kBM : kBM, kN);
             // issue one K step; in a pair the same call drives both CTAs' tensor cores
             auto mma_step = [&](uint32_t d_tmem, uint32_t a_addr, uint32_t b_addr, uint32_t accumulate) {
                 if constexpr (kPair)
@@ -508,14 +531,19 @@ moe_GemmGrouped_GemmUniversal_tcgen05(const __grid_constant__ CUtensorMap tma_a,
                             float a4[4];
 #pragma unroll
                             for (int u = 0; u < 4; ++u) {
-                                const float gate = bf_round_cvt(__uint_as_float(g[i + u]) * sg[u]);
-                                const float val = bf_round_cvt(__uint_as_float(v[i + u]) * sv[u]);
-                                const float act = bf_round_cvt(silu_bf16(gate) * val);
+                                const float gate = round16<kF16>(__uint_as_float(g[i + u]) * sg[u]);
+                                const float val = round16<kF16>(__uint_as_float(v[i + u]) * sv[u]);
+                                const float act = round16<kF16>(round16<kF16>(__fdividef(gate, 1.0f + __expf(-gate))) * val);
                                 a4[u] = act;
                                 if (col0 + i + u < I_or_H) amax_local = fmaxf(amax_local, fabsf(act));
                             }
-                            packed[i >> 1] = pack_bf16x2_exact(a4[0], a4[1]);  // act is already rounded to bf16
-                            packed[(i >> 1) + 1] = pack_bf16x2_exact(a4[2], a4[3]);
+                            if constexpr (kF16) {
+                                packed[i >> 1] = pack16x2<true>(a4[0], a4[1]);
+                                packed[(i >> 1) + 1] = pack16x2<true>(a4[2], a4[3]);
+                            } else {
+                                packed[i >> 1] = pack_bf16x2_exact(a4[0], a4[1]);  // act is already rounded to bf16
+                                packed[(i >> 1) + 1] = pack_bf16x2_exact(a4[2], a4[3]);
+                            }
                         }
                         store_rows_staged(st.stage[warp - 4], packed,
                                           row_ok ? reinterpret_cast<uint8_t*>(reinterpret_cast<__nv_bfloat16*>(p.out) +
@@ -565,9 +593,9 @@ moe_GemmGrouped_GemmUniversal_tcgen05(const __grid_constant__ CUtensorMap tma_a,
                                 const float4 a = cs4[i >> 2];
                                 sc[0] *= a.x, sc[1] *= a.y, sc[2] *= a.z, sc[3] *= a.w;
                             }
-                            packed[i >> 1] = pack_bf16x2(__uint_as_float(r[i]) * sc[0], __uint_as_float(r[i + 1]) * sc[1]);
+                            packed[i >> 1] = pack16x2<kF16>(__uint_as_float(r[i]) * sc[0], __uint_as_float(r[i + 1]) * sc[1]);
                             packed[(i >> 1) + 1] =
-                                pack_bf16x2(__uint_as_float(r[i + 2]) * sc[2], __uint_as_float(r[i + 3]) * sc[3]);
+                                pack16x2<kF16>(__uint_as_float(r[i + 2]) * sc[2], __uint_as_float(r[i + 3]) * sc[3]);
                         }
                         store_rows_staged(st.stage[warp - 4], packed,
                                           row_ok && orow_idx >= 0 ? reinterpret_cast<uint8_t*>(orow + col0) : nullptr,
@@ -789,9 +817,9 @@ static int make_map(CUtensorMap* map, const void* base, bool fp8, uint64_t rows,
     return DQMOE_OK;
 }
 
-template <bool kFp8, int kMode, bool kGated, bool kPair, int kBox>
+template <bool kFp8, int kMode, bool kGated, bool kPair, int kBox, bool kF16 = false>
 static int launch(const CUtensorMap& ma, const CUtensorMap& mb, const Params& p, cudaStream_t stream) {
-    auto kern = moe_GemmGrouped_GemmUniversal_tcgen05<kFp8, kMode, kGated, kPair, kBox>;
+    auto kern = moe_GemmGrouped_GemmUniversal_tcgen05<kFp8, kMode, kGated, kPair, kBox, kF16>;
     static bool configured = false;  // per instantiation
     static int configured_dev = -1;
     int dev = 0;
@@ -840,7 +868,9 @@ static bool use_pairs(int n, int E, int quant_mode) {
 
 int grouped_gemm(const void* a, const float* a_scale, const void* w, const float* w_scale, const int* offsets,
                  const int* mtile_prefix, int n, int N, int K, int E, int quant_mode, int gated, void* out,
-                 float* out_scale, float* amax, const int* dest_to_src, const void* row_dst, cudaStream_t stream) {
+                 float* out_scale, float* amax, const int* dest_to_src, const void* row_dst, cudaStream_t stream,
+                 bool f16) {
+    DQ_CHECK(!f16 || quant_mode == DQMOE_QUANT_NONE);
     DQ_CHECK(quant_mode == DQMOE_QUANT_NONE || quant_mode == DQMOE_QUANT_FP8_TENSOR ||
              quant_mode == DQMOE_QUANT_FP8_CHANNEL || quant_mode == DQMOE_QUANT_FP8_BLOCK);
     DQ_CHECK(n >= 0 && N > 0 && K > 0 && E > 0 && E <= kMaxExperts);
@@ -911,6 +941,12 @@ int grouped_gemm(const void* a, const float* a_scale, const void* w, const float
 #define DQ_GEMM_CASE(FP8, MODE)                                                              \
     return pair ? DQ_GEMM_LAUNCH(FP8, MODE, true, 128)                                        \
                 : (narrow ? DQ_GEMM_LAUNCH(FP8, MODE, false, 64) : DQ_GEMM_LAUNCH(FP8, MODE, false, 128))
+#define DQ_GEMM_LAUNCH_F16(PAIR, BOX)                                                          \
+    (gated ? launch<false, kNone, true, PAIR, BOX, true>(ma, mb, p, stream)                    \
+           : launch<false, kNone, false, PAIR, BOX, true>(ma, mb, p, stream))
+    if (f16)
+        return pair ? DQ_GEMM_LAUNCH_F16(true, 128) : (narrow ? DQ_GEMM_LAUNCH_F16(false, 64) : DQ_GEMM_LAUNCH_F16(false, 128));
+#undef DQ_GEMM_LAUNCH_F16
     switch (quant_mode) {
         case DQMOE_QUANT_NONE: DQ_GEMM_CASE(false, kNone);
         case DQMOE_QUANT_FP8_TENSOR: DQ_GEMM_CASE(true, kTensor);
@@ -933,12 +969,12 @@ extern "C" int dqmoe_grouped_gemm(const void* a, const float* a_scale, const voi
                                   int quant_mode, int gated, void* out, float* out_scale, float* amax,
                                   const int32_t* dest_to_src, dqmoe_stream_t stream) {
     return dq::gemm::grouped_gemm(a, a_scale, w, w_scale, offsets, mtile_prefix, n, N, K, E, quant_mode, gated, out,
-                                  out_scale, amax, dest_to_src, nullptr, static_cast<cudaStream_t>(stream));
+                                  out_scale, amax, dest_to_src, nullptr, static_cast<cudaStream_t>(stream), false);
 }
 
 extern "C" int dqmoe_grouped_gemm_rows(const void* a, const float* a_scale, const void* w, const float* w_scale,
                                        const int32_t* offsets, const int32_t* mtile_prefix, int n, int N, int K, int E,
                                        int quant_mode, const void* row_dst, dqmoe_stream_t stream) {
     return dq::gemm::grouped_gemm(a, a_scale, w, w_scale, offsets, mtile_prefix, n, N, K, E, quant_mode, 0, nullptr,
-                                  nullptr, nullptr, nullptr, row_dst, static_cast<cudaStream_t>(stream));
+                                  nullptr, nullptr, nullptr, row_dst, static_cast<cudaStream_t>(stream), false);
 }

@@ -19,7 +19,8 @@ int route_topk(const float* logits, int T, int E, int k, int n_shared, int scori
 namespace gemm {
 int grouped_gemm(const void* a, const float* a_scale, const void* w, const float* w_scale, const int* offsets,
                  const int* mtile_prefix, int n, int N, int K, int E, int quant_mode, int gated, void* out,
-                 float* out_scale, float* amax, const int* dest_to_src, const void* row_dst, cudaStream_t stream);
+                 float* out_scale, float* amax, const int* dest_to_src, const void* row_dst, cudaStream_t stream,
+                 bool f16 = false);
 }  // namespace gemm
 
 namespace decode {
@@ -108,12 +109,11 @@ void* dqmoe_moe_workspace_ptr(void* workspace, int which, int T, int H, int I, i
     }
 }
 
-int dqmoe_moe_forward(const void* a, const float* a_scale, const void* b, const float* b_scale, const void* b1,
-                      const float* b1_scale, void* d, const int32_t* m_indices, void* workspace,
-                      size_t workspace_bytes, int T, int H, int I, int E, int k, int quant_mode, int fused,
-                      dqmoe_stream_t stream_) {
-    (void) fused;
-    cudaStream_t stream = static_cast<cudaStream_t>(stream_);
+// f16: the operands and the output are IEEE half instead of bf16 (quant_mode NONE only)
+static int moe_forward_impl(const void* a, const float* a_scale, const void* b, const float* b_scale, const void* b1,
+                            const float* b1_scale, void* d, const int32_t* m_indices, void* workspace,
+                            size_t workspace_bytes, int T, int H, int I, int E, int k, int quant_mode, bool f16,
+                            cudaStream_t stream) {
     DQ_CHECK(T >= 0 && H > 0 && I > 0 && E > 0 && k > 0);
     DQ_CHECK_FMT(layer::valid_mode(quant_mode), "quant_mode_value=%d is not one of 0, 256, 512, 1024", quant_mode);
     if (T == 0) return DQMOE_OK;  // as csrc/pybind11_register.h:125-126
@@ -144,7 +144,7 @@ int dqmoe_moe_forward(const void* a, const float* a_scale, const void* b, const 
     void* act_bf16 = ws + L.act_bf16;
     float* amax = reinterpret_cast<float*>(ws + L.amax);
 
-    if (n <= layer::kDecodeRows && (quant_mode == DQMOE_QUANT_NONE || quant_mode == DQMOE_QUANT_FP8_TENSOR) &&
+    if (!f16 && n <= layer::kDecodeRows && (quant_mode == DQMOE_QUANT_NONE || quant_mode == DQMOE_QUANT_FP8_TENSOR) &&
         size_t(H > I ? H : I) * sizeof(float) <= 200 * 1024)
         return decode::forward(a, a_scale, b, b_scale, b1, b1_scale, d, m_indices, fp8 ? act_bf16 : act, amax, T, H, I,
                                E, k, fp8, stream);
@@ -164,7 +164,7 @@ int dqmoe_moe_forward(const void* a, const float* a_scale, const void* b, const 
         DQ_CUDA(cudaMemsetAsync(amax, 0, amax_bytes, stream));
     }
     rc = gemm::grouped_gemm(perm_a, sa1, b, b_scale, offsets, mtile_prefix, n, I, H, E, quant_mode, 1,
-                            two_pass ? act_bf16 : act, act_scale, amax, nullptr, nullptr, stream);
+                            two_pass ? act_bf16 : act, act_scale, amax, nullptr, nullptr, stream, f16);
     if (rc != DQMOE_OK) return rc;
     if (two_pass) {
         rc = dqmoe_requant_from_amax(act_bf16, n, I, amax, quant_mode == DQMOE_QUANT_FP8_CHANNEL ? 1 : 0, act,
@@ -172,8 +172,24 @@ int dqmoe_moe_forward(const void* a, const float* a_scale, const void* b, const 
         if (rc != DQMOE_OK) return rc;
     }
     rc = gemm::grouped_gemm(act, act_scale, b1, b1_scale, offsets, mtile_prefix, n, H, I, E, quant_mode, 0, d, nullptr,
-                            nullptr, dest_to_src, nullptr, stream);
+                            nullptr, dest_to_src, nullptr, stream, f16);
     return rc;
+}
+
+int dqmoe_moe_forward(const void* a, const float* a_scale, const void* b, const float* b_scale, const void* b1,
+                      const float* b1_scale, void* d, const int32_t* m_indices, void* workspace,
+                      size_t workspace_bytes, int T, int H, int I, int E, int k, int quant_mode, int fused,
+                      dqmoe_stream_t stream) {
+    (void) fused;
+    return moe_forward_impl(a, a_scale, b, b_scale, b1, b1_scale, d, m_indices, workspace, workspace_bytes, T, H, I, E, k,
+                            quant_mode, false, static_cast<cudaStream_t>(stream));
+}
+
+int dqmoe_moe_forward_f16(const void* a, const void* b, const void* b1, void* d, const int32_t* m_indices,
+                          void* workspace, size_t workspace_bytes, int T, int H, int I, int E, int k,
+                          dqmoe_stream_t stream) {
+    return moe_forward_impl(a, nullptr, b, nullptr, b1, nullptr, d, m_indices, workspace, workspace_bytes, T, H, I, E, k,
+                            DQMOE_QUANT_NONE, true, static_cast<cudaStream_t>(stream));
 }
 
 // ---------------------------------------------------------------------------------------------

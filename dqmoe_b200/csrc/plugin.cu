@@ -59,12 +59,14 @@ static int validate(const dqmoe_plugin_fields& f) {
     DQ_CHECK_FMT(f.max_num_tokens >= 0, "max_num_tokens=%d", f.max_num_tokens);
     // the reference's runner carries expert_bias1/2 but never reads them (csrc/moe_kernels.h:72-75)
     DQ_CHECK_FMT(f.use_bias == 0, "use_bias=%d: expert biases are not applied by the layer", f.use_bias);
-    DQ_CHECK_FMT(f.type == DQMOE_DT_FP8 || f.type == DQMOE_DT_BF16,
-                 "type=%d: built for FP8 (6) and BF16 (7) operands; the FP16/FP32 instantiations are not built", f.type);
+    DQ_CHECK_FMT(f.type == DQMOE_DT_FP8 || f.type == DQMOE_DT_BF16 || f.type == DQMOE_DT_HALF,
+                 "type=%d: built for FP8 (6), BF16 (7) and HALF (1) operands; the FP32 instantiation is not built", f.type);
     DQ_CHECK_FMT(f.output_type == DQMOE_DT_BF16 || f.output_type == DQMOE_DT_HALF || f.output_type == DQMOE_DT_FLOAT,
                  "output_type=%d", f.output_type);
-    if (f.type == DQMOE_DT_BF16)
-        DQ_CHECK_FMT(f.quant_mode == DQMOE_QUANT_NONE, "quant_mode=%d with BF16 operands", f.quant_mode);
+    if (f.type == DQMOE_DT_HALF)
+        DQ_CHECK_FMT(f.output_type == DQMOE_DT_HALF, "output_type=%d: HALF operands give HALF output", f.output_type);
+    if (f.type == DQMOE_DT_BF16 || f.type == DQMOE_DT_HALF)
+        DQ_CHECK_FMT(f.quant_mode == DQMOE_QUANT_NONE, "quant_mode=%d with unquantised operands", f.quant_mode);
     else
         DQ_CHECK_FMT(f.quant_mode == DQMOE_QUANT_FP8_TENSOR || f.quant_mode == DQMOE_QUANT_FP8_CHANNEL ||
                          f.quant_mode == DQMOE_QUANT_FP8_BLOCK,
@@ -108,7 +110,7 @@ int dqmoe_plugin_get_fields(const dqmoe_plugin* p, dqmoe_plugin_fields* out) {
 size_t dqmoe_plugin_workspace_size(const dqmoe_plugin* p, int num_tokens) {
     if (p == nullptr || num_tokens < 0 || num_tokens > p->f.max_num_tokens) return 0;
     size_t bytes = plugin::layer_bytes(p->f, num_tokens);
-    if (p->f.output_type != DQMOE_DT_BF16)  // the layer writes bf16; other output types go through a staging copy
+    if (p->f.type != DQMOE_DT_HALF && p->f.output_type != DQMOE_DT_BF16)  // bf16 result staged for conversion
         bytes += align_up(size_t(num_tokens) * p->f.top_k * p->f.expert_hidden_size * 2, plugin::kAlign);
     return bytes;
 }
@@ -126,6 +128,9 @@ int dqmoe_plugin_enqueue(const dqmoe_plugin* p, int num_tokens, const void* cons
     const bool fp8 = f.quant_mode != DQMOE_QUANT_NONE;
     const int T = num_tokens, H = f.expert_hidden_size, I = f.expert_inter_size, E = f.number_of_experts, k = f.top_k;
     const size_t lbytes = plugin::layer_bytes(f, T);
+    if (f.type == DQMOE_DT_HALF)
+        return dqmoe_moe_forward_f16(inputs[0], inputs[1], inputs[2], outputs[0], static_cast<const int32_t*>(inputs[3]),
+                                     workspace, lbytes, T, H, I, E, k, stream_);
     void* d = f.output_type == DQMOE_DT_BF16 ? outputs[0] : static_cast<char*>(workspace) + lbytes;
     int rc = dqmoe_moe_forward(inputs[0], fp8 ? static_cast<const float*>(inputs[6]) : nullptr, inputs[1],
                                fp8 ? static_cast<const float*>(inputs[7]) : nullptr, inputs[2],

@@ -98,6 +98,17 @@ int dqmoe_moe_forward(const void* a, const float* a_scale, const void* b, const 
                       int quant_mode, int fused, dqmoe_stream_t stream);
 
 /*
+ * The unquantised layer on IEEE half operands: a [T,H], b [E,2I,H], b1 [E,H,I] and
+ * d [T,k,H] are fp16, accumulation is fp32, every intermediate rounding is to fp16. The
+ * T = half instantiation of the reference's runner (csrc/pybind11_register.h:104-151
+ * is templated on the activation type; its Python module exports only the bf16 one). Same
+ * workspace size as quant_mode DQMOE_QUANT_NONE.
+ */
+int dqmoe_moe_forward_f16(const void* a, const void* b, const void* b1, void* d,
+                          const int32_t* m_indices, void* workspace, size_t workspace_bytes, int T,
+                          int H, int I, int E, int k, dqmoe_stream_t stream);
+
+/*
  * Addresses of intermediates inside a workspace laid out by dqmoe_moe_forward
  * for the same problem size (debug/testing aid; the reference has the unused
  * extractIntermediateResultsforTorch, csrc/moe_kernels.h:739-767).
@@ -153,10 +164,11 @@ int dqmoe_moe_block_shared(const void* x_bf16, const float* logits, const void* 
  * reference; its kernels are the ones dqmoe_moe_forward replaces.
  *
  * type / output_type use the nvinfer1::DataType codes below. Built: FP8 operands with
- * quant_mode 256 / 512 / 1024 and BF16 operands with quant_mode 0; outputs BF16 (written
- * directly), HALF or FLOAT (converted from the layer's bf16 result through workspace).
- * type FLOAT / HALF (the reference's unquantised FP32 / FP16 instantiations) and
- * use_bias != 0 return DQMOE_ERR_INVALID.
+ * quant_mode 256 / 512 / 1024 and BF16 operands with quant_mode 0, with outputs BF16
+ * (written directly), HALF or FLOAT (converted from the layer's bf16 result through
+ * workspace); HALF operands with quant_mode 0 and HALF output (dqmoe_moe_forward_f16).
+ * type FLOAT (the reference's unquantised FP32 instantiation) and use_bias != 0 return
+ * DQMOE_ERR_INVALID.
  * enqueue inputs: 0 input [T,H], 1 weight1 [E,2I,H], 2 weight2 [E,H,I], 3 index [T,k] int32,
  * 4 bias1, 5 bias2 (never read), 6 actscale, 7 scale_a (fc1 weight scales), 8 scale_b (fc2
  * weight scales); entries 6-8 are read only for FP8 operands. Scale shapes per mode as

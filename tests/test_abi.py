@@ -69,7 +69,9 @@ def test_plugin_descriptor_host_calls():
     assert plugin.MoePlugin.deserialize(blob).fields == f
     with pytest.raises(RuntimeError, match="expected 36"):
         plugin.MoePlugin.deserialize(blob[:-4])
-    for bad in (dict(use_bias=1), dict(type=plugin.DT_FLOAT, quant_mode=0), dict(type=plugin.DT_HALF, quant_mode=0),
+    for bad in (dict(use_bias=1), dict(type=plugin.DT_FLOAT, quant_mode=0),
+                dict(type=plugin.DT_HALF, quant_mode=0, output_type=plugin.DT_BF16),
+                dict(type=plugin.DT_HALF, quant_mode=512, output_type=plugin.DT_HALF),
                 dict(type=plugin.DT_BF16, quant_mode=512), dict(type=plugin.DT_FP8, quant_mode=0),
                 dict(output_type=3)):
         with pytest.raises(RuntimeError, match=r"\[ASSERT FAILED\] plugin.cu"):

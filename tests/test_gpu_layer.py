@@ -289,6 +289,24 @@ def test_moe_block_router_to_weighted_output(ops, mode, scoring):
     assert_close(out, ref)
 
 
+@pytest.mark.parametrize("E,T,H,I,k", [(8, 64, 1024, 2048, 2), (8, 300, 512, 384, 3), (4, 2000, 512, 256, 1), (3, 5, 192, 160, 2)])
+def test_layer_fp16_operands(ops, workspace, E, T, H, I, k):
+    """dqmoe_moe_forward_f16: fp16 activations, weights and output against the oracle's layer run on fp16
+    tensors (torch_moe_grouped of test/util.py:71-92 is dtype-generic). Includes the 2000-row-per-expert case
+    that takes the CTA-pair tiles and a ragged one."""
+    a, b, b1, _, m_indices = make_inputs(23, T, H, I, E, k, 1.0, 0.05)
+    a, b, b1 = a.half(), b.half(), b1.half()
+    ref = orc.moe_layer_bf16(a, b, b1, m_indices, E)
+    assert ref.dtype == torch.float16
+    d = torch.zeros(T, k, H, dtype=torch.float16, device=DEV)
+    ops.moe_forward_f16(a.to(DEV), b.to(DEV), b1.to(DEV), d, m_indices.to(DEV), workspace)
+    torch.cuda.synchronize()
+    assert ops.device_status() == 0
+    assert_close(d, ref)
+    # fp16 has three more mantissa bits than bf16: the result must be closer to the oracle than a bf16 run is
+    assert orc.max_rel_err(d.cpu(), ref) < 5e-3
+
+
 @pytest.mark.parametrize("mode,n_shared", [(0, 1), (1024, 1), (1024, 2)])
 def test_moe_block_with_shared_experts(ops, mode, n_shared):
     """dqmoe_moe_block_shared: the last n_shared experts of the weight tensors see every token with weight 1

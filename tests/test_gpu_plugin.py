@@ -43,6 +43,20 @@ def test_plugin_enqueue_matches_oracle(mode, out_type):
         assert torch.equal(direct.enqueue(inputs).float(), out.float())
 
 
+def test_plugin_half_operands():
+    """The fp16 engine of test/trt_test.py:386-455: HALF inputs, HALF output, quant_mode 0."""
+    from dqmoe_b200 import ops, plugin
+    E, T, H, I, k = 8, 96, 512, 384, 2
+    a, b, b1, _, idx = make_inputs(19, T, H, I, E, k, 1.0, 0.05)
+    a, b, b1 = a.half(), b.half(), b1.half()
+    p = plugin.MoePlugin(E, k, H, I, max_num_tokens=128, type=plugin.DT_HALF, output_type=plugin.DT_HALF, quant_mode=0)
+    out = p.enqueue([a.to(DEV), b.to(DEV), b1.to(DEV), idx.to(DEV), None, None])
+    torch.cuda.synchronize()
+    assert ops.device_status() == 0 and out.dtype == torch.float16
+    ref = orc.moe_layer_bf16(a, b, b1, idx, E)
+    assert orc.cosine(out.cpu(), ref) >= COS_MIN and orc.max_rel_err(out.cpu(), ref) <= REL_MAX
+
+
 def test_plugin_rejects_too_many_tokens():
     from dqmoe_b200 import plugin
     p = plugin.MoePlugin(8, 2, 512, 384, max_num_tokens=16, type=plugin.DT_BF16, quant_mode=0)
