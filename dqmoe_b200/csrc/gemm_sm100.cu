@@ -16,6 +16,7 @@
 #include <cuda_fp16.h>
 
 #include <cstdlib>
+#include <type_traits>
 
 #include "common.cuh"
 #include "ptx_sm100.cuh"
@@ -618,67 +619,72 @@ moe_GemmGrouped_GemmUniversal_tcgen05(const __grid_constant__ CUtensorMap tma_a,
                 const bool uniform = (c_switch & 31) == 0;
 
                 // Software pipeline over the four 32-column chunks of a K block: while 32 FMAs run
-                // on one register set the TMEM load of the next chunk lands in the other, and the
-                // first two chunks of the next K block are requested before the last two are added.
-                auto tcol = [&](int c) { return (c >> 1) * kBoxRows + h * 64 + (c & 1) * 32; };
-                auto fma_chunk = [&](int c, const uint32_t (&r)[32], float s0, float s1l, float s1h) {
-                    const int cin = h * 64 + (c & 1) * 32;  // column inside the 128-column group
-                    if (c < 2) {
-#pragma unroll
-                        for (int i = 0; i < 32; i += 2) ffma2(acc[c * 32 + i], acc[c * 32 + i + 1], r[i], r[i + 1], s0, s0);
-                    } else if (uniform) {
-                        const float s1 = cin < c_switch ? s1l : s1h;
-#pragma unroll
-                        for (int i = 0; i < 32; i += 2) ffma2(acc[c * 32 + i], acc[c * 32 + i + 1], r[i], r[i + 1], s1, s1);
-                    } else {
-#pragma unroll
-                        for (int i = 0; i < 32; i += 2)
-                            ffma2(acc[c * 32 + i], acc[c * 32 + i + 1], r[i], r[i + 1], (cin + i) < c_switch ? s1l : s1h,
-                                  (cin + i + 1) < c_switch ? s1l : s1h);
-                    }
-                };
+                // on one register set the TMEM load of the next chunk lands in the other.
                 // The TMEM buffer must go back to the MMA warp as early as possible (the round trip
                 // MMA -> drain -> MMA of one buffer bounds the K-block rate), so per K block: fetch the
                 // scales, wait for the buffer, pull the four 32-column chunks through two register
                 // sets, release the buffer, and only then add the last two chunks.
-                uint32_t r0[32], r1[32];
-                for (int kb = 0; kb < KB; ++kb, ++acc_it, ++sc_it) {
-                    const int slot = sc_it % kScaleSlots;
-                    if (!ptx::mbar_wait(&st.sc_full[slot], (sc_it / kScaleSlots) & 1u, abort_flag, kWaitLimit)) {
-                        ok = false;
-                        break;
-                    }
-                    const float a_s = st.sc_a[slot][r_in_tile];
-                    const float s0 = a_s * st.sc_b[slot][0], s1l = a_s * st.sc_b[slot][1], s1h = a_s * st.sc_b[slot][2];
-                    __syncwarp();
-                    if (lane == 0) ptx::mbar_arrive(&st.sc_empty[slot]);
+                // The loop exists twice: kOneScale when the second column group lies inside one 128-row
+                // weight-scale block (always in stage 2; in stage 1 unless I % 128 != 0), where no
+                // per-column choice of scale is left in the inner loop, and the general form.
+                auto tcol = [&](int c) { return (c >> 1) * kBoxRows + h * 64 + (c & 1) * 32; };
+                auto k_loop = [&](auto one_scale_tag) {
+                    constexpr bool kOneScale = decltype(one_scale_tag)::value;
+                    auto fma_chunk = [&](int c, const uint32_t (&r)[32], float s0, float s1l, float s1h) {
+                        const int cin = h * 64 + (c & 1) * 32;  // column inside the 128-column group
+                        if (c < 2) {
+#pragma unroll
+                            for (int i = 0; i < 32; i += 2) ffma2(acc[c * 32 + i], acc[c * 32 + i + 1], r[i], r[i + 1], s0, s0);
+                        } else if (kOneScale || uniform) {
+                            const float s1 = kOneScale || cin < c_switch ? s1l : s1h;
+#pragma unroll
+                            for (int i = 0; i < 32; i += 2) ffma2(acc[c * 32 + i], acc[c * 32 + i + 1], r[i], r[i + 1], s1, s1);
+                        } else {
+#pragma unroll
+                            for (int i = 0; i < 32; i += 2)
+                                ffma2(acc[c * 32 + i], acc[c * 32 + i + 1], r[i], r[i + 1], (cin + i) < c_switch ? s1l : s1h,
+                                      (cin + i + 1) < c_switch ? s1l : s1h);
+                        }
+                    };
+                    uint32_t r0[32], r1[32];
+                    for (int kb = 0; kb < KB; ++kb, ++acc_it, ++sc_it) {
+                        const int slot = sc_it % kScaleSlots;
+                        if (!ptx::mbar_wait(&st.sc_full[slot], (sc_it / kScaleSlots) & 1u, abort_flag, kWaitLimit)) return false;
+                        const float a_s = st.sc_a[slot][r_in_tile];
+                        const float s0 = a_s * st.sc_b[slot][0], s1l = a_s * st.sc_b[slot][1];
+                        const float s1h = kOneScale ? 0.0f : a_s * st.sc_b[slot][2];
+                        __syncwarp();
+                        if (lane == 0) ptx::mbar_arrive(&st.sc_empty[slot]);
 
-                    const uint32_t buf = acc_it & 1u;
-                    if (!ptx::mbar_wait(&st.tmem_full[buf], (acc_it >> 1) & 1u, abort_flag, kWaitLimit)) {
-                        ok = false;
-                        break;
+                        const uint32_t buf = acc_it & 1u;
+                        if (!ptx::mbar_wait(&st.tmem_full[buf], (acc_it >> 1) & 1u, abort_flag, kWaitLimit)) return false;
+                        if (lane == 0) DQ_STAMP(warp - 2, acc_it, 0);
+                        ptx::tc_fence_after();
+                        const uint32_t t_buf = t_lane + buf * kUmmaN;
+                        ptx::tmem_ld32(t_buf + tcol(0), r0);
+                        ptx::tmem_ld32(t_buf + tcol(1), r1);
+                        if (lane == 0) DQ_STAMP(warp - 2, acc_it, 1);
+                        ptx::tmem_wait_ld2(r0, r1);
+                        if (lane == 0) DQ_STAMP(warp - 2, acc_it, 2);
+                        fma_chunk(0, r0, s0, s1l, s1h);
+                        ptx::tmem_ld32(t_buf + tcol(2), r0);
+                        fma_chunk(1, r1, s0, s1l, s1h);
+                        ptx::tmem_ld32(t_buf + tcol(3), r1);
+                        ptx::tmem_wait_ld2(r0, r1);
+                        if (lane == 0) DQ_STAMP(warp - 2, acc_it, 3);
+                        ptx::tc_fence_before();
+                        __syncwarp();
+                        if (lane == 0) release_tmem(buf);
+                        fma_chunk(2, r0, s0, s1l, s1h);
+                        fma_chunk(3, r1, s0, s1l, s1h);
+                        if (lane == 0) DQ_STAMP(warp - 2, acc_it, 4);
                     }
-                    if (lane == 0) DQ_STAMP(warp - 2, acc_it, 0);
-                    ptx::tc_fence_after();
-                    const uint32_t t_buf = t_lane + buf * kUmmaN;
-                    ptx::tmem_ld32(t_buf + tcol(0), r0);
-                    ptx::tmem_ld32(t_buf + tcol(1), r1);
-                    if (lane == 0) DQ_STAMP(warp - 2, acc_it, 1);
-                    ptx::tmem_wait_ld2(r0, r1);
-                    if (lane == 0) DQ_STAMP(warp - 2, acc_it, 2);
-                    fma_chunk(0, r0, s0, s1l, s1h);
-                    ptx::tmem_ld32(t_buf + tcol(2), r0);
-                    fma_chunk(1, r1, s0, s1l, s1h);
-                    ptx::tmem_ld32(t_buf + tcol(3), r1);
-                    ptx::tmem_wait_ld2(r0, r1);
-                    if (lane == 0) DQ_STAMP(warp - 2, acc_it, 3);
-                    ptx::tc_fence_before();
-                    __syncwarp();
-                    if (lane == 0) release_tmem(buf);
-                    fma_chunk(2, r0, s0, s1l, s1h);
-                    fma_chunk(3, r1, s0, s1l, s1h);
-                    if (lane == 0) DQ_STAMP(warp - 2, acc_it, 4);
-                }
+                    return true;
+                };
+                if (!kGated || c_switch == 128)
+                    ok = k_loop(std::true_type{});
+                else
+                    ok = k_loop(std::false_type{});
                 if (!ok) break;
 
                 if constexpr (kGated) {
