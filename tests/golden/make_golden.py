@@ -108,7 +108,9 @@ def layer_case(util, seed, T, H, I, E, k, act_std, w_std, store_inputs):
 
 
 def main():
-    ref_root = sys.argv[1] if len(sys.argv) > 1 else "/root/reference"
+    ref_root = sys.argv[1] if len(sys.argv) > 1 else os.environ.get("DQMOE_REFERENCE_ROOT", "")
+    if not ref_root or not os.path.isdir(ref_root):
+        raise SystemExit("usage: make_golden.py <checkout of the reference repository>  (or DQMOE_REFERENCE_ROOT)")
     util = load_reference_util(ref_root)
     torch.set_num_threads(max(1, os.cpu_count() or 1))
     np.savez_compressed(os.path.join(HERE, "quantizers.npz"), **quantizer_cases(util))
