@@ -305,11 +305,17 @@ def grouped_gemm(a, a_scale, w, w_scale, offsets, mtile_pref, N: int, quant_mode
             int(bool(gated)), _p(out), _p(out_scale), _p(amax), _p(dest_to_src), _stream(a.device)))
 
 
-def requant_from_amax(act: torch.Tensor, amax: torch.Tensor, per_row: bool):
+def requant_from_amax(act: torch.Tensor, amax: torch.Tensor, per_row: bool, n_rows_device: Optional[torch.Tensor] = None,
+                      out: Optional[Tuple[torch.Tensor, torch.Tensor]] = None):
+    """Second pass of the tensor / channel modes. n_rows_device: int32 [1] on the device bounding the rows
+    that are processed (dqmoe_requant_from_amax_dev); rows past it keep what `out` held."""
     n, I = act.shape
-    q = torch.empty((n, I), dtype=FP8, device=act.device)
-    s = torch.empty(n if per_row else 1, dtype=torch.float32, device=act.device)
+    if out is None:
+        q = torch.empty((n, I), dtype=FP8, device=act.device)
+        s = torch.empty(n if per_row else 1, dtype=torch.float32, device=act.device)
+    else:
+        q, s = out
     with torch.cuda.device(act.device):
-        _lib.check(_lib.load().dqmoe_requant_from_amax(_p(act), n, I, _p(amax), int(per_row), _p(q), _p(s),
-                                                       _stream(act.device)))
+        _lib.check(_lib.load().dqmoe_requant_from_amax_dev(_p(act), n, I, _p(amax), int(per_row), _p(q), _p(s),
+                                                           _p(n_rows_device), _stream(act.device)))
     return q, s

@@ -156,3 +156,19 @@ def test_requant_from_amax_bit_exact(ops, rows, cols):
     rq, rs = orc.quant_tensor(x)
     assert np.array_equal(bits(q), bits(rq))
     assert torch.equal(s.cpu(), rs.reshape(-1))
+
+
+def test_requant_row_count_read_on_the_device(ops):
+    """dqmoe_requant_from_amax_dev: only the first *n_rows_device rows are quantised (an expert-parallel rank
+    learns how many rows it received on the device only); the rest of the output is left alone."""
+    rows, cols, live = 200, 256, 77
+    x = (torch.randn(rows, cols, generator=torch.Generator().manual_seed(3)) * 2).to(torch.bfloat16)
+    xd = x.to(DEV)
+    q = torch.full((rows, cols), 0x7b, dtype=torch.uint8, device=DEV).view(torch.float8_e4m3fn)
+    s = torch.full((rows,), -1.0, device=DEV)
+    count = torch.tensor([live], dtype=torch.int32, device=DEV)
+    ops.requant_from_amax(xd, xd.abs().float().amax(dim=1).contiguous(), True, n_rows_device=count, out=(q, s))
+    rq, rs = orc.quant_rowwise(x)
+    assert np.array_equal(bits(q[:live]), bits(rq[:live]))
+    assert torch.equal(s[:live].cpu(), rs.reshape(-1)[:live])
+    assert (q[live:].view(torch.uint8) == 0x7b).all() and (s[live:] == -1.0).all()
