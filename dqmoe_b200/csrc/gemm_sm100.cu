@@ -609,6 +609,7 @@ moe_GemmGrouped_GemmUniversal_tcgen05(const __grid_constant__ CUtensorMap tma_a,
             } else {
                 // ---------------------------------------------------- block-scaled accumulation
                 // acc[c*32 + i]: chunk c of this thread's four 32-column chunks.
+                if (lane == 0) DQ_STAMP(warp - 2, acc_it, 5);
                 float acc[128];
 #pragma unroll
                 for (int i = 0; i < 128; ++i) acc[i] = 0.0f;
@@ -655,6 +656,7 @@ moe_GemmGrouped_GemmUniversal_tcgen05(const __grid_constant__ CUtensorMap tma_a,
                         const float s1h = kOneScale ? 0.0f : a_s * st.sc_b[slot][2];
                         __syncwarp();
                         if (lane == 0) ptx::mbar_arrive(&st.sc_empty[slot]);
+                        if (lane == 0 && kb == 0) DQ_STAMP(warp - 2, acc_it, 6);
 
                         const uint32_t buf = acc_it & 1u;
                         if (!ptx::mbar_wait(&st.tmem_full[buf], (acc_it >> 1) & 1u, abort_flag, kWaitLimit)) return false;
