@@ -696,24 +696,31 @@ moe_GemmGrouped_GemmUniversal_tcgen05(const __grid_constant__ CUtensorMap tma_a,
                     // The tensor pipe idles during this part (the same warps drain its buffers), so it is
                     // written for throughput: bf16 roundings on the fp32 pipe (bf_round), eight elements
                     // per step and stage by stage so that the exp / reciprocal latencies overlap.
+                    auto swiglu = [&](auto full_tag) {
+                        constexpr bool kFullTile = decltype(full_tag)::value;  // all 64 columns inside the matrix
 #pragma unroll
-                    for (int i0 = 0; i0 < 64; i0 += 8) {
-                        float g8[8], e8[8];
+                        for (int i0 = 0; i0 < 64; i0 += 8) {
+                            float g8[8], e8[8];
 #pragma unroll
-                        for (int j = 0; j < 8; ++j) {
-                            g8[j] = bf_round(acc[i0 + j]);
-                            e8[j] = __expf(-g8[j]);
+                            for (int j = 0; j < 8; ++j) {
+                                g8[j] = bf_round(acc[i0 + j]);
+                                e8[j] = __expf(-g8[j]);
+                            }
+#pragma unroll
+                            for (int j = 0; j < 8; ++j) e8[j] = bf_round(__fdividef(g8[j], 1.0f + e8[j]));
+#pragma unroll
+                            for (int j = 0; j < 8; ++j) {
+                                float act = bf_round(e8[j] * bf_round(acc[64 + i0 + j]));
+                                if (!kFullTile && col0 + i0 + j >= I_or_H) act = 0.0f;
+                                acc[i0 + j] = act;
+                                amax_local = fmaxf(amax_local, fabsf(act));
+                            }
                         }
-#pragma unroll
-                        for (int j = 0; j < 8; ++j) e8[j] = bf_round(__fdividef(g8[j], 1.0f + e8[j]));
-#pragma unroll
-                        for (int j = 0; j < 8; ++j) {
-                            float act = bf_round(e8[j] * bf_round(acc[64 + i0 + j]));
-                            if (col0 + i0 + j >= I_or_H) act = 0.0f;
-                            acc[i0 + j] = act;
-                            amax_local = fmaxf(amax_local, fabsf(act));
-                        }
-                    }
+                    };
+                    if (col0 + 64 <= I_or_H)
+                        swiglu(std::true_type{});
+                    else
+                        swiglu(std::false_type{});
                     if (lane == 0) DQ_STAMP(warp - 2, acc_it - 1, 5);
                     // the 1x128 group spans both halves: exchange the partial amax through shared memory
                     st.amax[tile_it & 1u][h][r_in_tile] = amax_local;
