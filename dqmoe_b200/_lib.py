@@ -28,6 +28,10 @@ SIGNATURES = {
     "dqmoe_moe_forward": (_c_int, [_ptr] * 9 + [_c_size] + [_c_int] * 7 + [_ptr]),
     "dqmoe_moe_workspace_ptr": (_ptr, [_ptr] + [_c_int] * 7),
     "dqmoe_moe_forward_f16": (_c_int, [_ptr] * 6 + [_c_size] + [_c_int] * 5 + [_ptr]),
+    "dqmoe_moe_forward_bias": (_c_int, [_ptr] * 11 + [_c_size] + [_c_int] * 6 + [_ptr]),
+    "dqmoe_moe_forward_f16_bias": (_c_int, [_ptr] * 8 + [_c_size] + [_c_int] * 5 + [_ptr]),
+    "dqmoe_moe_workspace_bytes_f32": (_c_size, [_c_int] * 5),
+    "dqmoe_moe_forward_f32": (_c_int, [_ptr] * 8 + [_c_size] + [_c_int] * 5 + [_ptr]),
     "dqmoe_moe_block_workspace_bytes": (_c_size, [_c_int] * 6),
     "dqmoe_moe_block": (_c_int, [_ptr] * 8 + [_c_size] + [_c_int] * 7 + [_ptr]),
     "dqmoe_moe_block_shared": (_c_int, [_ptr] * 8 + [_c_size] + [_c_int] * 8 + [_ptr]),
@@ -47,7 +51,8 @@ SIGNATURES = {
     "dqmoe_grouped_gemm": (_c_int, [_ptr] * 6 + [_c_int] * 6 + [_ptr] * 5),
     "dqmoe_grouped_gemm_rows": (_c_int, [_ptr] * 6 + [_c_int] * 5 + [_ptr, _ptr]),
     "dqmoe_ep_publish_counts": (_c_int, [_ptr, _c_int, _c_int, _c_int, _ptr, _ptr, _c_int, _ptr]),
-    "dqmoe_ep_plan": (_c_int, [_ptr, _ptr, _c_int, _c_int, _c_int, _c_int, _ptr, _ptr, _ptr, _ptr]),
+    "dqmoe_ep_plan": (_c_int, [_ptr, _ptr, _c_int, _c_int, _c_int, _c_int, _c_int, _ptr, _ptr, _ptr, _ptr]),
+    "dqmoe_ep_set_wait_limit": (_c_int, [_c_i64]),
     "dqmoe_ep_dispatch": (_c_int, [_ptr, _ptr, _c_size, _c_int, _c_int, _c_int, _ptr, _ptr, _ptr, _c_int, _c_int,
                                    _c_int, _ptr, _ptr, _ptr, _ptr, _ptr, _c_int, _ptr]),
     "dqmoe_ep_wait": (_c_int, [_ptr, _c_int, _c_int, _c_int, _ptr]),

@@ -12,6 +12,8 @@
 // Flags carry a per-call epoch, so nothing is reset between calls. Every wait is bounded: a
 // wait that gives up writes the device status word and returns (no trap, no hang).
 // The reference has no multi-GPU path; this extends its layer (csrc/moe_kernels.h:770-892).
+#include <atomic>
+
 #include "common.cuh"
 
 namespace dq {
@@ -19,7 +21,12 @@ namespace ep {
 
 constexpr int kMaxRanks = 8;
 constexpr int kMaxExperts = 1024;
-constexpr long long kWaitLimit = 20000000000LL;  // cycles (~10 s): peers may be late on the host side
+constexpr long long kDefaultWaitLimit = 20000000000LL;  // cycles (~10 s): peers may be late on the host side
+
+// Cycles a flag wait may spin before it gives up; process-wide, set by dqmoe_ep_set_wait_limit and
+// handed to every kernel as an argument at launch.
+static std::atomic<long long> g_wait_limit{kDefaultWaitLimit};
+static long long wait_limit() { return g_wait_limit.load(std::memory_order_relaxed); }
 
 struct Peers {
     void* p[kMaxRanks];
@@ -35,13 +42,13 @@ __device__ __forceinline__ void st_release_sys(int* p, int v) {
 }
 
 // bounded wait until flag == epoch; false (and status written) when it gives up
-__device__ bool wait_flag(const int* flag, int epoch, int* status, int code) {
+__device__ bool wait_flag(const int* flag, int epoch, int* status, int code, long long limit) {
     const long long t0 = clock64();
     unsigned spins = 0;
     while (ld_acquire_sys(flag) != epoch) {
         if (((++spins) & 0x3f) == 0) {
             __nanosleep(200);
-            if (clock64() - t0 > kWaitLimit) {
+            if (clock64() - t0 > limit) {
                 if (status != nullptr) {
                     *reinterpret_cast<volatile int*>(status) = code;
                     __threadfence_system();
@@ -66,24 +73,40 @@ __global__ void __launch_bounds__(256) publish_counts_kernel(const int* __restri
 }
 
 // One block. cnt: my copy of the count matrix [W][E]. Outputs (all local):
-//   send_base[E]      row in the owner's receive buffer where my rows of expert e start
+//   send_base[e]      e < E: row in the owner's receive buffer where my rows of expert e start
+//   send_base[E]      (one more word) 0, or 1 when the plan is void: the counts never arrived, or some rank
+//                     would receive more than `cap` rows
 //   rx_offsets[El+1]  first received row of each of my experts (sum over sources), [El] = rows received
 //   rx_mtiles[El+1]   cumulative 128-row tiles of my experts
+// Every rank sees the same count matrix and so reaches the same verdict on the capacity: on overflow
+// all ranks report status 202, dispatch sends nothing and the GEMMs see zero rows, so nothing is
+// written past a receive buffer.
 __global__ void __launch_bounds__(256) plan_kernel(const int* __restrict__ cnt, const int* __restrict__ my_flags,
-                                                   int E, int me, int W, int epoch, int* __restrict__ send_base,
-                                                   int* __restrict__ rx_offsets, int* __restrict__ rx_mtiles,
-                                                   int* status) {
+                                                   int E, int me, int W, int epoch, int cap,
+                                                   int* __restrict__ send_base, int* __restrict__ rx_offsets,
+                                                   int* __restrict__ rx_mtiles, int* status, long long limit) {
     __shared__ int s_tot[kMaxExperts];
     __shared__ int s_before[kMaxExperts];
     __shared__ int s_ok;
-    if (threadIdx.x == 0) s_ok = 1;
-    __syncthreads();
-    if (threadIdx.x < W) {
-        if (!wait_flag(my_flags + 0 * kMaxRanks + threadIdx.x, epoch, status, 201)) s_ok = 0;
+    __shared__ int s_over;
+    if (threadIdx.x == 0) {
+        s_ok = 1;
+        s_over = 0;
     }
     __syncthreads();
-    if (!s_ok) return;
+    if (threadIdx.x < W) {
+        if (!wait_flag(my_flags + 0 * kMaxRanks + threadIdx.x, epoch, status, 201, limit)) s_ok = 0;
+    }
+    __syncthreads();
     const int El = E / W;
+    if (!s_ok) {  // counts never arrived: leave a plan that moves and computes nothing
+        for (int e = threadIdx.x; e <= El; e += blockDim.x) {
+            rx_offsets[e] = 0;
+            rx_mtiles[e] = 0;
+        }
+        if (threadIdx.x == 0) send_base[E] = 1;
+        return;
+    }
     for (int e = threadIdx.x; e < E; e += blockDim.x) {
         int tot = 0, before = 0;
         for (int s = 0; s < W; ++s) {
@@ -95,6 +118,20 @@ __global__ void __launch_bounds__(256) plan_kernel(const int* __restrict__ cnt, 
         s_before[e] = before;
     }
     __syncthreads();
+    if (threadIdx.x < W) {  // one thread per owner rank: rows it will receive
+        int run = 0;
+        for (int el = 0; el < El; ++el) run += s_tot[threadIdx.x * El + el];
+        if (run > cap) s_over = 1;
+    }
+    __syncthreads();
+    const bool over = s_over != 0;
+    if (threadIdx.x == 0) {
+        send_base[E] = over ? 1 : 0;
+        if (over && status != nullptr) {
+            *reinterpret_cast<volatile int*>(status) = 202;
+            __threadfence_system();
+        }
+    }
     if (threadIdx.x < W) {  // one thread per owner rank: running base over its experts
         const int d = threadIdx.x;
         int run = 0, tiles = 0;
@@ -102,15 +139,15 @@ __global__ void __launch_bounds__(256) plan_kernel(const int* __restrict__ cnt, 
             const int e = d * El + el;
             send_base[e] = run + s_before[e];
             if (d == me) {
-                rx_offsets[el] = run;
-                rx_mtiles[el] = tiles;
+                rx_offsets[el] = over ? 0 : run;
+                rx_mtiles[el] = over ? 0 : tiles;
             }
             run += s_tot[e];
             tiles += (s_tot[e] + 127) / 128;
         }
         if (d == me) {
-            rx_offsets[El] = run;
-            rx_mtiles[El] = tiles;
+            rx_offsets[El] = over ? 0 : run;
+            rx_mtiles[El] = over ? 0 : tiles;
         }
     }
 }
@@ -139,7 +176,7 @@ __global__ void __launch_bounds__(256) dispatch_kernel(const uint8_t* __restrict
     __shared__ int s_off[kMaxExperts + 1];
     for (int e = threadIdx.x; e <= E; e += blockDim.x) s_off[e] = offsets[e];
     __syncthreads();
-    const int kept = s_off[E];
+    const int kept = send_base[E] != 0 ? 0 : s_off[E];  // the plan found a receive buffer too small: send nothing
     const int El = E / W;
     const int lane = threadIdx.x & 31;
     const int warps = gridDim.x * (blockDim.x >> 5);
@@ -176,8 +213,9 @@ __global__ void __launch_bounds__(256) dispatch_kernel(const uint8_t* __restrict
     }
 }
 
-__global__ void wait_kernel(const int* __restrict__ my_flags, int phase, int W, int epoch, int* status) {
-    if (threadIdx.x < W) wait_flag(my_flags + phase * kMaxRanks + threadIdx.x, epoch, status, 210 + phase);
+__global__ void wait_kernel(const int* __restrict__ my_flags, int phase, int W, int epoch, int* status,
+                            long long limit) {
+    if (threadIdx.x < W) wait_flag(my_flags + phase * kMaxRanks + threadIdx.x, epoch, status, 210 + phase, limit);
 }
 
 __global__ void signal_kernel(Peers flags, int phase, int me, int W, int epoch) {
@@ -228,12 +266,21 @@ int dqmoe_ep_publish_counts(const int32_t* counts, int E, int me, int W, const v
     return DQMOE_OK;
 }
 
-int dqmoe_ep_plan(const int32_t* cnt, const int32_t* my_flags, int E, int me, int W, int epoch, int32_t* send_base,
-                  int32_t* rx_offsets, int32_t* rx_mtiles, dqmoe_stream_t stream) {
+int dqmoe_ep_set_wait_limit(int64_t cycles) {
+    DQ_CHECK(cycles >= 0);
+    ep::g_wait_limit.store(cycles == 0 ? ep::kDefaultWaitLimit : static_cast<long long>(cycles),
+                           std::memory_order_relaxed);
+    return DQMOE_OK;
+}
+
+int dqmoe_ep_plan(const int32_t* cnt, const int32_t* my_flags, int E, int me, int W, int epoch, int cap,
+                  int32_t* send_base, int32_t* rx_offsets, int32_t* rx_mtiles, dqmoe_stream_t stream) {
     DQ_CHECK(cnt != nullptr && my_flags != nullptr && send_base != nullptr && rx_offsets != nullptr && rx_mtiles != nullptr);
     DQ_CHECK(E > 0 && E <= ep::kMaxExperts && W >= 1 && W <= ep::kMaxRanks && me >= 0 && me < W && E % W == 0);
-    ep::plan_kernel<<<1, 256, 0, static_cast<cudaStream_t>(stream)>>>(cnt, my_flags, E, me, W, epoch, send_base,
-                                                                      rx_offsets, rx_mtiles, device_status_word());
+    DQ_CHECK(cap >= 0);
+    ep::plan_kernel<<<1, 256, 0, static_cast<cudaStream_t>(stream)>>>(cnt, my_flags, E, me, W, epoch, cap, send_base,
+                                                                      rx_offsets, rx_mtiles, device_status_word(),
+                                                                      ep::wait_limit());
     DQ_LAUNCH_CHECK();
     return DQMOE_OK;
 }
@@ -270,7 +317,8 @@ int dqmoe_ep_dispatch(const void* a, const float* a_scale, size_t row_bytes, int
 
 int dqmoe_ep_wait(const int32_t* my_flags, int phase, int W, int epoch, dqmoe_stream_t stream) {
     DQ_CHECK(my_flags != nullptr && phase >= 0 && phase < 3 && W >= 1 && W <= ep::kMaxRanks);
-    ep::wait_kernel<<<1, 32, 0, static_cast<cudaStream_t>(stream)>>>(my_flags, phase, W, epoch, device_status_word());
+    ep::wait_kernel<<<1, 32, 0, static_cast<cudaStream_t>(stream)>>>(my_flags, phase, W, epoch, device_status_word(),
+                                                                     ep::wait_limit());
     DQ_LAUNCH_CHECK();
     return DQMOE_OK;
 }

@@ -15,7 +15,7 @@
 // (csrc/moe_kernels.h:301-444, 581-620).
 #include <cuda_fp16.h>
 
-#include <cstdlib>
+#include <mutex>
 #include <type_traits>
 
 #include "common.cuh"
@@ -37,11 +37,12 @@ constexpr int kBBytes = kUmmaN * kBKBytes;        // 32 KiB
 constexpr int kStageBytes = kABytes + kBBytes;    // 48 KiB
 constexpr int kStageBytesPair = kABytes + kBBytes / 2;  // 32 KiB per CTA of a pair
 static_assert(kStages * kStageBytes == kStagesPair * kStageBytesPair, "both layouts fill the same stage area");
-constexpr int kThreads = 384;                     // warp 0 TMA, warp 1 MMA, warps 2-3 idle, warps 4..11 epilogue
+constexpr int kThreads = 384;                     // warp 0 TMA, warp 1 MMA, warp 2 scale loader (block mode), warp 3 idle, warps 4..11 epilogue
 constexpr int kRegsControl = 56;                  // registers per thread of the TMA/MMA warpgroup
 constexpr int kRegsEpilogue = 224;                // registers per thread of the two epilogue warpgroups
 constexpr int kEpiWarps = 8;
 constexpr int kMaxExperts = 1024;
+constexpr int kMaxDevices = 64;
 constexpr int kScaleSlots = 8;                     // ring of per-K-block scale sets (block mode)
 constexpr int kTmemCols = 512;                    // two accumulator buffers of 256 columns
 constexpr long long kWaitLimit = 1000000000LL;    // clock cycles before a wait gives up (~0.5 s)
@@ -65,24 +66,11 @@ struct Params {
     void* out;
     float* out_scale;         // stage 1 block mode: [n, ceil(I/128)]
     float* amax;              // stage 1 channel: [n]; tensor: [1]
+    const float* bias;        // [E, w_rows] fp32 added to the dequantised product, or nullptr
     const int* dest_to_src;   // stage 2 scatter map or nullptr
     const unsigned long long* row_dst;  // stage 2: address of each row's output row (may be peer memory), or nullptr
     int* status;              // host-mapped status word
-#ifdef DQ_TRACE
-    long long* trace;         // [3 roles][kTraceEvents][4] clock64 stamps of CTA 0 (diagnostic builds only)
-#endif
 };
-
-#ifdef DQ_TRACE
-constexpr int kTraceEvents = 96;
-#define DQ_STAMP(role, idx, slot)                                                        \
-    do {                                                                                \
-        if (blockIdx.x == 0 && p.trace != nullptr && (idx) < kTraceEvents)               \
-            p.trace[((role) * kTraceEvents + (idx)) * 8 + (slot)] = clock64();           \
-    } while (0)
-#else
-#define DQ_STAMP(role, idx, slot) do { } while (0)
-#endif
 
 struct SharedTail {
     uint64_t full[kMaxStages];
@@ -185,18 +173,47 @@ __device__ __forceinline__ void store_rows_staged(uint4* stage, const uint32_t (
     }
 }
 
-// Rounding / packing to the 16-bit output type of the unquantised path: bf16, or IEEE half (kF16) for the
-// FP16 instantiation of the reference's template (csrc/pybind11_register.h:104-151 with T = half).
-template <bool kF16>
+// One 32-column chunk of a tile row per lane: 32 values of 16 bits (packed[16]) or of 32 bits (packed[32], two
+// 64-byte halves). cols_left = columns of the matrix from the chunk's first column on.
+template <bool kWide, int kWords>
+__device__ __forceinline__ void store_chunk(uint4* stage, const uint32_t (&packed)[kWords], uint8_t* row_ptr,
+                                            int cols_left, int lane) {
+    if constexpr (!kWide) {
+        static_assert(kWords == 16, "32 values of 16 bits");
+        store_rows_staged(stage, packed, row_ptr, min(4, max(0, (cols_left + 7) / 8)), lane);
+    } else {
+        static_assert(kWords == 32, "32 values of 32 bits");
+        uint32_t half[16];
+#pragma unroll
+        for (int i = 0; i < 16; ++i) half[i] = packed[i];
+        store_rows_staged(stage, half, row_ptr, min(4, max(0, (cols_left + 3) / 4)), lane);
+#pragma unroll
+        for (int i = 0; i < 16; ++i) half[i] = packed[16 + i];
+        store_rows_staged(stage, half, row_ptr != nullptr ? row_ptr + 64 : nullptr,
+                          min(4, max(0, (cols_left - 16 + 3) / 4)), lane);
+    }
+}
+
+// Element type of the unquantised path: bf16, IEEE half or fp32 - the T = bf16 / half / float instantiations
+// of the reference's template (csrc/pybind11_register.h:104-151, csrc/moe_gemm_template.h:487-569). fp32
+// operands go through the tensor cores as TF32 (kind::tf32), as the reference's float instantiation does
+// on its mma.sync path; intermediates and outputs then stay fp32.
+enum Elem : int { kBf16 = 0, kHalf = 1, kF32 = 2 };
+
+// Rounding to the storage type of the intermediate and the output.
+template <int kElem>
 __device__ __forceinline__ float round16(float x) {
-    if constexpr (kF16)
+    if constexpr (kElem == kHalf)
         return __half2float(__float2half_rn(x));
+    else if constexpr (kElem == kF32)
+        return x;
     else
         return bf_round_cvt(x);
 }
-template <bool kF16>
+template <int kElem>
 __device__ __forceinline__ uint32_t pack16x2(float lo, float hi) {
-    if constexpr (kF16) {
+    static_assert(kElem != kF32, "fp32 outputs are not packed");
+    if constexpr (kElem == kHalf) {
         const __half2 h = __floats2half2_rn(lo, hi);
         return *reinterpret_cast<const uint32_t*>(&h);
     } else {
@@ -214,7 +231,7 @@ __device__ __forceinline__ void ffma2(float& a0, float& a1, uint32_t x0, uint32_
 
 // kBox = weight rows per TMA box (two boxes per stage, 2*kBox accumulator columns): 128 for
 // throughput, 64 when a launch would otherwise have fewer tiles than SMs (decode shapes).
-template <bool kFp8, int kMode, bool kGated, bool kPair, int kBox, bool kF16 = false>
+template <bool kFp8, int kMode, bool kGated, bool kPair, int kBox, int kElem = kBf16>
 __global__ void __launch_bounds__(kThreads, 1)
 moe_GemmGrouped_GemmUniversal_tcgen05(const __grid_constant__ CUtensorMap tma_a,
                                       const __grid_constant__ CUtensorMap tma_b, const Params p) {
@@ -224,9 +241,11 @@ moe_GemmGrouped_GemmUniversal_tcgen05(const __grid_constant__ CUtensorMap tma_a,
 
     const int warp = threadIdx.x >> 5;
     const int lane = threadIdx.x & 31;
-    constexpr int kBKElems = kFp8 ? kBKBytes : kBKBytes / 2;
+    constexpr int kBKElems = kFp8 ? kBKBytes : (kElem == kF32 ? kBKBytes / 4 : kBKBytes / 2);
+    constexpr int kKind = kFp8 ? 0 : (kElem == kF32 ? 2 : 1);  // kind::f8f6f4, kind::f16, kind::tf32
     static_assert(kBox == 128 || (kBox == 64 && !kPair && kMode != kBlock), "narrow tiles: single CTA, non-block modes");
-    static_assert(!kF16 || (!kFp8 && kMode == kNone), "fp16 operands: the unquantised path only");
+    static_assert(kElem == kBf16 || (!kFp8 && kMode == kNone), "fp16 / fp32 operands: the unquantised path only");
+    static_assert(kElem != kF32 || (!kPair && kBox == 128), "fp32 operands: single-CTA 256-column tiles only");
     constexpr int kN = 2 * kBox;                      // accumulator columns of a tile
     constexpr int kStageSz = kPair ? kStageBytesPair : kABytes + kN * kBKBytes;
     constexpr int kNumStages = (kStages * kStageBytes) / kStageSz;   // 4 (wide), 6 (pairs, narrow)
@@ -312,7 +331,6 @@ moe_GemmGrouped_GemmUniversal_tcgen05(const __grid_constant__ CUtensorMap tma_a,
                 for (int kb = 0; kb < kb_count; ++kb, ++it) {
                     const int s = it % kNumStages;
                     const uint32_t ph = (it / kNumStages) & 1u;
-                    DQ_STAMP(0, it, 0);
                     if (!ptx::mbar_wait(&st.empty[s], ph ^ 1u, abort_flag, kWaitLimit)) {
                         ok = false;
                         break;
@@ -333,7 +351,6 @@ moe_GemmGrouped_GemmUniversal_tcgen05(const __grid_constant__ CUtensorMap tma_a,
                         ptx::tma_load_2d(sb, &tma_b, k0, wrow0, &st.full[s]);
                         ptx::tma_load_2d(sb + kBox * kBKBytes, &tma_b, k0, wrow1, &st.full[s]);
                     }
-                    DQ_STAMP(0, it, 1);
                 }
             }
         }
@@ -341,14 +358,15 @@ moe_GemmGrouped_GemmUniversal_tcgen05(const __grid_constant__ CUtensorMap tma_a,
       } else if (warp == 1) {
         // ------------------------------------------------------------ MMA issuer
         if (lane == 0 && leader) {
-            // operand format code: e4m3 = 0 (kind::f8f6f4); f16 = 0, bf16 = 1 (kind::f16)
-            constexpr uint32_t idesc = ptx::make_idesc(kFp8 || kF16 ? 0u : 1u, kPair ? 2 * kBM : kBM, kN);
+            // operand format code: e4m3 = 0 (kind::f8f6f4); f16 = 0, bf16 = 1 (kind::f16); tf32 = 2 (kind::tf32)
+            constexpr uint32_t idesc =
+                ptx::make_idesc(kFp8 || kElem == kHalf ? 0u : (kElem == kF32 ? 2u : 1u), kPair ? 2 * kBM : kBM, kN);
             // issue one K step; in a pair the same call drives both CTAs' tensor cores
             auto mma_step = [&](uint32_t d_tmem, uint32_t a_addr, uint32_t b_addr, uint32_t accumulate) {
                 if constexpr (kPair)
-                    ptx::umma_pair<kFp8>(d_tmem, ptx::smem_desc_sw128(a_addr), ptx::smem_desc_sw128(b_addr), idesc, accumulate);
+                    ptx::umma_pair<kKind>(d_tmem, ptx::smem_desc_sw128(a_addr), ptx::smem_desc_sw128(b_addr), idesc, accumulate);
                 else
-                    ptx::umma<kFp8>(d_tmem, ptx::smem_desc_sw128(a_addr), ptx::smem_desc_sw128(b_addr), idesc, accumulate);
+                    ptx::umma<kKind>(d_tmem, ptx::smem_desc_sw128(a_addr), ptx::smem_desc_sw128(b_addr), idesc, accumulate);
             };
             // completion of everything issued so far -> one barrier (of both CTAs in a pair)
             auto commit = [&](uint64_t* bar) {
@@ -393,17 +411,14 @@ moe_GemmGrouped_GemmUniversal_tcgen05(const __grid_constant__ CUtensorMap tma_a,
                     for (int kb = 0; kb < kb_count; ++kb, ++it, ++acc_it) {
                         const uint32_t buf = acc_it & 1u;
                         const int s = it % kNumStages;
-                        DQ_STAMP(1, it, 0);
                         if (!ptx::mbar_wait(&st.tmem_empty[buf], ((acc_it >> 1) & 1u) ^ 1u, abort_flag, kWaitLimit)) {
                             ok = false;
                             break;
                         }
-                        DQ_STAMP(1, it, 1);
                         if (!ptx::mbar_wait(&st.full[s], (it / kNumStages) & 1u, abort_flag, kWaitLimit)) {
                             ok = false;
                             break;
                         }
-                        DQ_STAMP(1, it, 2);
                         ptx::tc_fence_after();
                         const uint32_t a_addr = ptx::smem_u32(smem + size_t(s) * kStageSz);
                         const uint32_t b_addr = a_addr + kABytes;
@@ -413,7 +428,6 @@ moe_GemmGrouped_GemmUniversal_tcgen05(const __grid_constant__ CUtensorMap tma_a,
                                      k != 0 ? 1u : 0u);
                         commit(&st.tmem_full[buf]);
                         commit(&st.empty[s]);
-                        DQ_STAMP(1, it, 3);
                     }
                 }
             }
@@ -491,11 +505,21 @@ moe_GemmGrouped_GemmUniversal_tcgen05(const __grid_constant__ CUtensorMap tma_a,
                 ptx::tc_fence_after();
                 const uint32_t t_buf = t_lane + buf * kUmmaN;
 
+                // Per-chunk column constants (channel-mode weight scales, bias) are staged once per warp in its
+                // store buffer and read back as broadcast 16-byte loads: floats [0,32) gate / plain scales,
+                // [32,64) value scales, [64,96) gate / plain bias, [96,128) value bias. The buffer is free
+                // until the staged store of the same chunk.
+                float* csw = reinterpret_cast<float*>(st.stage[warp - 4]);
+                [[maybe_unused]] const float4* cs4 = reinterpret_cast<const float4*>(st.stage[warp - 4]);
+                const bool has_bias = p.bias != nullptr;
+                const float* bias_e = has_bias ? p.bias + size_t(tl.e) * p.w_rows : nullptr;
+                float row_scale = 1.0f;
+                if constexpr (kMode == kTensor) row_scale = p.sa[0] * p.sb[tl.e];
+                if constexpr (kMode == kChannel) row_scale = p.sa[grow_ld];
+                constexpr int kOutBytes = kElem == kF32 ? 4 : 2;
+
                 if constexpr (kGated) {
                     // columns [h*kHalf, (h+1)*kHalf) of the gate group and of the value group
-                    float row_scale = 1.0f;
-                    if constexpr (kMode == kTensor) row_scale = p.sa[0] * p.sb[tl.e];
-                    if constexpr (kMode == kChannel) row_scale = p.sa[grow_ld];
                     float amax_local = 0.0f;
 #pragma unroll 1
                     for (int j = 0; j < kChunks; ++j) {
@@ -504,22 +528,24 @@ moe_GemmGrouped_GemmUniversal_tcgen05(const __grid_constant__ CUtensorMap tma_a,
                         ptx::tmem_ld32(t_buf + c0, g);
                         ptx::tmem_ld32(t_buf + kBox + c0, v);
                         const int col0 = tl.nt * kBox + c0;
-                        if constexpr (kMode == kChannel) {
-                            // this chunk's 32 gate and 32 value column scales, staged once per warp and read back
-                            // as broadcast 16-byte loads (the buffer is free until the staged store below)
-                            float* csw = reinterpret_cast<float*>(st.stage[warp - 4]);
+                        if (kMode == kChannel || has_bias) {
                             __syncwarp();
                             const int c = min(col0 + lane, I_or_H - 1);
-                            csw[lane] = p.sb[size_t(tl.e) * p.w_rows + c];
-                            csw[32 + lane] = p.sb[size_t(tl.e) * p.w_rows + I_or_H + c];
+                            if constexpr (kMode == kChannel) {
+                                csw[lane] = p.sb[size_t(tl.e) * p.w_rows + c];
+                                csw[32 + lane] = p.sb[size_t(tl.e) * p.w_rows + I_or_H + c];
+                            }
+                            if (has_bias) {
+                                csw[64 + lane] = bias_e[c];
+                                csw[96 + lane] = bias_e[I_or_H + c];
+                            }
                             __syncwarp();
                         }
                         ptx::tmem_wait_ld(g);
                         ptx::tmem_wait_ld(v);
-                        uint32_t packed[16];
+                        uint32_t packed[kElem == kF32 ? 32 : 16];
                         // This epilogue runs beside the next tile's MMAs; its roundings use the conversion
                         // instruction (one issue slot each), which measured faster here than bf_round.
-                        [[maybe_unused]] const float4* cs4 = reinterpret_cast<const float4*>(st.stage[warp - 4]);
 #pragma unroll
                         for (int i = 0; i < 32; i += 4) {
                             float sg[4] = {row_scale, row_scale, row_scale, row_scale};
@@ -529,28 +555,35 @@ moe_GemmGrouped_GemmUniversal_tcgen05(const __grid_constant__ CUtensorMap tma_a,
                                 sg[0] *= a.x, sg[1] *= a.y, sg[2] *= a.z, sg[3] *= a.w;
                                 sv[0] *= b.x, sv[1] *= b.y, sv[2] *= b.z, sv[3] *= b.w;
                             }
+                            float bg[4] = {0.0f, 0.0f, 0.0f, 0.0f}, bv[4] = {0.0f, 0.0f, 0.0f, 0.0f};
+                            if (has_bias) {
+                                const float4 a = cs4[16 + (i >> 2)], b = cs4[24 + (i >> 2)];
+                                bg[0] = a.x, bg[1] = a.y, bg[2] = a.z, bg[3] = a.w;
+                                bv[0] = b.x, bv[1] = b.y, bv[2] = b.z, bv[3] = b.w;
+                            }
                             float a4[4];
 #pragma unroll
                             for (int u = 0; u < 4; ++u) {
-                                const float gate = round16<kF16>(__uint_as_float(g[i + u]) * sg[u]);
-                                const float val = round16<kF16>(__uint_as_float(v[i + u]) * sv[u]);
-                                const float act = round16<kF16>(round16<kF16>(__fdividef(gate, 1.0f + __expf(-gate))) * val);
+                                const float gate = round16<kElem>(__uint_as_float(g[i + u]) * sg[u] + bg[u]);
+                                const float val = round16<kElem>(__uint_as_float(v[i + u]) * sv[u] + bv[u]);
+                                const float act = round16<kElem>(round16<kElem>(__fdividef(gate, 1.0f + __expf(-gate))) * val);
                                 a4[u] = act;
                                 if (col0 + i + u < I_or_H) amax_local = fmaxf(amax_local, fabsf(act));
                             }
-                            if constexpr (kF16) {
-                                packed[i >> 1] = pack16x2<true>(a4[0], a4[1]);
-                                packed[(i >> 1) + 1] = pack16x2<true>(a4[2], a4[3]);
+                            if constexpr (kElem == kF32) {
+#pragma unroll
+                                for (int u = 0; u < 4; ++u) packed[i + u] = __float_as_uint(a4[u]);
+                            } else if constexpr (kElem == kHalf) {
+                                packed[i >> 1] = pack16x2<kHalf>(a4[0], a4[1]);
+                                packed[(i >> 1) + 1] = pack16x2<kHalf>(a4[2], a4[3]);
                             } else {
                                 packed[i >> 1] = pack_bf16x2_exact(a4[0], a4[1]);  // act is already rounded to bf16
                                 packed[(i >> 1) + 1] = pack_bf16x2_exact(a4[2], a4[3]);
                             }
                         }
-                        store_rows_staged(st.stage[warp - 4], packed,
-                                          row_ok ? reinterpret_cast<uint8_t*>(reinterpret_cast<__nv_bfloat16*>(p.out) +
-                                                                              size_t(grow) * I_or_H + col0)
-                                                 : nullptr,
-                                          min(4, max(0, (I_or_H - col0 + 7) / 8)), lane);
+                        uint8_t* optr = row_ok ? static_cast<uint8_t*>(p.out) + (size_t(grow) * I_or_H + col0) * kOutBytes
+                                               : nullptr;
+                        store_chunk<kElem == kF32>(st.stage[warp - 4], packed, optr, I_or_H - col0, lane);
                     }
                     if constexpr (kMode == kChannel) {
                         if (row_ok) atomic_max_nonneg(p.amax + grow, amax_local);
@@ -562,14 +595,11 @@ moe_GemmGrouped_GemmUniversal_tcgen05(const __grid_constant__ CUtensorMap tma_a,
                     }
                 } else {
                     // stage 2: this warpgroup's half of each of the two kBox-column groups
-                    float row_scale = 1.0f;
-                    if constexpr (kMode == kTensor) row_scale = p.sa[0] * p.sb[tl.e];
-                    if constexpr (kMode == kChannel) row_scale = p.sa[grow_ld];
                     int orow_idx = grow;
                     if (row_ok && p.dest_to_src != nullptr) orow_idx = p.dest_to_src[grow];
-                    __nv_bfloat16* orow = reinterpret_cast<__nv_bfloat16*>(p.out) + size_t(orow_idx) * I_or_H;
+                    uint8_t* orow = static_cast<uint8_t*>(p.out) + size_t(orow_idx) * I_or_H * kOutBytes;
                     if (p.row_dst != nullptr) {  // rows go to explicit addresses (expert parallel: the home rank's output)
-                        orow = row_ok ? reinterpret_cast<__nv_bfloat16*>(p.row_dst[grow]) : nullptr;
+                        orow = row_ok ? reinterpret_cast<uint8_t*>(p.row_dst[grow]) : nullptr;
                         orow_idx = orow != nullptr ? 0 : -1;
                     }
 #pragma unroll 1
@@ -578,15 +608,15 @@ moe_GemmGrouped_GemmUniversal_tcgen05(const __grid_constant__ CUtensorMap tma_a,
                         const int tc = (c / kChunks) * kBox + h * kHalf + (c % kChunks) * 32;
                         ptx::tmem_ld32(t_buf + tc, r);
                         const int col0 = tl.nt * kN + tc;
-                        if constexpr (kMode == kChannel) {  // column scales of the chunk, as in stage 1
-                            float* csw = reinterpret_cast<float*>(st.stage[warp - 4]);
+                        if (kMode == kChannel || has_bias) {  // column constants of the chunk, as in stage 1
                             __syncwarp();
-                            csw[lane] = p.sb[size_t(tl.e) * p.w_rows + min(col0 + lane, I_or_H - 1)];
+                            const int cc = min(col0 + lane, I_or_H - 1);
+                            if constexpr (kMode == kChannel) csw[lane] = p.sb[size_t(tl.e) * p.w_rows + cc];
+                            if (has_bias) csw[64 + lane] = bias_e[cc];
                             __syncwarp();
                         }
                         ptx::tmem_wait_ld(r);
-                        uint32_t packed[16];
-                        [[maybe_unused]] const float4* cs4 = reinterpret_cast<const float4*>(st.stage[warp - 4]);
+                        uint32_t packed[kElem == kF32 ? 32 : 16];
 #pragma unroll
                         for (int i = 0; i < 32; i += 4) {
                             float sc[4] = {row_scale, row_scale, row_scale, row_scale};
@@ -594,13 +624,25 @@ moe_GemmGrouped_GemmUniversal_tcgen05(const __grid_constant__ CUtensorMap tma_a,
                                 const float4 a = cs4[i >> 2];
                                 sc[0] *= a.x, sc[1] *= a.y, sc[2] *= a.z, sc[3] *= a.w;
                             }
-                            packed[i >> 1] = pack16x2<kF16>(__uint_as_float(r[i]) * sc[0], __uint_as_float(r[i + 1]) * sc[1]);
-                            packed[(i >> 1) + 1] =
-                                pack16x2<kF16>(__uint_as_float(r[i + 2]) * sc[2], __uint_as_float(r[i + 3]) * sc[3]);
+                            float bb[4] = {0.0f, 0.0f, 0.0f, 0.0f};
+                            if (has_bias) {
+                                const float4 a = cs4[16 + (i >> 2)];
+                                bb[0] = a.x, bb[1] = a.y, bb[2] = a.z, bb[3] = a.w;
+                            }
+                            float o4[4];
+#pragma unroll
+                            for (int u = 0; u < 4; ++u) o4[u] = __uint_as_float(r[i + u]) * sc[u] + bb[u];
+                            if constexpr (kElem == kF32) {
+#pragma unroll
+                                for (int u = 0; u < 4; ++u) packed[i + u] = __float_as_uint(o4[u]);
+                            } else {
+                                packed[i >> 1] = pack16x2<kElem>(o4[0], o4[1]);
+                                packed[(i >> 1) + 1] = pack16x2<kElem>(o4[2], o4[3]);
+                            }
                         }
-                        store_rows_staged(st.stage[warp - 4], packed,
-                                          row_ok && orow_idx >= 0 ? reinterpret_cast<uint8_t*>(orow + col0) : nullptr,
-                                          min(4, max(0, (I_or_H - col0 + 7) / 8)), lane);
+                        store_chunk<kElem == kF32>(st.stage[warp - 4], packed,
+                                                   row_ok && orow_idx >= 0 ? orow + size_t(col0) * kOutBytes : nullptr,
+                                                   I_or_H - col0, lane);
                     }
                 }
                 ptx::tc_fence_before();
@@ -609,7 +651,6 @@ moe_GemmGrouped_GemmUniversal_tcgen05(const __grid_constant__ CUtensorMap tma_a,
             } else {
                 // ---------------------------------------------------- block-scaled accumulation
                 // acc[c*32 + i]: chunk c of this thread's four 32-column chunks.
-                if (lane == 0) DQ_STAMP(warp - 2, acc_it, 5);
                 float acc[128];
 #pragma unroll
                 for (int i = 0; i < 128; ++i) acc[i] = 0.0f;
@@ -656,30 +697,24 @@ moe_GemmGrouped_GemmUniversal_tcgen05(const __grid_constant__ CUtensorMap tma_a,
                         const float s1h = kOneScale ? 0.0f : a_s * st.sc_b[slot][2];
                         __syncwarp();
                         if (lane == 0) ptx::mbar_arrive(&st.sc_empty[slot]);
-                        if (lane == 0 && kb == 0) DQ_STAMP(warp - 2, acc_it, 6);
 
                         const uint32_t buf = acc_it & 1u;
                         if (!ptx::mbar_wait(&st.tmem_full[buf], (acc_it >> 1) & 1u, abort_flag, kWaitLimit)) return false;
-                        if (lane == 0) DQ_STAMP(warp - 2, acc_it, 0);
                         ptx::tc_fence_after();
                         const uint32_t t_buf = t_lane + buf * kUmmaN;
                         ptx::tmem_ld32(t_buf + tcol(0), r0);
                         ptx::tmem_ld32(t_buf + tcol(1), r1);
-                        if (lane == 0) DQ_STAMP(warp - 2, acc_it, 1);
                         ptx::tmem_wait_ld2(r0, r1);
-                        if (lane == 0) DQ_STAMP(warp - 2, acc_it, 2);
                         fma_chunk(0, r0, s0, s1l, s1h);
                         ptx::tmem_ld32(t_buf + tcol(2), r0);
                         fma_chunk(1, r1, s0, s1l, s1h);
                         ptx::tmem_ld32(t_buf + tcol(3), r1);
                         ptx::tmem_wait_ld2(r0, r1);
-                        if (lane == 0) DQ_STAMP(warp - 2, acc_it, 3);
                         ptx::tc_fence_before();
                         __syncwarp();
                         if (lane == 0) release_tmem(buf);
                         fma_chunk(2, r0, s0, s1l, s1h);
                         fma_chunk(3, r1, s0, s1l, s1h);
-                        if (lane == 0) DQ_STAMP(warp - 2, acc_it, 4);
                     }
                     return true;
                 };
@@ -688,6 +723,15 @@ moe_GemmGrouped_GemmUniversal_tcgen05(const __grid_constant__ CUtensorMap tma_a,
                 else
                     ok = k_loop(std::false_type{});
                 if (!ok) break;
+                if (p.bias != nullptr) {  // the same address in every lane: broadcast loads
+                    const float* bias_e = p.bias + size_t(tl.e) * p.w_rows;
+#pragma unroll
+                    for (int i = 0; i < 128; ++i) {
+                        const int cg = kGated ? (i >> 6) * I_or_H + tl.nt * kBoxRows + h * 64 + (i & 63)
+                                              : tl.nt * kUmmaN + tcol(i >> 5) + (i & 31);
+                        acc[i] += __ldg(bias_e + min(cg, p.w_rows - 1));
+                    }
+                }
 
                 if constexpr (kGated) {
                     // act columns nt*128 + h*64 + [0, 64): gate = acc[0..63], value = acc[64..127]
@@ -721,7 +765,6 @@ moe_GemmGrouped_GemmUniversal_tcgen05(const __grid_constant__ CUtensorMap tma_a,
                         swiglu(std::true_type{});
                     else
                         swiglu(std::false_type{});
-                    if (lane == 0) DQ_STAMP(warp - 2, acc_it - 1, 5);
                     // the 1x128 group spans both halves: exchange the partial amax through shared memory
                     st.amax[tile_it & 1u][h][r_in_tile] = amax_local;
                     __syncwarp();
@@ -731,7 +774,6 @@ moe_GemmGrouped_GemmUniversal_tcgen05(const __grid_constant__ CUtensorMap tma_a,
                         break;
                     }
                     epi_phase ^= 1u;
-                    if (lane == 0) DQ_STAMP(warp - 2, acc_it - 1, 6);
                     const float amax = fmaxf(amax_local, st.amax[tile_it & 1u][h ^ 1][r_in_tile]);
                     const float sf = scale_from_amax(amax);
                     const float inv = inv_scale(sf);
@@ -746,7 +788,6 @@ moe_GemmGrouped_GemmUniversal_tcgen05(const __grid_constant__ CUtensorMap tma_a,
                                           row_ok ? reinterpret_cast<uint8_t*>(p.out) + size_t(grow) * I_or_H + col0 : nullptr,
                                           min(4, max(0, (I_or_H - col0 + 15) / 16)), lane);
                         if (row_ok && h == 0) p.out_scale[size_t(grow) * ((I_or_H + 127) / 128) + tl.nt] = sf;
-                        if (lane == 0) DQ_STAMP(warp - 2, acc_it - 1, 7);
                     }
                 } else {
                     int orow_idx = grow;
@@ -794,10 +835,6 @@ moe_GemmGrouped_GemmUniversal_tcgen05(const __grid_constant__ CUtensorMap tma_a,
 
 // ---------------------------------------------------------------- host side
 
-#ifdef DQ_TRACE
-static long long* g_trace = nullptr;
-#endif
-
 typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
                                   const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
                                   CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
@@ -814,17 +851,17 @@ static EncodeTiledFn encode_fn() {
     return fn;
 }
 
-// 2-D row-major matrix [rows, cols] of 1- or 2-byte elements, box = 128 bytes x 128 rows, 128B swizzle.
-static int make_map(CUtensorMap* map, const void* base, bool fp8, uint64_t rows, uint64_t cols, int box_rows) {
+// 2-D row-major matrix [rows, cols] of 1-, 2- or 4-byte elements, box = 128 bytes x box_rows rows, 128B swizzle.
+static int make_map(CUtensorMap* map, const void* base, int esz, uint64_t rows, uint64_t cols, int box_rows) {
     EncodeTiledFn fn = encode_fn();
     if (fn == nullptr) return fail(DQMOE_ERR_CUDA, __FILE__, __LINE__, "cuTensorMapEncodeTiled", "driver entry point not found");
-    const uint64_t esz = fp8 ? 1 : 2;
     cuuint64_t gdim[2] = {cols, rows};
-    cuuint64_t gstride[1] = {cols * esz};
+    cuuint64_t gstride[1] = {cols * uint64_t(esz)};
     cuuint32_t box[2] = {static_cast<cuuint32_t>(kBKBytes / esz), static_cast<cuuint32_t>(box_rows)};
     cuuint32_t estr[2] = {1, 1};
-    CUresult r = fn(map, fp8 ? CU_TENSOR_MAP_DATA_TYPE_UINT8 : CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2,
-                    const_cast<void*>(base), gdim, gstride, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+    const CUtensorMapDataType dt = esz == 1 ? CU_TENSOR_MAP_DATA_TYPE_UINT8
+                                   : esz == 2 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT32;
+    CUresult r = fn(map, dt, 2, const_cast<void*>(base), gdim, gstride, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
                     CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
     if (r != CUDA_SUCCESS)
         return fail(DQMOE_ERR_CUDA, __FILE__, __LINE__, "cuTensorMapEncodeTiled", "CUresult %d (rows %llu cols %llu)",
@@ -832,17 +869,21 @@ static int make_map(CUtensorMap* map, const void* base, bool fp8, uint64_t rows,
     return DQMOE_OK;
 }
 
-template <bool kFp8, int kMode, bool kGated, bool kPair, int kBox, bool kF16 = false>
+template <bool kFp8, int kMode, bool kGated, bool kPair, int kBox, int kElem = kBf16>
 static int launch(const CUtensorMap& ma, const CUtensorMap& mb, const Params& p, cudaStream_t stream) {
-    auto kern = moe_GemmGrouped_GemmUniversal_tcgen05<kFp8, kMode, kGated, kPair, kBox, kF16>;
-    static bool configured = false;  // per instantiation
-    static int configured_dev = -1;
+    auto kern = moe_GemmGrouped_GemmUniversal_tcgen05<kFp8, kMode, kGated, kPair, kBox, kElem>;
+    // the shared-memory opt-in is per function and per device
+    static std::mutex mu;
+    static bool configured[kMaxDevices] = {};
     int dev = 0;
     DQ_CUDA(cudaGetDevice(&dev));
-    if (!configured || configured_dev != dev) {
-        DQ_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, int(kSmemBytes)));
-        configured = true;
-        configured_dev = dev;
+    DQ_CHECK(dev >= 0 && dev < kMaxDevices);
+    {
+        std::lock_guard<std::mutex> lk(mu);
+        if (!configured[dev]) {
+            DQ_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, int(kSmemBytes)));
+            configured[dev] = true;
+        }
     }
     if constexpr (kPair) {
         // clusters of two CTAs on neighbouring SMs; an even grid
@@ -867,33 +908,29 @@ static int launch(const CUtensorMap& ma, const CUtensorMap& mb, const Params& p,
 }
 
 // CTA pairs halve the weight bytes each SM stages per flop; they pay off once experts have
-// several row tiles. DQMOE_GEMM_PAIR=0/1 overrides the choice (for measurements).
+// several row tiles.
 static bool use_pairs(int n, int E, int quant_mode) {
-    static int forced = -2;
-    if (forced == -2) {
-        const char* env = getenv("DQMOE_GEMM_PAIR");
-        forced = env == nullptr ? -1 : (env[0] == '0' ? 0 : 1);
-    }
-    if (forced >= 0) return forced == 1;
     // Block mode hands a TMEM buffer back every K block and is bound by that round trip, not by the
     // shared-memory traffic a pair saves (measured: +1 % with pairs, while ragged experts waste more
     // rows in 256-row tiles), so it stays on single CTAs.
     return quant_mode != DQMOE_QUANT_FP8_BLOCK && n / E >= 512;
 }
 
+// elem: element type of the unquantised path (kBf16 / kHalf / kF32); bias: [E, gated ? 2N : N] fp32 or nullptr.
 int grouped_gemm(const void* a, const float* a_scale, const void* w, const float* w_scale, const int* offsets,
                  const int* mtile_prefix, int n, int N, int K, int E, int quant_mode, int gated, void* out,
                  float* out_scale, float* amax, const int* dest_to_src, const void* row_dst, cudaStream_t stream,
-                 bool f16) {
-    DQ_CHECK(!f16 || quant_mode == DQMOE_QUANT_NONE);
+                 int elem, const float* bias) {
+    DQ_CHECK(elem == kBf16 || ((elem == kHalf || elem == kF32) && quant_mode == DQMOE_QUANT_NONE));
     DQ_CHECK(quant_mode == DQMOE_QUANT_NONE || quant_mode == DQMOE_QUANT_FP8_TENSOR ||
              quant_mode == DQMOE_QUANT_FP8_CHANNEL || quant_mode == DQMOE_QUANT_FP8_BLOCK);
     DQ_CHECK(n >= 0 && N > 0 && K > 0 && E > 0 && E <= kMaxExperts);
     if (n == 0) return DQMOE_OK;
     const bool fp8 = quant_mode != DQMOE_QUANT_NONE;
-    const int esz = fp8 ? 1 : 2;
+    const int esz = fp8 ? 1 : (elem == kF32 ? 4 : 2);
     DQ_CHECK_FMT((size_t(K) * esz) % 16 == 0, "K=%d: rows must be a multiple of 16 bytes", K);
-    DQ_CHECK_FMT(N % (gated && quant_mode == DQMOE_QUANT_FP8_BLOCK ? 16 : 8) == 0, "N=%d: output rows must be 16-byte vectors", N);
+    DQ_CHECK_FMT(N % (gated && quant_mode == DQMOE_QUANT_FP8_BLOCK ? 16 : (elem == kF32 ? 4 : 8)) == 0,
+                 "N=%d: output rows must be 16-byte vectors", N);
     DQ_CHECK(is_aligned(a, 16) && is_aligned(w, 16) && is_aligned(out, 16) && is_aligned(row_dst, 8));
     DQ_CHECK(a != nullptr && w != nullptr && (out != nullptr || row_dst != nullptr) && offsets != nullptr && mtile_prefix != nullptr);
     DQ_CHECK(row_dst == nullptr || !gated);
@@ -903,21 +940,13 @@ int grouped_gemm(const void* a, const float* a_scale, const void* w, const float
 
     // Tile width: 256 accumulator columns, or 128 when the launch would leave many SMs without a tile.
     // The row-tile count is known only on the device; ceil(n/128) + min(E, n) - 1 bounds it.
-    const bool pair = use_pairs(n, E, quant_mode);
+    const bool pair = elem != kF32 && use_pairs(n, E, quant_mode);
     const int mtiles_max = ceil_div(n, kBM) + (E < n ? E : n) - 1;
     const int wide_tiles = mtiles_max * (gated ? ceil_div(N, kBoxRows) : ceil_div(N, kUmmaN));
-    // (DQMOE_GEMM_BOX=64/128 overrides the choice for measurements.)
-    static int forced_box = -1;
-    if (forced_box == -1) {
-        const char* env = getenv("DQMOE_GEMM_BOX");
-        forced_box = env == nullptr ? 0 : atoi(env);
-    }
     // measured on decode shapes: 128-column tiles win when 256-column tiles would fill at most half of
     // the SMs, or when there are at most two row tiles (one or two tokens); otherwise 256 columns win
-    bool narrow = quant_mode != DQMOE_QUANT_FP8_BLOCK && !pair &&
-                  (2 * wide_tiles <= sm_count() || (mtiles_max <= 2 && wide_tiles < 2 * sm_count()));
-    if (forced_box == 64 && quant_mode != DQMOE_QUANT_FP8_BLOCK && !pair) narrow = true;
-    if (forced_box == 128) narrow = false;
+    const bool narrow = quant_mode != DQMOE_QUANT_FP8_BLOCK && !pair && elem != kF32 &&
+                        (2 * wide_tiles <= sm_count() || (mtiles_max <= 2 && wide_tiles < 2 * sm_count()));
     const int box = narrow ? 64 : kBoxRows;
 
     Params p;
@@ -937,18 +966,16 @@ int grouped_gemm(const void* a, const float* a_scale, const void* w, const float
     p.out = out;
     p.out_scale = out_scale;
     p.amax = amax;
+    p.bias = bias;
     p.dest_to_src = dest_to_src;
     p.row_dst = static_cast<const unsigned long long*>(row_dst);
     p.status = device_status_word();
-#ifdef DQ_TRACE
-    p.trace = g_trace;
-#endif
     if (p.status == nullptr) return DQMOE_ERR_CUDA;
 
     CUtensorMap ma, mb;
-    int rc = make_map(&ma, a, fp8, uint64_t(n), uint64_t(K), kBM);
+    int rc = make_map(&ma, a, esz, uint64_t(n), uint64_t(K), kBM);
     if (rc != DQMOE_OK) return rc;
-    rc = make_map(&mb, w, fp8, uint64_t(E) * p.w_rows, uint64_t(K), box);
+    rc = make_map(&mb, w, esz, uint64_t(E) * p.w_rows, uint64_t(K), box);
     if (rc != DQMOE_OK) return rc;
 
 #define DQ_GEMM_LAUNCH(FP8, MODE, PAIR, BOX)                                                 \
@@ -957,11 +984,14 @@ int grouped_gemm(const void* a, const float* a_scale, const void* w, const float
     return pair ? DQ_GEMM_LAUNCH(FP8, MODE, true, 128)                                        \
                 : (narrow ? DQ_GEMM_LAUNCH(FP8, MODE, false, 64) : DQ_GEMM_LAUNCH(FP8, MODE, false, 128))
 #define DQ_GEMM_LAUNCH_F16(PAIR, BOX)                                                          \
-    (gated ? launch<false, kNone, true, PAIR, BOX, true>(ma, mb, p, stream)                    \
-           : launch<false, kNone, false, PAIR, BOX, true>(ma, mb, p, stream))
-    if (f16)
+    (gated ? launch<false, kNone, true, PAIR, BOX, kHalf>(ma, mb, p, stream)                   \
+           : launch<false, kNone, false, PAIR, BOX, kHalf>(ma, mb, p, stream))
+    if (elem == kHalf)
         return pair ? DQ_GEMM_LAUNCH_F16(true, 128) : (narrow ? DQ_GEMM_LAUNCH_F16(false, 64) : DQ_GEMM_LAUNCH_F16(false, 128));
 #undef DQ_GEMM_LAUNCH_F16
+    if (elem == kF32)
+        return gated ? launch<false, kNone, true, false, 128, kF32>(ma, mb, p, stream)
+                     : launch<false, kNone, false, false, 128, kF32>(ma, mb, p, stream);
     switch (quant_mode) {
         case DQMOE_QUANT_NONE: DQ_GEMM_CASE(false, kNone);
         case DQMOE_QUANT_FP8_TENSOR: DQ_GEMM_CASE(true, kTensor);
@@ -975,21 +1005,19 @@ int grouped_gemm(const void* a, const float* a_scale, const void* w, const float
 }  // namespace gemm
 }  // namespace dq
 
-#ifdef DQ_TRACE
-extern "C" void dqmoe_debug_set_trace(long long* p) { dq::gemm::g_trace = p; }
-#endif
-
 extern "C" int dqmoe_grouped_gemm(const void* a, const float* a_scale, const void* w, const float* w_scale,
                                   const int32_t* offsets, const int32_t* mtile_prefix, int n, int N, int K, int E,
                                   int quant_mode, int gated, void* out, float* out_scale, float* amax,
                                   const int32_t* dest_to_src, dqmoe_stream_t stream) {
     return dq::gemm::grouped_gemm(a, a_scale, w, w_scale, offsets, mtile_prefix, n, N, K, E, quant_mode, gated, out,
-                                  out_scale, amax, dest_to_src, nullptr, static_cast<cudaStream_t>(stream), false);
+                                  out_scale, amax, dest_to_src, nullptr, static_cast<cudaStream_t>(stream),
+                                  dq::gemm::kBf16, nullptr);
 }
 
 extern "C" int dqmoe_grouped_gemm_rows(const void* a, const float* a_scale, const void* w, const float* w_scale,
                                        const int32_t* offsets, const int32_t* mtile_prefix, int n, int N, int K, int E,
                                        int quant_mode, const void* row_dst, dqmoe_stream_t stream) {
     return dq::gemm::grouped_gemm(a, a_scale, w, w_scale, offsets, mtile_prefix, n, N, K, E, quant_mode, 0, nullptr,
-                                  nullptr, nullptr, nullptr, row_dst, static_cast<cudaStream_t>(stream), false);
+                                  nullptr, nullptr, nullptr, row_dst, static_cast<cudaStream_t>(stream), dq::gemm::kBf16,
+                                  nullptr);
 }

@@ -20,7 +20,8 @@ namespace gemm {
 int grouped_gemm(const void* a, const float* a_scale, const void* w, const float* w_scale, const int* offsets,
                  const int* mtile_prefix, int n, int N, int K, int E, int quant_mode, int gated, void* out,
                  float* out_scale, float* amax, const int* dest_to_src, const void* row_dst, cudaStream_t stream,
-                 bool f16 = false);
+                 int elem = 0, const float* bias = nullptr);
+enum Elem : int { kBf16 = 0, kHalf = 1, kF32 = 2 };  // element type of the unquantised path
 }  // namespace gemm
 
 namespace decode {
@@ -31,8 +32,8 @@ int forward(const void* a, const float* a_scale, const void* b, const float* b_s
 
 namespace layer {
 
-constexpr size_t kAlign = 256;
-constexpr int kDecodeRows = 8;  // up to this many expanded rows the GEMV path of decode.cu is used (bf16, per-tensor FP8)  // CUDA_MEM_ALIGN of the reference (csrc/util.h:54-59)
+constexpr size_t kAlign = 256;  // CUDA_MEM_ALIGN of the reference (csrc/util.h:54-59)
+constexpr int kDecodeRows = 8;  // up to this many expanded rows the GEMV path of decode.cu is used (bf16, per-tensor FP8)
 
 struct Layout {
     size_t offsets, counts, mtile_prefix, sort_ws, dest_to_src, perm_a, perm_a_scale, act, act_scale, act_bf16, amax;
@@ -46,10 +47,10 @@ static bool valid_mode(int q) {
            q == DQMOE_QUANT_FP8_BLOCK;
 }
 
-static Layout make_layout(int T, int H, int I, int E, int k, int quant_mode) {
+static Layout make_layout(int T, int H, int I, int E, int k, int quant_mode, int elem = gemm::kBf16) {
     Layout L{};
     const size_t n = size_t(T) * k;
-    const size_t esz = quant_mode == DQMOE_QUANT_NONE ? 2 : 1;
+    const size_t esz = quant_mode != DQMOE_QUANT_NONE ? 1 : (elem == gemm::kF32 ? 4 : 2);
     size_t off = 0;
     auto add = [&](size_t bytes) {
         const size_t at = off;
@@ -109,11 +110,12 @@ void* dqmoe_moe_workspace_ptr(void* workspace, int which, int T, int H, int I, i
     }
 }
 
-// f16: the operands and the output are IEEE half instead of bf16 (quant_mode NONE only)
+// elem: the operands and the output are bf16, IEEE half or fp32 (the last two with quant_mode NONE only);
+// bias1 [E, 2I] / bias2 [E, H]: fp32 biases of fc1 / fc2 added to the dequantised products, or nullptr.
 static int moe_forward_impl(const void* a, const float* a_scale, const void* b, const float* b_scale, const void* b1,
                             const float* b1_scale, void* d, const int32_t* m_indices, void* workspace,
-                            size_t workspace_bytes, int T, int H, int I, int E, int k, int quant_mode, bool f16,
-                            cudaStream_t stream) {
+                            size_t workspace_bytes, int T, int H, int I, int E, int k, int quant_mode, int elem,
+                            const float* bias1, const float* bias2, cudaStream_t stream) {
     DQ_CHECK(T >= 0 && H > 0 && I > 0 && E > 0 && k > 0);
     DQ_CHECK_FMT(layer::valid_mode(quant_mode), "quant_mode_value=%d is not one of 0, 256, 512, 1024", quant_mode);
     if (T == 0) return DQMOE_OK;  // as csrc/pybind11_register.h:125-126
@@ -122,12 +124,13 @@ static int moe_forward_impl(const void* a, const float* a_scale, const void* b, 
                  workspace);
     const bool fp8 = quant_mode != DQMOE_QUANT_NONE;
     if (fp8) DQ_CHECK(a_scale != nullptr && b_scale != nullptr && b1_scale != nullptr);
-    const size_t esz = fp8 ? 1 : 2;
+    DQ_CHECK(elem == gemm::kBf16 || !fp8);
+    const size_t esz = fp8 ? 1 : (elem == gemm::kF32 ? 4 : 2);
     DQ_CHECK_FMT((H * esz) % 16 == 0 && (I * esz) % 16 == 0,
                  "hidden_size=%d and inter_size=%d rows must be multiples of 16 bytes", H, I);
     DQ_CHECK(int64_t(T) * k < (int64_t(1) << 31));
     const int n = T * k;
-    const layer::Layout L = layer::make_layout(T, H, I, E, k, quant_mode);
+    const layer::Layout L = layer::make_layout(T, H, I, E, k, quant_mode, elem);
     if (workspace_bytes != 0 && workspace_bytes < L.total)
         return fail(DQMOE_ERR_WORKSPACE, __FILE__, __LINE__, "workspace_bytes >= dqmoe_moe_workspace_bytes(...)",
                     "workspace has %zu bytes, the layer needs %zu", workspace_bytes, L.total);
@@ -144,7 +147,8 @@ static int moe_forward_impl(const void* a, const float* a_scale, const void* b, 
     void* act_bf16 = ws + L.act_bf16;
     float* amax = reinterpret_cast<float*>(ws + L.amax);
 
-    if (!f16 && n <= layer::kDecodeRows && (quant_mode == DQMOE_QUANT_NONE || quant_mode == DQMOE_QUANT_FP8_TENSOR) &&
+    if (elem == gemm::kBf16 && bias1 == nullptr && bias2 == nullptr && n <= layer::kDecodeRows &&
+        (quant_mode == DQMOE_QUANT_NONE || quant_mode == DQMOE_QUANT_FP8_TENSOR) &&
         size_t(H > I ? H : I) * sizeof(float) <= 200 * 1024)
         return decode::forward(a, a_scale, b, b_scale, b1, b1_scale, d, m_indices, fp8 ? act_bf16 : act, amax, T, H, I,
                                E, k, fp8, stream);
@@ -164,7 +168,7 @@ static int moe_forward_impl(const void* a, const float* a_scale, const void* b, 
         DQ_CUDA(cudaMemsetAsync(amax, 0, amax_bytes, stream));
     }
     rc = gemm::grouped_gemm(perm_a, sa1, b, b_scale, offsets, mtile_prefix, n, I, H, E, quant_mode, 1,
-                            two_pass ? act_bf16 : act, act_scale, amax, nullptr, nullptr, stream, f16);
+                            two_pass ? act_bf16 : act, act_scale, amax, nullptr, nullptr, stream, elem, bias1);
     if (rc != DQMOE_OK) return rc;
     if (two_pass) {
         rc = dqmoe_requant_from_amax(act_bf16, n, I, amax, quant_mode == DQMOE_QUANT_FP8_CHANNEL ? 1 : 0, act,
@@ -172,7 +176,7 @@ static int moe_forward_impl(const void* a, const float* a_scale, const void* b, 
         if (rc != DQMOE_OK) return rc;
     }
     rc = gemm::grouped_gemm(act, act_scale, b1, b1_scale, offsets, mtile_prefix, n, H, I, E, quant_mode, 0, d, nullptr,
-                            nullptr, dest_to_src, nullptr, stream, f16);
+                            nullptr, dest_to_src, nullptr, stream, elem, bias2);
     return rc;
 }
 
@@ -182,14 +186,41 @@ int dqmoe_moe_forward(const void* a, const float* a_scale, const void* b, const 
                       dqmoe_stream_t stream) {
     (void) fused;
     return moe_forward_impl(a, a_scale, b, b_scale, b1, b1_scale, d, m_indices, workspace, workspace_bytes, T, H, I, E, k,
-                            quant_mode, false, static_cast<cudaStream_t>(stream));
+                            quant_mode, gemm::kBf16, nullptr, nullptr, static_cast<cudaStream_t>(stream));
+}
+
+int dqmoe_moe_forward_bias(const void* a, const float* a_scale, const void* b, const float* b_scale, const void* b1,
+                           const float* b1_scale, const float* bias1, const float* bias2, void* d,
+                           const int32_t* m_indices, void* workspace, size_t workspace_bytes, int T, int H, int I, int E,
+                           int k, int quant_mode, dqmoe_stream_t stream) {
+    return moe_forward_impl(a, a_scale, b, b_scale, b1, b1_scale, d, m_indices, workspace, workspace_bytes, T, H, I, E, k,
+                            quant_mode, gemm::kBf16, bias1, bias2, static_cast<cudaStream_t>(stream));
 }
 
 int dqmoe_moe_forward_f16(const void* a, const void* b, const void* b1, void* d, const int32_t* m_indices,
                           void* workspace, size_t workspace_bytes, int T, int H, int I, int E, int k,
                           dqmoe_stream_t stream) {
     return moe_forward_impl(a, nullptr, b, nullptr, b1, nullptr, d, m_indices, workspace, workspace_bytes, T, H, I, E, k,
-                            DQMOE_QUANT_NONE, true, static_cast<cudaStream_t>(stream));
+                            DQMOE_QUANT_NONE, gemm::kHalf, nullptr, nullptr, static_cast<cudaStream_t>(stream));
+}
+
+size_t dqmoe_moe_workspace_bytes_f32(int T, int H, int I, int E, int k) {
+    if (T < 0 || H <= 0 || I <= 0 || E <= 0 || k <= 0) return 0;
+    return layer::make_layout(T, H, I, E, k, DQMOE_QUANT_NONE, gemm::kF32).total;
+}
+
+int dqmoe_moe_forward_f32(const void* a, const void* b, const void* b1, const float* bias1, const float* bias2, void* d,
+                          const int32_t* m_indices, void* workspace, size_t workspace_bytes, int T, int H, int I, int E,
+                          int k, dqmoe_stream_t stream) {
+    return moe_forward_impl(a, nullptr, b, nullptr, b1, nullptr, d, m_indices, workspace, workspace_bytes, T, H, I, E, k,
+                            DQMOE_QUANT_NONE, gemm::kF32, bias1, bias2, static_cast<cudaStream_t>(stream));
+}
+
+int dqmoe_moe_forward_f16_bias(const void* a, const void* b, const void* b1, const float* bias1, const float* bias2,
+                               void* d, const int32_t* m_indices, void* workspace, size_t workspace_bytes, int T, int H,
+                               int I, int E, int k, dqmoe_stream_t stream) {
+    return moe_forward_impl(a, nullptr, b, nullptr, b1, nullptr, d, m_indices, workspace, workspace_bytes, T, H, I, E, k,
+                            DQMOE_QUANT_NONE, gemm::kHalf, bias1, bias2, static_cast<cudaStream_t>(stream));
 }
 
 // ---------------------------------------------------------------------------------------------

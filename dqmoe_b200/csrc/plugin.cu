@@ -57,15 +57,16 @@ static int validate(const dqmoe_plugin_fields& f) {
                  f.expert_hidden_size);
     DQ_CHECK_FMT(f.expert_inter_size > 0 && f.expert_inter_size % 16 == 0, "expert_inter_size=%d", f.expert_inter_size);
     DQ_CHECK_FMT(f.max_num_tokens >= 0, "max_num_tokens=%d", f.max_num_tokens);
-    // the reference's runner carries expert_bias1/2 but never reads them (csrc/moe_kernels.h:72-75)
-    DQ_CHECK_FMT(f.use_bias == 0, "use_bias=%d: expert biases are not applied by the layer", f.use_bias);
-    DQ_CHECK_FMT(f.type == DQMOE_DT_FP8 || f.type == DQMOE_DT_BF16 || f.type == DQMOE_DT_HALF,
-                 "type=%d: built for FP8 (6), BF16 (7) and HALF (1) operands; the FP32 instantiation is not built", f.type);
+    DQ_CHECK_FMT(f.use_bias == 0 || f.use_bias == 1, "use_bias=%d", f.use_bias);
+    DQ_CHECK_FMT(f.type == DQMOE_DT_FP8 || f.type == DQMOE_DT_BF16 || f.type == DQMOE_DT_HALF || f.type == DQMOE_DT_FLOAT,
+                 "type=%d: operands are FP8 (6), BF16 (7), HALF (1) or FLOAT (0)", f.type);
     DQ_CHECK_FMT(f.output_type == DQMOE_DT_BF16 || f.output_type == DQMOE_DT_HALF || f.output_type == DQMOE_DT_FLOAT,
                  "output_type=%d", f.output_type);
     if (f.type == DQMOE_DT_HALF)
         DQ_CHECK_FMT(f.output_type == DQMOE_DT_HALF, "output_type=%d: HALF operands give HALF output", f.output_type);
-    if (f.type == DQMOE_DT_BF16 || f.type == DQMOE_DT_HALF)
+    if (f.type == DQMOE_DT_FLOAT)
+        DQ_CHECK_FMT(f.output_type == DQMOE_DT_FLOAT, "output_type=%d: FLOAT operands give FLOAT output", f.output_type);
+    if (f.type == DQMOE_DT_BF16 || f.type == DQMOE_DT_HALF || f.type == DQMOE_DT_FLOAT)
         DQ_CHECK_FMT(f.quant_mode == DQMOE_QUANT_NONE, "quant_mode=%d with unquantised operands", f.quant_mode);
     else
         DQ_CHECK_FMT(f.quant_mode == DQMOE_QUANT_FP8_TENSOR || f.quant_mode == DQMOE_QUANT_FP8_CHANNEL ||
@@ -75,6 +76,10 @@ static int validate(const dqmoe_plugin_fields& f) {
 }
 
 static size_t layer_bytes(const dqmoe_plugin_fields& f, int T) {
+    if (f.type == DQMOE_DT_FLOAT)
+        return align_up(dqmoe_moe_workspace_bytes_f32(T, f.expert_hidden_size, f.expert_inter_size, f.number_of_experts,
+                                                      f.top_k),
+                        kAlign);
     return align_up(dqmoe_moe_workspace_bytes(T, f.expert_hidden_size, f.expert_inter_size, f.number_of_experts, f.top_k,
                                               f.quant_mode),
                     kAlign);
@@ -110,7 +115,7 @@ int dqmoe_plugin_get_fields(const dqmoe_plugin* p, dqmoe_plugin_fields* out) {
 size_t dqmoe_plugin_workspace_size(const dqmoe_plugin* p, int num_tokens) {
     if (p == nullptr || num_tokens < 0 || num_tokens > p->f.max_num_tokens) return 0;
     size_t bytes = plugin::layer_bytes(p->f, num_tokens);
-    if (p->f.type != DQMOE_DT_HALF && p->f.output_type != DQMOE_DT_BF16)  // bf16 result staged for conversion
+    if (p->f.type != DQMOE_DT_HALF && p->f.type != DQMOE_DT_FLOAT && p->f.output_type != DQMOE_DT_BF16)  // bf16 result staged for conversion
         bytes += align_up(size_t(num_tokens) * p->f.top_k * p->f.expert_hidden_size * 2, plugin::kAlign);
     return bytes;
 }
@@ -128,15 +133,21 @@ int dqmoe_plugin_enqueue(const dqmoe_plugin* p, int num_tokens, const void* cons
     const bool fp8 = f.quant_mode != DQMOE_QUANT_NONE;
     const int T = num_tokens, H = f.expert_hidden_size, I = f.expert_inter_size, E = f.number_of_experts, k = f.top_k;
     const size_t lbytes = plugin::layer_bytes(f, T);
+    const float* bias1 = f.use_bias ? static_cast<const float*>(inputs[4]) : nullptr;
+    const float* bias2 = f.use_bias ? static_cast<const float*>(inputs[5]) : nullptr;
+    if (f.use_bias) DQ_CHECK(bias1 != nullptr && bias2 != nullptr);
     if (f.type == DQMOE_DT_HALF)
-        return dqmoe_moe_forward_f16(inputs[0], inputs[1], inputs[2], outputs[0], static_cast<const int32_t*>(inputs[3]),
-                                     workspace, lbytes, T, H, I, E, k, stream_);
+        return dqmoe_moe_forward_f16_bias(inputs[0], inputs[1], inputs[2], bias1, bias2, outputs[0],
+                                          static_cast<const int32_t*>(inputs[3]), workspace, lbytes, T, H, I, E, k, stream_);
+    if (f.type == DQMOE_DT_FLOAT)
+        return dqmoe_moe_forward_f32(inputs[0], inputs[1], inputs[2], bias1, bias2, outputs[0],
+                                     static_cast<const int32_t*>(inputs[3]), workspace, lbytes, T, H, I, E, k, stream_);
     void* d = f.output_type == DQMOE_DT_BF16 ? outputs[0] : static_cast<char*>(workspace) + lbytes;
-    int rc = dqmoe_moe_forward(inputs[0], fp8 ? static_cast<const float*>(inputs[6]) : nullptr, inputs[1],
-                               fp8 ? static_cast<const float*>(inputs[7]) : nullptr, inputs[2],
-                               fp8 ? static_cast<const float*>(inputs[8]) : nullptr, d,
-                               static_cast<const int32_t*>(inputs[3]), workspace, lbytes, T, H, I, E, k, f.quant_mode, 1,
-                               stream_);
+    int rc = dqmoe_moe_forward_bias(inputs[0], fp8 ? static_cast<const float*>(inputs[6]) : nullptr, inputs[1],
+                                    fp8 ? static_cast<const float*>(inputs[7]) : nullptr, inputs[2],
+                                    fp8 ? static_cast<const float*>(inputs[8]) : nullptr, bias1, bias2, d,
+                                    static_cast<const int32_t*>(inputs[3]), workspace, lbytes, T, H, I, E, k,
+                                    f.quant_mode, stream_);
     if (rc != DQMOE_OK || f.output_type == DQMOE_DT_BF16) return rc;
     cudaStream_t stream = static_cast<cudaStream_t>(stream_);
     const size_t n8 = size_t(T) * k * H / 8;  // H is a multiple of 16

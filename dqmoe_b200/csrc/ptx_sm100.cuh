@@ -148,7 +148,7 @@ __device__ __forceinline__ uint64_t smem_desc_sw128(uint32_t smem_addr) {
 }
 
 // Instruction descriptor: D fp32, A and B both K-major, M x N tile.
-// ab_format: kind::f8f6f4 -> 0 = e4m3 ; kind::f16 -> 1 = bf16.
+// ab_format: kind::f8f6f4 -> 0 = e4m3 ; kind::f16 -> 0 = f16, 1 = bf16 ; kind::tf32 -> 2 = tf32.
 __host__ __device__ constexpr uint32_t make_idesc(uint32_t ab_format, uint32_t m, uint32_t n) {
     return (1u << 4)               // D format fp32
            | (ab_format << 7)      // A format
@@ -157,10 +157,11 @@ __host__ __device__ constexpr uint32_t make_idesc(uint32_t ab_format, uint32_t m
            | ((m >> 4) << 24);     // M / 16
 }
 
-template <bool kFp8>
+// kKind: 0 = kind::f8f6f4 (e4m3), 1 = kind::f16 (bf16 / fp16), 2 = kind::tf32 (fp32 operands read as TF32)
+template <int kKind>
 __device__ __forceinline__ void umma(uint32_t tmem_d, uint64_t desc_a, uint64_t desc_b, uint32_t idesc,
                                      uint32_t accumulate) {
-    if constexpr (kFp8) {
+    if constexpr (kKind == 0) {
         asm volatile(
             "{\n\t"
             ".reg .pred p;\n\t"
@@ -169,12 +170,21 @@ __device__ __forceinline__ void umma(uint32_t tmem_d, uint64_t desc_a, uint64_t 
             "}" ::"r"(tmem_d),
             "l"(desc_a), "l"(desc_b), "r"(idesc), "r"(accumulate)
             : "memory");
-    } else {
+    } else if constexpr (kKind == 1) {
         asm volatile(
             "{\n\t"
             ".reg .pred p;\n\t"
             "setp.ne.b32 p, %4, 0;\n\t"
             "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t"
+            "}" ::"r"(tmem_d),
+            "l"(desc_a), "l"(desc_b), "r"(idesc), "r"(accumulate)
+            : "memory");
+    } else {
+        asm volatile(
+            "{\n\t"
+            ".reg .pred p;\n\t"
+            "setp.ne.b32 p, %4, 0;\n\t"
+            "tcgen05.mma.cta_group::1.kind::tf32 [%0], %1, %2, %3, p;\n\t"
             "}" ::"r"(tmem_d),
             "l"(desc_a), "l"(desc_b), "r"(idesc), "r"(accumulate)
             : "memory");
@@ -233,10 +243,11 @@ __device__ __forceinline__ void tmem_dealloc_pair(uint32_t taddr, uint32_t ncols
 }
 // One MMA over both CTAs of a pair: M = 256 (128 rows from each CTA's A tile and TMEM), the B
 // operand is the concatenation of the two CTAs' B tiles. Issued by one thread of the leader CTA.
-template <bool kFp8>
+template <int kKind>
 __device__ __forceinline__ void umma_pair(uint32_t tmem_d, uint64_t desc_a, uint64_t desc_b, uint32_t idesc,
                                           uint32_t accumulate) {
-    if constexpr (kFp8) {
+    static_assert(kKind == 0 || kKind == 1, "pairs: e4m3 and 16-bit operands");
+    if constexpr (kKind == 0) {
         asm volatile(
             "{\n\t"
             ".reg .pred p;\n\t"

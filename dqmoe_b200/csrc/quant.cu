@@ -7,6 +7,8 @@
 //   128x128       one scale per weight block  per_block_cast_to_fp8
 //   tensor        one scale per tensor/expert (the reference has it for the intermediate only)
 //   requant       second pass for the intermediate when stage 1 collected the amax
+#include <mutex>
+
 #include "common.cuh"
 
 namespace dq {
@@ -185,9 +187,11 @@ static __device__ __align__(256) float g_static_amax[kStaticMaxSlices];
 static int static_amax_address(float** out) {
     constexpr int kMaxDevices = 64;
     static float* cached[kMaxDevices] = {nullptr};
+    static std::mutex mu;  // two host threads may make their first call on a device at once
     int dev = 0;
     DQ_CUDA(cudaGetDevice(&dev));
     DQ_CHECK(dev >= 0 && dev < kMaxDevices);
+    std::lock_guard<std::mutex> lk(mu);
     if (cached[dev] == nullptr) {
         float* p = nullptr;
         DQ_CUDA(cudaGetSymbolAddress(reinterpret_cast<void**>(&p), g_static_amax));

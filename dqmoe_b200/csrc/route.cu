@@ -305,13 +305,15 @@ __global__ void __launch_bounds__(256) route_topk_kernel(const float* __restrict
     float sel_score = 0.0f;  // lane j keeps the j-th selected score
     int sel_idx = 0;
     float denom = 0.0f;
+    uint32_t taken = 0;      // bit i: this lane's i-th expert has been selected (an expert is chosen at most once,
+                             // also when fewer than k logits are above -inf)
     for (int j = 0; j < k; ++j) {
         float bv = -INFINITY;
         int bi = 0x7fffffff;
 #pragma unroll
         for (int i = 0; i < kPerLane; ++i) {
             const int e = i * 32 + lane;
-            if (e < E && (x[i] > bv || (x[i] == bv && e < bi))) {
+            if (e < E && ((taken >> i) & 1u) == 0u && (x[i] > bv || (x[i] == bv && e < bi))) {
                 bv = x[i];
                 bi = e;
             }
@@ -328,7 +330,7 @@ __global__ void __launch_bounds__(256) route_topk_kernel(const float* __restrict
         // remove the winner from its owner lane
 #pragma unroll
         for (int i = 0; i < kPerLane; ++i)
-            if (i * 32 + lane == bi) x[i] = -INFINITY;
+            if (i * 32 + lane == bi) taken |= 1u << i;
         const float score = scoring == DQMOE_SCORE_SIGMOID ? 1.0f / (1.0f + expf(-bv)) : expf(bv - m);
         denom += score;
         if (lane == j) {

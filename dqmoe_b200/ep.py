@@ -72,6 +72,24 @@ class CudaBackend:
         return self.ops.finalize_weighted(d, weights)
 
 
+def check_same_config(group, **config) -> None:
+    """Every rank must have built its layer with the same sizes: a rank with another E or k would send
+    counts and rows the others lay out differently. One small all_gather at construction; raises on every
+    rank when the values differ."""
+    names = sorted(config)
+    mine = torch.tensor([int(config[n]) for n in names], dtype=torch.int64)
+    backend = dist.get_backend(group)
+    dev = torch.device("cuda", torch.cuda.current_device()) if backend == "nccl" else torch.device("cpu")
+    mine = mine.to(dev)
+    everyone = [torch.empty_like(mine) for _ in range(dist.get_world_size(group))]
+    dist.all_gather(everyone, mine, group=group)
+    for r, other in enumerate(everyone):
+        if not torch.equal(other, everyone[0]):
+            diff = {n: (int(everyone[0][i]), int(other[i])) for i, n in enumerate(names) if other[i] != everyone[0][i]}
+            raise RuntimeError(f"[ASSERT FAILED] ep.py  Condition: all ranks built the layer with the same sizes  "
+                               f"Info: rank {r} differs from rank 0 in {diff}")
+
+
 class ExpertParallelLayer:
     """One expert-parallel MoE layer; `weights_q` holds this rank's experts only."""
 
@@ -80,6 +98,7 @@ class ExpertParallelLayer:
         self.world = dist.get_world_size(group)
         self.rank = dist.get_rank(group)
         self.E, self.k, self.mode = E, k, mode
+        check_same_config(group, E=E, k=k, mode=mode)
         self.lo, self.hi = expert_range(self.rank, self.world, E)
         self.E_local = self.hi - self.lo
         self.weights_q = weights_q
@@ -98,6 +117,9 @@ class ExpertParallelLayer:
 
     def all_to_all_rows(self, x: torch.Tensor, out_rows: int, in_splits, out_splits) -> torch.Tensor:
         """Variable-size all-to-all over the leading (row) dimension; bytes are moved as uint8."""
+        if sum(in_splits) != x.shape[0] or sum(out_splits) != out_rows or min(list(in_splits) + list(out_splits) + [0]) < 0:
+            raise RuntimeError(f"[ASSERT FAILED] ep.py  Condition: split sizes add up to the rows exchanged  "
+                               f"Info: sending {x.shape[0]} rows as {list(in_splits)}, receiving {out_rows} as {list(out_splits)}")
         flat = x.reshape(x.shape[0], -1)
         as_bytes = flat.view(torch.uint8) if flat.dtype != torch.uint8 else flat
         out = torch.empty((out_rows, as_bytes.shape[1]), dtype=torch.uint8, device=x.device)
@@ -216,7 +238,7 @@ class PeerExpertParallelLayer:
     """
 
     def __init__(self, T: int, H: int, I: int, E: int, k: int, mode: int, weights_q, ops, group=None,
-                 capacity_rows: Optional[int] = None):
+                 capacity_rows: Optional[int] = None, capacity_factor: float = 2.0):
         import ctypes
         import os
         os.environ.setdefault("TORCH_SYMM_MEM_DISABLE_MULTICAST", "1")  # plain peer loads/stores only
@@ -230,12 +252,24 @@ class PeerExpertParallelLayer:
         if self.W > 8:
             raise RuntimeError("[ASSERT FAILED] ep.py  Condition: world <= 8")
         self.T, self.H, self.I, self.E, self.k, self.mode = T, H, I, E, k, mode
+        check_same_config(self.group, T=T, H=H, I=I, E=E, k=k, mode=mode,
+                          capacity_rows=-1 if capacity_rows is None else capacity_rows,
+                          capacity_factor_x1000=int(capacity_factor * 1000))
         self.lo, self.hi = expert_range(self.me, self.W, E)
         self.El = self.hi - self.lo
         self.weights_q = weights_q
         self.esz = 1 if mode else 2
         self.n = T * k
-        self.cap = capacity_rows if capacity_rows is not None else self.W * self.n  # worst case: every row comes here
+        # Rows this rank can receive in one call. Balanced routing sends about n = T*k rows to every rank;
+        # the default leaves room for `capacity_factor` times that (never more than the worst case W*n).
+        # The plan kernel compares every rank's incoming rows with the capacity: on overflow the call moves
+        # and computes nothing on any rank and the device status word reads 202 (see check_status()).
+        worst = self.W * self.n
+        if capacity_rows is None:
+            capacity_rows = min(worst, int(capacity_factor * self.n + 127) // 128 * 128)
+        if capacity_rows < 0:
+            raise RuntimeError("[ASSERT FAILED] ep.py  Condition: capacity_rows >= 0")
+        self.cap = min(capacity_rows, worst)
         self.scale_cols = (H + 127) // 128 if mode == 1024 else (1 if mode == 512 else 0)
         dev = torch.device("cuda", torch.cuda.current_device())
         self.dev = dev
@@ -257,7 +291,7 @@ class PeerExpertParallelLayer:
             arr = (ctypes.c_void_p * self.W)(*[b + self.off[name] for b in bases])
             self._ptr_arrays[name] = arr
         self.local = {name: self.sym.data_ptr() + o for name, o in self.off.items()}
-        self.send_base = torch.zeros(E, dtype=torch.int32, device=dev)
+        self.send_base = torch.zeros(E + 1, dtype=torch.int32, device=dev)  # [E] = plan void (see dqmoe_ep_plan)
         self.rx_offsets = torch.zeros(self.El + 1, dtype=torch.int32, device=dev)
         self.rx_mtiles = torch.zeros(self.El + 1, dtype=torch.int32, device=dev)
         self.done = torch.zeros(1, dtype=torch.int32, device=dev)
@@ -271,6 +305,16 @@ class PeerExpertParallelLayer:
         self.epoch = 0
         torch.cuda.synchronize()
         dist.barrier(self.group)  # every rank's flags are zero before anyone publishes
+
+    def check_status(self) -> None:
+        """Synchronise and raise if a kernel of an earlier call gave up: forward() enqueues without a host
+        synchronisation, so a caller that must know whether an output is complete calls this after it.
+        202 = a rank's receive buffer (capacity_rows) was too small for the routing of that call; 201 / 211 /
+        212 = a peer never arrived at the count exchange / the dispatch / the combine."""
+        code = self.ops.device_status()
+        if code != 0:
+            raise RuntimeError(f"[ASSERT FAILED] ep.py  Condition: device_status() == 0  Info: status {code}"
+                               + (f": more than capacity_rows={self.cap} rows for one rank" if code == 202 else ""))
 
     def forward(self, a: torch.Tensor, a_scale: Optional[torch.Tensor], m_indices: torch.Tensor,
                 route_weights: Optional[torch.Tensor] = None, zero_dropped: bool = False) -> torch.Tensor:
@@ -287,7 +331,7 @@ class PeerExpertParallelLayer:
             self.d_out.zero_()
         counts, offsets, d2s, _ = ops.route_sort(m_indices, E)
         self.check(lib.dqmoe_ep_publish_counts(vp(counts.data_ptr()), E, me, W, P["cnt"], P["flags"], ep_, stream))
-        self.check(lib.dqmoe_ep_plan(vp(self.local["cnt"]), vp(self.local["flags"]), E, me, W, ep_,
+        self.check(lib.dqmoe_ep_plan(vp(self.local["cnt"]), vp(self.local["flags"]), E, me, W, ep_, self.cap,
                                      vp(self.send_base.data_ptr()), vp(self.rx_offsets.data_ptr()),
                                      vp(self.rx_mtiles.data_ptr()), stream))
         sc_ptr = vp(a_scale.data_ptr()) if self.scale_cols else None

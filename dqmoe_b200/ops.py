@@ -54,9 +54,31 @@ def moe_workspace_bytes(T: int, H: int, I: int, E: int, k: int, quant_mode: int)
     return int(_lib.load().dqmoe_moe_workspace_bytes(T, H, I, E, k, quant_mode))
 
 
+def _check_scales(a_scale, b_scale, b1_scale, T, H, I, E, quant_mode):
+    """Scale tensors must be fp32 CUDA tensors with exactly the element count the mode reads
+    (include/dqmoe.h lists the shapes); a short tensor would be read out of bounds by the kernels."""
+    g = lambda x: (x + 127) // 128
+    want = {QUANT_FP8_TENSOR: (1, E, E), QUANT_FP8_CHANNEL: (T, E * 2 * I, E * H),
+            QUANT_FP8_BLOCK: (T * g(H), E * g(2 * I) * g(H), E * g(H) * g(I))}[quant_mode]
+    for name, t, n in zip(("a_scale", "b_scale", "b1_scale"), (a_scale, b_scale, b1_scale), want):
+        if t is None or not t.is_cuda or t.dtype != torch.float32 or not t.is_contiguous() or t.numel() != n:
+            got = "None" if t is None else f"{t.dtype} {tuple(t.shape)} on {t.device}"
+            raise RuntimeError(f"[ASSERT FAILED] ops.py  Condition: {name} is a contiguous fp32 CUDA tensor of {n} "
+                               f"elements for quant mode {quant_mode}  Info: got {got}")
+
+
+def _check_bias(bias, E, cols, name):
+    if bias is None:
+        return
+    if not bias.is_cuda or bias.dtype != torch.float32 or not bias.is_contiguous() or tuple(bias.shape) != (E, cols):
+        raise RuntimeError(f"[ASSERT FAILED] ops.py  Condition: {name} is a contiguous fp32 CUDA tensor [{E}, {cols}]")
+
+
 def moe_forward(a, a_scale, b, b_scale, b1, b1_scale, d, m_indices, workspace, quant_mode: int,
-                fused: bool = True) -> None:
-    """One MoE layer into d[T, k, H]; see dqmoe_moe_forward in include/dqmoe.h."""
+                fused: bool = True, bias1: Optional[torch.Tensor] = None,
+                bias2: Optional[torch.Tensor] = None) -> None:
+    """One MoE layer into d[T, k, H]; see dqmoe_moe_forward (and dqmoe_moe_forward_bias for
+    the fp32 expert biases bias1 [E, 2I] / bias2 [E, H]) in include/dqmoe.h."""
     lib = _lib.load()
     T, H = a.shape
     E, I2, _ = b.shape
@@ -64,27 +86,45 @@ def moe_forward(a, a_scale, b, b_scale, b1, b1_scale, d, m_indices, workspace, q
     k = d.shape[1]
     for name, t in (("a", a), ("b", b), ("b1", b1), ("d", d), ("m_indices", m_indices), ("workspace", workspace)):
         _cuda(t, name)
+    quant_mode = int(quant_mode)
+    if quant_mode in (QUANT_FP8_TENSOR, QUANT_FP8_CHANNEL, QUANT_FP8_BLOCK):
+        _check_scales(a_scale, b_scale, b1_scale, T, H, I, E, quant_mode)
+    _check_bias(bias1, E, 2 * I, "bias1")
+    _check_bias(bias2, E, H, "bias2")
     with torch.cuda.device(a.device):
-        _lib.check(lib.dqmoe_moe_forward(
-            _p(a), _p(a_scale), _p(b), _p(b_scale), _p(b1), _p(b1_scale), _p(d), _p(m_indices),
-            _p(workspace), workspace.numel() * workspace.element_size(), T, H, I, E, k,
-            int(quant_mode), int(bool(fused)), _stream(a.device)))
+        if bias1 is None and bias2 is None:
+            _lib.check(lib.dqmoe_moe_forward(
+                _p(a), _p(a_scale), _p(b), _p(b_scale), _p(b1), _p(b1_scale), _p(d), _p(m_indices),
+                _p(workspace), workspace.numel() * workspace.element_size(), T, H, I, E, k,
+                quant_mode, int(bool(fused)), _stream(a.device)))
+        else:
+            _lib.check(lib.dqmoe_moe_forward_bias(
+                _p(a), _p(a_scale), _p(b), _p(b_scale), _p(b1), _p(b1_scale), _p(bias1), _p(bias2), _p(d),
+                _p(m_indices), _p(workspace), workspace.numel() * workspace.element_size(), T, H, I, E, k,
+                quant_mode, _stream(a.device)))
 
 
-def moe_forward_f16(a, b, b1, d, m_indices, workspace) -> None:
-    """The unquantised layer on fp16 tensors into d[T, k, H] (fp16); see dqmoe_moe_forward_f16."""
+def moe_workspace_bytes_f32(T: int, H: int, I: int, E: int, k: int) -> int:
+    return int(_lib.load().dqmoe_moe_workspace_bytes_f32(T, H, I, E, k))
+
+
+def moe_forward_f32(a, b, b1, d, m_indices, workspace, bias1=None, bias2=None) -> None:
+    """The unquantised layer on fp32 tensors (TF32 tensor-core products) into d[T, k, H] fp32;
+    see dqmoe_moe_forward_f32."""
     lib = _lib.load()
     for name, t in (("a", a), ("b", b), ("b1", b1), ("d", d), ("m_indices", m_indices), ("workspace", workspace)):
         _cuda(t, name)
     for name, t in (("a", a), ("b", b), ("b1", b1), ("d", d)):
-        if t.dtype != torch.float16:
-            raise RuntimeError(f"[ASSERT FAILED] ops.py  Condition: {name}.scalar_type() == at::kHalf")
+        if t.dtype != torch.float32:
+            raise RuntimeError(f"[ASSERT FAILED] ops.py  Condition: {name}.scalar_type() == at::kFloat")
     T, H = a.shape
     E, I, k = b.shape[0], b1.shape[2], d.shape[1]
+    _check_bias(bias1, E, 2 * I, "bias1")
+    _check_bias(bias2, E, H, "bias2")
     with torch.cuda.device(a.device):
-        _lib.check(lib.dqmoe_moe_forward_f16(_p(a), _p(b), _p(b1), _p(d), _p(m_indices), _p(workspace),
-                                             workspace.numel() * workspace.element_size(), T, H, I, E, k,
-                                             _stream(a.device)))
+        _lib.check(lib.dqmoe_moe_forward_f32(_p(a), _p(b), _p(b1), _p(bias1), _p(bias2), _p(d), _p(m_indices),
+                                             _p(workspace), workspace.numel() * workspace.element_size(), T, H, I, E,
+                                             k, _stream(a.device)))
 
 
 def moe_block(x: torch.Tensor, logits: torch.Tensor, b, b_scale, b1, b1_scale, k: int, scoring: str = "softmax",

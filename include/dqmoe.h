@@ -109,6 +109,34 @@ int dqmoe_moe_forward_f16(const void* a, const void* b, const void* b1, void* d,
                           int H, int I, int E, int k, dqmoe_stream_t stream);
 
 /*
+ * The layer with expert biases: bias1 [E, 2I] and bias2 [E, H], fp32, are added to the dequantised fc1 and
+ * fc2 products before their rounding (out = A W^T + bias, as torch's F.linear); either may be NULL. Other
+ * arguments as dqmoe_moe_forward / dqmoe_moe_forward_f16. The reference's runner carries expert_bias1 /
+ * expert_bias2 and its plugin a use_bias field (csrc/moe_kernels.h:72-78, test/trt_test.py:82-89, :121), but
+ * its GEMMs are launched with C = nullptr (csrc/moe_kernels.h:908), so it defines no bias arithmetic.
+ */
+int dqmoe_moe_forward_bias(const void* a, const float* a_scale, const void* b, const float* b_scale,
+                           const void* b1, const float* b1_scale, const float* bias1, const float* bias2,
+                           void* d, const int32_t* m_indices, void* workspace, size_t workspace_bytes, int T,
+                           int H, int I, int E, int k, int quant_mode, dqmoe_stream_t stream);
+int dqmoe_moe_forward_f16_bias(const void* a, const void* b, const void* b1, const float* bias1,
+                               const float* bias2, void* d, const int32_t* m_indices, void* workspace,
+                               size_t workspace_bytes, int T, int H, int I, int E, int k,
+                               dqmoe_stream_t stream);
+
+/*
+ * The unquantised layer on fp32 operands: a [T,H], b [E,2I,H], b1 [E,H,I] and d [T,k,H] are fp32, the
+ * intermediate stays fp32. The products run on the tensor cores as TF32 (operands read with a 10-bit
+ * mantissa, fp32 accumulation), which is also what the reference's T = float instantiation does on its
+ * tensor-op GEMM (csrc/moe_gemm_template.h:487-528, README.md:7); results agree with an fp32 reference to
+ * about 1e-3 relative, not bit for bit. H and I must be multiples of 4. bias1 / bias2 as above, or NULL.
+ */
+size_t dqmoe_moe_workspace_bytes_f32(int T, int H, int I, int E, int k);
+int dqmoe_moe_forward_f32(const void* a, const void* b, const void* b1, const float* bias1,
+                          const float* bias2, void* d, const int32_t* m_indices, void* workspace,
+                          size_t workspace_bytes, int T, int H, int I, int E, int k, dqmoe_stream_t stream);
+
+/*
  * Addresses of intermediates inside a workspace laid out by dqmoe_moe_forward
  * for the same problem size (debug/testing aid; the reference has the unused
  * extractIntermediateResultsforTorch, csrc/moe_kernels.h:739-767).
@@ -166,13 +194,13 @@ int dqmoe_moe_block_shared(const void* x_bf16, const float* logits, const void* 
  * type / output_type use the nvinfer1::DataType codes below. Built: FP8 operands with
  * quant_mode 256 / 512 / 1024 and BF16 operands with quant_mode 0, with outputs BF16
  * (written directly), HALF or FLOAT (converted from the layer's bf16 result through
- * workspace); HALF operands with quant_mode 0 and HALF output (dqmoe_moe_forward_f16).
- * type FLOAT (the reference's unquantised FP32 instantiation) and use_bias != 0 return
- * DQMOE_ERR_INVALID.
+ * workspace); HALF operands with quant_mode 0 and HALF output (dqmoe_moe_forward_f16);
+ * FLOAT operands with quant_mode 0 and FLOAT output (dqmoe_moe_forward_f32).
  * enqueue inputs: 0 input [T,H], 1 weight1 [E,2I,H], 2 weight2 [E,H,I], 3 index [T,k] int32,
- * 4 bias1, 5 bias2 (never read), 6 actscale, 7 scale_a (fc1 weight scales), 8 scale_b (fc2
- * weight scales); entries 6-8 are read only for FP8 operands. Scale shapes per mode as
- * listed at the top of this file.
+ * 4 bias1 [E,2I] fp32, 5 bias2 [E,H] fp32 (read only when use_bias != 0; the reference's test
+ * passes weight-shaped dummies with use_bias = 0), 6 actscale, 7 scale_a (fc1 weight scales),
+ * 8 scale_b (fc2 weight scales); entries 6-8 are read only for FP8 operands. Scale shapes per
+ * mode as listed at the top of this file.
  */
 #define DQMOE_DT_FLOAT 0
 #define DQMOE_DT_HALF 1
@@ -211,6 +239,10 @@ int dqmoe_plugin_deserialize(const void* buffer, size_t bytes, dqmoe_plugin** ou
  * order (ties: lower expert id first), weights [T, k] fp32 normalised to sum 1.
  * The reference has no router kernel; its tests use torch.randn + torch.topk
  * (test/torch_test.py:78-80). E <= 1024, k <= 32.
+ * An expert is chosen at most once per token, also when fewer than k logits are above -inf
+ * (masked experts then fill the last slots in id order with weight 0 under softmax). A NaN logit is
+ * never chosen; a row with fewer than k non-NaN logits gets the id 0x7fffffff in the slots that are
+ * left, which the expert sort drops like any id outside [0, E).
  */
 int dqmoe_route_topk(const float* logits, int T, int E, int k, int scoring, int32_t* indices,
                      float* weights, dqmoe_stream_t stream);
@@ -366,14 +398,20 @@ int dqmoe_requant_from_amax_dev(const void* act_bf16, int64_t n_max, int I, cons
  * owns experts [me*E/W, (me+1)*E/W). The *_ptrs arguments are host arrays of W device addresses,
  * entry r being rank r's copy of the same buffer (this rank's own copy included). Flags are
  * int32[3][8] per rank and carry a per-call `epoch` (any value different from the previous
- * call's), so nothing is cleared between calls. Waits are bounded (about 10 s) and report through
- * dqmoe_device_status() instead of hanging. The reference has no multi-GPU path.
+ * call's), so nothing is cleared between calls. Waits are bounded (about 10 s unless
+ * dqmoe_ep_set_wait_limit says otherwise) and report through dqmoe_device_status() instead of
+ * hanging: 201 = plan never saw every rank's counts, 202 = some rank would receive more than `cap`
+ * rows (every rank then sends and computes nothing in this call), 211 / 212 = wait on phase 1 / 2
+ * ran out. The status word is sticky; a caller that must know whether a call's output is complete
+ * reads it after the call. The reference has no multi-GPU path.
  *
  *   publish_counts  counts[E] of the local expert sort -> row `me` of every rank's cnt[W][E]; flag 0
  *   plan            waits flag 0 of all ranks; send_base[E] = row in the owner's receive buffer where
  *                   this rank's rows of expert e start (the receive buffer is grouped by expert, then
- *                   by source rank); rx_offsets / rx_mtiles [E/W + 1] describe this rank's own
- *                   receive buffer for dqmoe_grouped_gemm
+ *                   by source rank; send_base has E + 1 words, the last one is set to 1 when the plan
+ *                   is void: counts missing, or a receive buffer of `cap` rows too small);
+ *                   rx_offsets / rx_mtiles [E/W + 1] describe this rank's own receive buffer for
+ *                   dqmoe_grouped_gemm
  *   dispatch        a[dest_to_src[i] / k] (+ scale row, + home slot) of every kept sorted row i ->
  *                   the owner's rx_rows / rx_scale / rx_home; flag 1 when all rows are written
  *   wait / signal   flag `phase` (1: rows landed, 2: results landed)
@@ -381,8 +419,11 @@ int dqmoe_requant_from_amax_dev(const void* act_bf16, int64_t n_max, int I, cons
  */
 int dqmoe_ep_publish_counts(const int32_t* counts, int E, int me, int W, const void* const* cnt_ptrs,
                             const void* const* flag_ptrs, int epoch, dqmoe_stream_t stream);
-int dqmoe_ep_plan(const int32_t* cnt, const int32_t* my_flags, int E, int me, int W, int epoch,
+int dqmoe_ep_plan(const int32_t* cnt, const int32_t* my_flags, int E, int me, int W, int epoch, int cap,
                   int32_t* send_base, int32_t* rx_offsets, int32_t* rx_mtiles, dqmoe_stream_t stream);
+/* Clock cycles a flag wait of the kernels above may spin before it gives up (process-wide, applies to
+ * launches made afterwards); 0 restores the default of about 10 s. */
+int dqmoe_ep_set_wait_limit(int64_t cycles);
 int dqmoe_ep_dispatch(const void* a, const float* a_scale, size_t row_bytes, int scale_cols, int k, int n,
                       const int32_t* offsets, const int32_t* dest_to_src, const int32_t* send_base,
                       int E, int me, int W, const void* const* rx_rows, const void* const* rx_scale,

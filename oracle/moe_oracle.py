@@ -161,16 +161,25 @@ def _swiglu_bf16(inter: torch.Tensor) -> torch.Tensor:
     return F.silu(gate) * value
 
 
-def moe_layer_bf16(a, b, b1, m_indices, E: int) -> torch.Tensor:
-    """torch_moe_grouped (test/util.py:71-92): bf16 linear, SwiGLU, bf16 linear, scatter to [T, k, H]."""
+def _linear_bias(x, w, bias):
+    """x w^T + bias with the product accumulated and the bias added in fp32, one rounding to x's type."""
+    return (F.linear(x.float(), w.float()) + bias.float()).to(x.dtype)
+
+
+def moe_layer_bf16(a, b, b1, m_indices, E: int, bias1=None, bias2=None) -> torch.Tensor:
+    """torch_moe_grouped (test/util.py:71-92): linear, SwiGLU, linear, scatter to [T, k, H], in the operands'
+    type (bf16 in the reference's test; fp16 and fp32 operands take the same steps). With expert biases
+    bias1 [E, 2I] / bias2 [E, H] (fp32; parity unpinned: the reference never applies its bias arguments)
+    each linear adds its expert's bias before rounding."""
     T, k = m_indices.shape
     d = torch.zeros((T, k, a.shape[1]), dtype=a.dtype)
     for e in range(E):
         tok, slot = torch.where(m_indices == e)
         if tok.numel() == 0:
             continue
-        act = _swiglu_bf16(F.linear(a[tok], b[e]))
-        d[tok, slot] = F.linear(act, b1[e])
+        inter = F.linear(a[tok], b[e]) if bias1 is None else _linear_bias(a[tok], b[e], bias1[e])
+        act = _swiglu_bf16(inter)
+        d[tok, slot] = F.linear(act, b1[e]) if bias2 is None else _linear_bias(act, b1[e], bias2[e])
     return d
 
 
@@ -183,12 +192,13 @@ def _expand(scale: torch.Tensor, rows: int, cols: int) -> torch.Tensor:
 
 
 def moe_layer_fp8(a_q, a_s, b_q, b_s, b1_q, b1_s, m_indices, E: int, quant_mode: int,
-                  return_intermediate: bool = False):
+                  return_intermediate: bool = False, bias1=None, bias2=None):
     """FP8-simulating layer. Block mode restates fp8_blockwise_torch_moe_grouped
     (test/util.py:95-158): dequantise, fp32 linear, round to bf16, SwiGLU in bf16,
     re-quantise the intermediate, dequantise, fp32 linear, round to bf16. Channel and
     tensor modes apply the same steps with their scale shapes (parity unpinned: the
-    reference has no torch model of them)."""
+    reference has no torch model of them). bias1 [E, 2I] / bias2 [E, H] (fp32, parity unpinned)
+    are added to the fp32 products before the rounding to bf16."""
     T, k = m_indices.shape
     H = a_q.shape[1]
     I = b1_q.shape[2]
@@ -212,8 +222,10 @@ def moe_layer_fp8(a_q, a_s, b_q, b_s, b1_q, b1_s, m_indices, E: int, quant_mode:
             dq_b = b_q[e].float() * b_s[e]
         else:
             raise ValueError(quant_mode)
-        inter = F.linear(dq_a, dq_b).to(torch.bfloat16)
-        acts[e] = (tok, slot, _swiglu_bf16(inter))
+        inter = F.linear(dq_a, dq_b)
+        if bias1 is not None:
+            inter = inter + bias1[e].float()
+        acts[e] = (tok, slot, _swiglu_bf16(inter.to(torch.bfloat16)))
 
     if quant_mode == QUANT_TENSOR:
         # one scale for the whole intermediate (csrc/moe_kernels.h:136-204), torch formula
@@ -236,7 +248,10 @@ def moe_layer_fp8(a_q, a_s, b_q, b_s, b1_q, b1_s, m_indices, E: int, quant_mode:
             dq_act = q.float() * sf_all
             dq_b1 = b1_q[e].float() * b1_s[e]
         inter_store[e] = (q, s)
-        d[tok, slot] = F.linear(dq_act, dq_b1).to(torch.bfloat16)
+        out = F.linear(dq_act, dq_b1)
+        if bias2 is not None:
+            out = out + bias2[e].float()
+        d[tok, slot] = out.to(torch.bfloat16)
     if return_intermediate:
         return d, inter_store
     return d

@@ -69,7 +69,12 @@ def test_plugin_descriptor_host_calls():
     assert plugin.MoePlugin.deserialize(blob).fields == f
     with pytest.raises(RuntimeError, match="expected 36"):
         plugin.MoePlugin.deserialize(blob[:-4])
-    for bad in (dict(use_bias=1), dict(type=plugin.DT_FLOAT, quant_mode=0),
+    # use_bias = 1 and FLOAT operands (with FLOAT output) are accepted
+    assert plugin.MoePlugin(8, 2, 1024, 2048, 64, use_bias=1).fields["use_bias"] == 1
+    f32 = plugin.MoePlugin(8, 2, 1024, 2048, 64, type=plugin.DT_FLOAT, output_type=plugin.DT_FLOAT, quant_mode=0)
+    assert f32.workspace_size(64) == lib.dqmoe_moe_workspace_bytes_f32(64, 1024, 2048, 8, 2)
+    for bad in (dict(use_bias=2), dict(type=plugin.DT_FLOAT, quant_mode=0),
+                dict(type=plugin.DT_FLOAT, quant_mode=512, output_type=plugin.DT_FLOAT),
                 dict(type=plugin.DT_HALF, quant_mode=0, output_type=plugin.DT_BF16),
                 dict(type=plugin.DT_HALF, quant_mode=512, output_type=plugin.DT_HALF),
                 dict(type=plugin.DT_BF16, quant_mode=512), dict(type=plugin.DT_FP8, quant_mode=0),

@@ -116,3 +116,76 @@ def test_expert_range_and_splits():
         ep.expert_range(0, 3, 8)
     counts = torch.tensor([1, 2, 3, 4, 5, 6], dtype=torch.int32)
     assert ep.send_splits(counts, 3) == [3, 7, 11]
+
+
+def _mismatch_worker(rank, world, init_file, results):
+    sys.path.insert(0, ROOT)
+    from dqmoe_b200 import ep
+    dist.init_process_group("gloo", init_method=f"file://{init_file}", rank=rank, world_size=world)
+    try:
+        try:
+            ep.ExpertParallelLayer(4 if rank == 0 else 8, 2, 0, (None, None, None, None), OracleBackend())
+            results[rank] = "no error"
+        except RuntimeError as e:
+            results[rank] = str(e)
+    finally:
+        dist.destroy_process_group()
+
+
+def test_ranks_built_with_different_expert_counts_raise_on_every_rank():
+    with tempfile.TemporaryDirectory() as tmp:
+        results = mp.Manager().dict()
+        mp.spawn(_mismatch_worker, args=(2, os.path.join(tmp, "init"), results), nprocs=2, join=True)
+        for rank in range(2):
+            assert "all ranks built the layer with the same sizes" in results[rank], results[rank]
+            assert "'E': (4, 8)" in results[rank]
+
+
+def _leaving_worker(rank, world, init_file, results):
+    """Rank 1 leaves between two steps (no call in flight); rank 0's next step must end with an error,
+    not hang: the process group carries a short timeout."""
+    import datetime
+    sys.path.insert(0, ROOT)
+    sys.path.insert(0, os.path.join(ROOT, "tests"))
+    from dqmoe_b200 import ep
+    from helpers import make_inputs
+    torch.set_num_threads(2)
+    dist.init_process_group("gloo", init_method=f"file://{init_file}", rank=rank, world_size=world,
+                            timeout=datetime.timedelta(seconds=5))
+    E, T, H, I, k = 4, 16, 128, 128, 2
+    _, b, b1, _, _ = make_inputs(100, T, H, I, E, k, 1.0, 0.05)
+    a, _, _, _, m_indices = make_inputs(200 + rank, T, H, I, E, k, 1.0, 0.05)
+    lo, hi = ep.expert_range(rank, world, E)
+    layer = ep.ExpertParallelLayer(E, k, 0, (b[lo:hi].contiguous(), None, b1[lo:hi].contiguous(), None), OracleBackend())
+    layer.forward(a, None, m_indices)  # step 1: both ranks
+    if rank == 1:
+        results[rank] = "left after step 1"
+        dist.destroy_process_group()
+        return
+    try:
+        layer.forward(a, None, m_indices)  # step 2: the peer is gone
+        results[rank] = "no error"
+    except RuntimeError as e:
+        results[rank] = "error: " + str(e)[:200]
+    try:
+        dist.destroy_process_group()
+    except Exception:
+        pass
+
+
+def test_a_rank_leaving_between_steps_ends_the_next_step_with_an_error():
+    with tempfile.TemporaryDirectory() as tmp:
+        results = mp.Manager().dict()
+        mp.spawn(_leaving_worker, args=(2, os.path.join(tmp, "init"), results), nprocs=2, join=True)
+        assert results[1] == "left after step 1"
+        assert results[0].startswith("error: "), results[0]
+
+
+def test_send_splits_that_do_not_match_the_rows_raise():
+    """A split-size list that does not add up to the rows sent is refused on the host, before any exchange."""
+    from dqmoe_b200 import ep
+    layer = object.__new__(ep.ExpertParallelLayer)
+    layer.group = None
+    x = torch.zeros(10, 4)
+    with pytest.raises(RuntimeError, match="split sizes"):
+        ep.ExpertParallelLayer.all_to_all_rows(layer, x, 10, [4, 4], [5, 5])

@@ -82,3 +82,79 @@ def test_expert_parallel_matches_single_gpu(mode, impl, world):
             assert status == 0
             assert cos >= 0.9999, (rank, cos)
             assert same and wsame, (rank, cos)
+
+
+def _failure_worker(rank, world, init_file, results):
+    """Failure paths of the peer exchange on one GPU, none of which faults or hangs it: a receive buffer that is
+    too small (status 202, nothing moved), flag waits that run out after a millisecond (201, 211), and a clean
+    call on the same context afterwards."""
+    import ctypes
+    sys.path.insert(0, ROOT)
+    sys.path.insert(0, os.path.join(ROOT, "tests"))
+    os.environ.setdefault("NCCL_NVLS_ENABLE", "0")
+    from dqmoe_b200 import _lib, ep, ops
+    from helpers import make_inputs
+    torch.cuda.set_device(rank)
+    dev = torch.device("cuda", rank)
+    dist.init_process_group("nccl", init_method=f"file://{init_file}", rank=rank, world_size=world, device_id=dev)
+    try:
+        lib = _lib.load()
+        E, T, H, I, k = 8, 300, 512, 384, 2
+        a, b, b1, _, m_indices = make_inputs(300, T, H, I, E, k, 1.0, 0.05)
+        full = (b.to(dev), None, b1.to(dev), None)
+        aq, idx = a.to(dev), m_indices.to(dev)
+        ws = torch.empty(ops.moe_workspace_bytes(T, H, I, E, k, 0), dtype=torch.uint8, device=dev)
+        ref = torch.zeros(T, k, H, dtype=torch.bfloat16, device=dev)
+        ops.moe_forward(aq, None, full[0], None, full[2], None, ref, idx, ws, 0)
+        out = {}
+        # 1. capacity smaller than the rows received: every rank sends and computes nothing, status 202
+        small = ep.PeerExpertParallelLayer(T, H, I, E, k, 0, full, ops, capacity_rows=128)
+        d = small.forward(aq, None, idx, zero_dropped=True)
+        torch.cuda.synchronize()
+        out["overflow_untouched"] = bool(torch.count_nonzero(d) == 0)
+        try:
+            small.check_status()
+            out["overflow_raises"] = False
+        except RuntimeError as e:
+            out["overflow_raises"] = "202" in str(e) and "capacity_rows=128" in str(e)
+        out["status_cleared"] = ops.device_status() == 0
+        # the same layer object keeps working for a routing that fits: all rows to one slot of one expert pair
+        few = idx.clone()
+        few[64:] = -1
+        d = small.forward(aq, None, few, zero_dropped=True)
+        torch.cuda.synchronize()
+        out["fits_after_overflow"] = ops.device_status() == 0 and bool(torch.equal(d[:64], ref[:64])) and \
+            bool(torch.count_nonzero(d[64:]) == 0)
+        # 2. waits that run out: a flag nobody sets, limit of about one millisecond
+        _lib.check(lib.dqmoe_ep_set_wait_limit(2_000_000))
+        layer = ep.PeerExpertParallelLayer(T, H, I, E, k, 0, full, ops)
+        vp = ctypes.c_void_p
+        stream = vp(torch.cuda.current_stream(dev).cuda_stream)
+        _lib.check(lib.dqmoe_ep_wait(vp(layer.local["flags"]), 1, world, 987654, stream))
+        out["wait_status"] = ops.device_status()
+        _lib.check(lib.dqmoe_ep_wait(vp(layer.local["flags"]), 2, world, 987654, stream))
+        out["wait2_status"] = ops.device_status()
+        _lib.check(lib.dqmoe_ep_plan(vp(layer.local["cnt"]), vp(layer.local["flags"]), E, rank, world, 987654, layer.cap,
+                                     vp(layer.send_base.data_ptr()), vp(layer.rx_offsets.data_ptr()),
+                                     vp(layer.rx_mtiles.data_ptr()), stream))
+        out["plan_status"] = ops.device_status()
+        out["plan_void"] = int(layer.send_base[E].item()) == 1 and int(layer.rx_offsets[-1].item()) == 0
+        _lib.check(lib.dqmoe_ep_set_wait_limit(0))
+        # 3. the context is intact: a normal call is bit-identical to the single-GPU layer
+        d = layer.forward(aq, None, idx, zero_dropped=True)
+        torch.cuda.synchronize()
+        out["clean_after"] = ops.device_status() == 0 and bool(torch.equal(d, ref))
+        results[rank] = out
+    finally:
+        dist.destroy_process_group()
+
+
+def test_peer_exchange_failure_paths_report_status_and_leave_the_context_usable():
+    with tempfile.TemporaryDirectory() as tmp:
+        results = mp.Manager().dict()
+        mp.spawn(_failure_worker, args=(1, os.path.join(tmp, "init"), results), nprocs=1, join=True)
+        r = results[0]
+        assert r["overflow_untouched"] and r["overflow_raises"] and r["status_cleared"], r
+        assert r["fits_after_overflow"], r
+        assert r["wait_status"] == 211 and r["wait2_status"] == 212 and r["plan_status"] == 201 and r["plan_void"], r
+        assert r["clean_after"], r
