@@ -198,22 +198,22 @@ __device__ __forceinline__ void store_chunk(uint4* stage, const uint32_t (&packe
 // of the reference's template (csrc/pybind11_register.h:104-151, csrc/moe_gemm_template.h:487-569). fp32
 // operands go through the tensor cores as TF32 (kind::tf32), as the reference's float instantiation does
 // on its mma.sync path; intermediates and outputs then stay fp32.
-enum Elem : int { kBf16 = 0, kHalf = 1, kF32 = 2 };
+enum Elem : int { kElemBf16 = 0, kElemHalf = 1, kElemF32 = 2 };
 
 // Rounding to the storage type of the intermediate and the output.
 template <int kElem>
 __device__ __forceinline__ float round16(float x) {
-    if constexpr (kElem == kHalf)
+    if constexpr (kElem == kElemHalf)
         return __half2float(__float2half_rn(x));
-    else if constexpr (kElem == kF32)
+    else if constexpr (kElem == kElemF32)
         return x;
     else
         return bf_round_cvt(x);
 }
 template <int kElem>
 __device__ __forceinline__ uint32_t pack16x2(float lo, float hi) {
-    static_assert(kElem != kF32, "fp32 outputs are not packed");
-    if constexpr (kElem == kHalf) {
+    static_assert(kElem != kElemF32, "fp32 outputs are not packed");
+    if constexpr (kElem == kElemHalf) {
         const __half2 h = __floats2half2_rn(lo, hi);
         return *reinterpret_cast<const uint32_t*>(&h);
     } else {
@@ -231,7 +231,7 @@ __device__ __forceinline__ void ffma2(float& a0, float& a1, uint32_t x0, uint32_
 
 // kBox = weight rows per TMA box (two boxes per stage, 2*kBox accumulator columns): 128 for
 // throughput, 64 when a launch would otherwise have fewer tiles than SMs (decode shapes).
-template <bool kFp8, int kMode, bool kGated, bool kPair, int kBox, int kElem = kBf16>
+template <bool kFp8, int kMode, bool kGated, bool kPair, int kBox, int kElem = kElemBf16>
 __global__ void __launch_bounds__(kThreads, 1)
 moe_GemmGrouped_GemmUniversal_tcgen05(const __grid_constant__ CUtensorMap tma_a,
                                       const __grid_constant__ CUtensorMap tma_b, const Params p) {
@@ -241,11 +241,11 @@ moe_GemmGrouped_GemmUniversal_tcgen05(const __grid_constant__ CUtensorMap tma_a,
 
     const int warp = threadIdx.x >> 5;
     const int lane = threadIdx.x & 31;
-    constexpr int kBKElems = kFp8 ? kBKBytes : (kElem == kF32 ? kBKBytes / 4 : kBKBytes / 2);
-    constexpr int kKind = kFp8 ? 0 : (kElem == kF32 ? 2 : 1);  // kind::f8f6f4, kind::f16, kind::tf32
+    constexpr int kBKElems = kFp8 ? kBKBytes : (kElem == kElemF32 ? kBKBytes / 4 : kBKBytes / 2);
+    constexpr int kKind = kFp8 ? 0 : (kElem == kElemF32 ? 2 : 1);  // kind::f8f6f4, kind::f16, kind::tf32
     static_assert(kBox == 128 || (kBox == 64 && !kPair && kMode != kBlock), "narrow tiles: single CTA, non-block modes");
-    static_assert(kElem == kBf16 || (!kFp8 && kMode == kNone), "fp16 / fp32 operands: the unquantised path only");
-    static_assert(kElem != kF32 || (!kPair && kBox == 128), "fp32 operands: single-CTA 256-column tiles only");
+    static_assert(kElem == kElemBf16 || (!kFp8 && kMode == kNone), "fp16 / fp32 operands: the unquantised path only");
+    static_assert(kElem != kElemF32 || (!kPair && kBox == 128), "fp32 operands: single-CTA 256-column tiles only");
     constexpr int kN = 2 * kBox;                      // accumulator columns of a tile
     constexpr int kStageSz = kPair ? kStageBytesPair : kABytes + kN * kBKBytes;
     constexpr int kNumStages = (kStages * kStageBytes) / kStageSz;   // 4 (wide), 6 (pairs, narrow)
@@ -360,7 +360,7 @@ moe_GemmGrouped_GemmUniversal_tcgen05(const __grid_constant__ CUtensorMap tma_a,
         if (lane == 0 && leader) {
             // operand format code: e4m3 = 0 (kind::f8f6f4); f16 = 0, bf16 = 1 (kind::f16); tf32 = 2 (kind::tf32)
             constexpr uint32_t idesc =
-                ptx::make_idesc(kFp8 || kElem == kHalf ? 0u : (kElem == kF32 ? 2u : 1u), kPair ? 2 * kBM : kBM, kN);
+                ptx::make_idesc(kFp8 || kElem == kElemHalf ? 0u : (kElem == kElemF32 ? 2u : 1u), kPair ? 2 * kBM : kBM, kN);
             // issue one K step; in a pair the same call drives both CTAs' tensor cores
             auto mma_step = [&](uint32_t d_tmem, uint32_t a_addr, uint32_t b_addr, uint32_t accumulate) {
                 if constexpr (kPair)
@@ -516,7 +516,7 @@ moe_GemmGrouped_GemmUniversal_tcgen05(const __grid_constant__ CUtensorMap tma_a,
                 float row_scale = 1.0f;
                 if constexpr (kMode == kTensor) row_scale = p.sa[0] * p.sb[tl.e];
                 if constexpr (kMode == kChannel) row_scale = p.sa[grow_ld];
-                constexpr int kOutBytes = kElem == kF32 ? 4 : 2;
+                constexpr int kOutBytes = kElem == kElemF32 ? 4 : 2;
 
                 if constexpr (kGated) {
                     // columns [h*kHalf, (h+1)*kHalf) of the gate group and of the value group
@@ -543,7 +543,7 @@ moe_GemmGrouped_GemmUniversal_tcgen05(const __grid_constant__ CUtensorMap tma_a,
                         }
                         ptx::tmem_wait_ld(g);
                         ptx::tmem_wait_ld(v);
-                        uint32_t packed[kElem == kF32 ? 32 : 16];
+                        uint32_t packed[kElem == kElemF32 ? 32 : 16];
                         // This epilogue runs beside the next tile's MMAs; its roundings use the conversion
                         // instruction (one issue slot each), which measured faster here than bf_round.
 #pragma unroll
@@ -570,12 +570,12 @@ moe_GemmGrouped_GemmUniversal_tcgen05(const __grid_constant__ CUtensorMap tma_a,
                                 a4[u] = act;
                                 if (col0 + i + u < I_or_H) amax_local = fmaxf(amax_local, fabsf(act));
                             }
-                            if constexpr (kElem == kF32) {
+                            if constexpr (kElem == kElemF32) {
 #pragma unroll
                                 for (int u = 0; u < 4; ++u) packed[i + u] = __float_as_uint(a4[u]);
-                            } else if constexpr (kElem == kHalf) {
-                                packed[i >> 1] = pack16x2<kHalf>(a4[0], a4[1]);
-                                packed[(i >> 1) + 1] = pack16x2<kHalf>(a4[2], a4[3]);
+                            } else if constexpr (kElem == kElemHalf) {
+                                packed[i >> 1] = pack16x2<kElemHalf>(a4[0], a4[1]);
+                                packed[(i >> 1) + 1] = pack16x2<kElemHalf>(a4[2], a4[3]);
                             } else {
                                 packed[i >> 1] = pack_bf16x2_exact(a4[0], a4[1]);  // act is already rounded to bf16
                                 packed[(i >> 1) + 1] = pack_bf16x2_exact(a4[2], a4[3]);
@@ -583,7 +583,7 @@ moe_GemmGrouped_GemmUniversal_tcgen05(const __grid_constant__ CUtensorMap tma_a,
                         }
                         uint8_t* optr = row_ok ? static_cast<uint8_t*>(p.out) + (size_t(grow) * I_or_H + col0) * kOutBytes
                                                : nullptr;
-                        store_chunk<kElem == kF32>(st.stage[warp - 4], packed, optr, I_or_H - col0, lane);
+                        store_chunk<kElem == kElemF32>(st.stage[warp - 4], packed, optr, I_or_H - col0, lane);
                     }
                     if constexpr (kMode == kChannel) {
                         if (row_ok) atomic_max_nonneg(p.amax + grow, amax_local);
@@ -616,7 +616,7 @@ moe_GemmGrouped_GemmUniversal_tcgen05(const __grid_constant__ CUtensorMap tma_a,
                             __syncwarp();
                         }
                         ptx::tmem_wait_ld(r);
-                        uint32_t packed[kElem == kF32 ? 32 : 16];
+                        uint32_t packed[kElem == kElemF32 ? 32 : 16];
 #pragma unroll
                         for (int i = 0; i < 32; i += 4) {
                             float sc[4] = {row_scale, row_scale, row_scale, row_scale};
@@ -632,7 +632,7 @@ moe_GemmGrouped_GemmUniversal_tcgen05(const __grid_constant__ CUtensorMap tma_a,
                             float o4[4];
 #pragma unroll
                             for (int u = 0; u < 4; ++u) o4[u] = __uint_as_float(r[i + u]) * sc[u] + bb[u];
-                            if constexpr (kElem == kF32) {
+                            if constexpr (kElem == kElemF32) {
 #pragma unroll
                                 for (int u = 0; u < 4; ++u) packed[i + u] = __float_as_uint(o4[u]);
                             } else {
@@ -640,7 +640,7 @@ moe_GemmGrouped_GemmUniversal_tcgen05(const __grid_constant__ CUtensorMap tma_a,
                                 packed[(i >> 1) + 1] = pack16x2<kElem>(o4[2], o4[3]);
                             }
                         }
-                        store_chunk<kElem == kF32>(st.stage[warp - 4], packed,
+                        store_chunk<kElem == kElemF32>(st.stage[warp - 4], packed,
                                                    row_ok && orow_idx >= 0 ? orow + size_t(col0) * kOutBytes : nullptr,
                                                    I_or_H - col0, lane);
                     }
@@ -869,7 +869,7 @@ static int make_map(CUtensorMap* map, const void* base, int esz, uint64_t rows, 
     return DQMOE_OK;
 }
 
-template <bool kFp8, int kMode, bool kGated, bool kPair, int kBox, int kElem = kBf16>
+template <bool kFp8, int kMode, bool kGated, bool kPair, int kBox, int kElem = kElemBf16>
 static int launch(const CUtensorMap& ma, const CUtensorMap& mb, const Params& p, cudaStream_t stream) {
     auto kern = moe_GemmGrouped_GemmUniversal_tcgen05<kFp8, kMode, kGated, kPair, kBox, kElem>;
     // the shared-memory opt-in is per function and per device
@@ -916,20 +916,20 @@ static bool use_pairs(int n, int E, int quant_mode) {
     return quant_mode != DQMOE_QUANT_FP8_BLOCK && n / E >= 512;
 }
 
-// elem: element type of the unquantised path (kBf16 / kHalf / kF32); bias: [E, gated ? 2N : N] fp32 or nullptr.
+// elem: element type of the unquantised path (kElemBf16 / kElemHalf / kElemF32); bias: [E, gated ? 2N : N] fp32 or nullptr.
 int grouped_gemm(const void* a, const float* a_scale, const void* w, const float* w_scale, const int* offsets,
                  const int* mtile_prefix, int n, int N, int K, int E, int quant_mode, int gated, void* out,
                  float* out_scale, float* amax, const int* dest_to_src, const void* row_dst, cudaStream_t stream,
                  int elem, const float* bias) {
-    DQ_CHECK(elem == kBf16 || ((elem == kHalf || elem == kF32) && quant_mode == DQMOE_QUANT_NONE));
+    DQ_CHECK(elem == kElemBf16 || ((elem == kElemHalf || elem == kElemF32) && quant_mode == DQMOE_QUANT_NONE));
     DQ_CHECK(quant_mode == DQMOE_QUANT_NONE || quant_mode == DQMOE_QUANT_FP8_TENSOR ||
              quant_mode == DQMOE_QUANT_FP8_CHANNEL || quant_mode == DQMOE_QUANT_FP8_BLOCK);
     DQ_CHECK(n >= 0 && N > 0 && K > 0 && E > 0 && E <= kMaxExperts);
     if (n == 0) return DQMOE_OK;
     const bool fp8 = quant_mode != DQMOE_QUANT_NONE;
-    const int esz = fp8 ? 1 : (elem == kF32 ? 4 : 2);
+    const int esz = fp8 ? 1 : (elem == kElemF32 ? 4 : 2);
     DQ_CHECK_FMT((size_t(K) * esz) % 16 == 0, "K=%d: rows must be a multiple of 16 bytes", K);
-    DQ_CHECK_FMT(N % (gated && quant_mode == DQMOE_QUANT_FP8_BLOCK ? 16 : (elem == kF32 ? 4 : 8)) == 0,
+    DQ_CHECK_FMT(N % (gated && quant_mode == DQMOE_QUANT_FP8_BLOCK ? 16 : (elem == kElemF32 ? 4 : 8)) == 0,
                  "N=%d: output rows must be 16-byte vectors", N);
     DQ_CHECK(is_aligned(a, 16) && is_aligned(w, 16) && is_aligned(out, 16) && is_aligned(row_dst, 8));
     DQ_CHECK(a != nullptr && w != nullptr && (out != nullptr || row_dst != nullptr) && offsets != nullptr && mtile_prefix != nullptr);
@@ -940,12 +940,12 @@ int grouped_gemm(const void* a, const float* a_scale, const void* w, const float
 
     // Tile width: 256 accumulator columns, or 128 when the launch would leave many SMs without a tile.
     // The row-tile count is known only on the device; ceil(n/128) + min(E, n) - 1 bounds it.
-    const bool pair = elem != kF32 && use_pairs(n, E, quant_mode);
+    const bool pair = elem != kElemF32 && use_pairs(n, E, quant_mode);
     const int mtiles_max = ceil_div(n, kBM) + (E < n ? E : n) - 1;
     const int wide_tiles = mtiles_max * (gated ? ceil_div(N, kBoxRows) : ceil_div(N, kUmmaN));
     // measured on decode shapes: 128-column tiles win when 256-column tiles would fill at most half of
     // the SMs, or when there are at most two row tiles (one or two tokens); otherwise 256 columns win
-    const bool narrow = quant_mode != DQMOE_QUANT_FP8_BLOCK && !pair && elem != kF32 &&
+    const bool narrow = quant_mode != DQMOE_QUANT_FP8_BLOCK && !pair && elem != kElemF32 &&
                         (2 * wide_tiles <= sm_count() || (mtiles_max <= 2 && wide_tiles < 2 * sm_count()));
     const int box = narrow ? 64 : kBoxRows;
 
@@ -984,14 +984,14 @@ int grouped_gemm(const void* a, const float* a_scale, const void* w, const float
     return pair ? DQ_GEMM_LAUNCH(FP8, MODE, true, 128)                                        \
                 : (narrow ? DQ_GEMM_LAUNCH(FP8, MODE, false, 64) : DQ_GEMM_LAUNCH(FP8, MODE, false, 128))
 #define DQ_GEMM_LAUNCH_F16(PAIR, BOX)                                                          \
-    (gated ? launch<false, kNone, true, PAIR, BOX, kHalf>(ma, mb, p, stream)                   \
-           : launch<false, kNone, false, PAIR, BOX, kHalf>(ma, mb, p, stream))
-    if (elem == kHalf)
+    (gated ? launch<false, kNone, true, PAIR, BOX, kElemHalf>(ma, mb, p, stream)                   \
+           : launch<false, kNone, false, PAIR, BOX, kElemHalf>(ma, mb, p, stream))
+    if (elem == kElemHalf)
         return pair ? DQ_GEMM_LAUNCH_F16(true, 128) : (narrow ? DQ_GEMM_LAUNCH_F16(false, 64) : DQ_GEMM_LAUNCH_F16(false, 128));
 #undef DQ_GEMM_LAUNCH_F16
-    if (elem == kF32)
-        return gated ? launch<false, kNone, true, false, 128, kF32>(ma, mb, p, stream)
-                     : launch<false, kNone, false, false, 128, kF32>(ma, mb, p, stream);
+    if (elem == kElemF32)
+        return gated ? launch<false, kNone, true, false, 128, kElemF32>(ma, mb, p, stream)
+                     : launch<false, kNone, false, false, 128, kElemF32>(ma, mb, p, stream);
     switch (quant_mode) {
         case DQMOE_QUANT_NONE: DQ_GEMM_CASE(false, kNone);
         case DQMOE_QUANT_FP8_TENSOR: DQ_GEMM_CASE(true, kTensor);
@@ -1011,13 +1011,13 @@ extern "C" int dqmoe_grouped_gemm(const void* a, const float* a_scale, const voi
                                   const int32_t* dest_to_src, dqmoe_stream_t stream) {
     return dq::gemm::grouped_gemm(a, a_scale, w, w_scale, offsets, mtile_prefix, n, N, K, E, quant_mode, gated, out,
                                   out_scale, amax, dest_to_src, nullptr, static_cast<cudaStream_t>(stream),
-                                  dq::gemm::kBf16, nullptr);
+                                  dq::gemm::kElemBf16, nullptr);
 }
 
 extern "C" int dqmoe_grouped_gemm_rows(const void* a, const float* a_scale, const void* w, const float* w_scale,
                                        const int32_t* offsets, const int32_t* mtile_prefix, int n, int N, int K, int E,
                                        int quant_mode, const void* row_dst, dqmoe_stream_t stream) {
     return dq::gemm::grouped_gemm(a, a_scale, w, w_scale, offsets, mtile_prefix, n, N, K, E, quant_mode, 0, nullptr,
-                                  nullptr, nullptr, nullptr, row_dst, static_cast<cudaStream_t>(stream), dq::gemm::kBf16,
+                                  nullptr, nullptr, nullptr, row_dst, static_cast<cudaStream_t>(stream), dq::gemm::kElemBf16,
                                   nullptr);
 }

@@ -21,7 +21,7 @@ int grouped_gemm(const void* a, const float* a_scale, const void* w, const float
                  const int* mtile_prefix, int n, int N, int K, int E, int quant_mode, int gated, void* out,
                  float* out_scale, float* amax, const int* dest_to_src, const void* row_dst, cudaStream_t stream,
                  int elem = 0, const float* bias = nullptr);
-enum Elem : int { kBf16 = 0, kHalf = 1, kF32 = 2 };  // element type of the unquantised path
+enum Elem : int { kElemBf16 = 0, kElemHalf = 1, kElemF32 = 2 };  // element type of the unquantised path
 }  // namespace gemm
 
 namespace decode {
@@ -47,10 +47,10 @@ static bool valid_mode(int q) {
            q == DQMOE_QUANT_FP8_BLOCK;
 }
 
-static Layout make_layout(int T, int H, int I, int E, int k, int quant_mode, int elem = gemm::kBf16) {
+static Layout make_layout(int T, int H, int I, int E, int k, int quant_mode, int elem = gemm::kElemBf16) {
     Layout L{};
     const size_t n = size_t(T) * k;
-    const size_t esz = quant_mode != DQMOE_QUANT_NONE ? 1 : (elem == gemm::kF32 ? 4 : 2);
+    const size_t esz = quant_mode != DQMOE_QUANT_NONE ? 1 : (elem == gemm::kElemF32 ? 4 : 2);
     size_t off = 0;
     auto add = [&](size_t bytes) {
         const size_t at = off;
@@ -124,8 +124,8 @@ static int moe_forward_impl(const void* a, const float* a_scale, const void* b, 
                  workspace);
     const bool fp8 = quant_mode != DQMOE_QUANT_NONE;
     if (fp8) DQ_CHECK(a_scale != nullptr && b_scale != nullptr && b1_scale != nullptr);
-    DQ_CHECK(elem == gemm::kBf16 || !fp8);
-    const size_t esz = fp8 ? 1 : (elem == gemm::kF32 ? 4 : 2);
+    DQ_CHECK(elem == gemm::kElemBf16 || !fp8);
+    const size_t esz = fp8 ? 1 : (elem == gemm::kElemF32 ? 4 : 2);
     DQ_CHECK_FMT((H * esz) % 16 == 0 && (I * esz) % 16 == 0,
                  "hidden_size=%d and inter_size=%d rows must be multiples of 16 bytes", H, I);
     DQ_CHECK(int64_t(T) * k < (int64_t(1) << 31));
@@ -147,7 +147,7 @@ static int moe_forward_impl(const void* a, const float* a_scale, const void* b, 
     void* act_bf16 = ws + L.act_bf16;
     float* amax = reinterpret_cast<float*>(ws + L.amax);
 
-    if (elem == gemm::kBf16 && bias1 == nullptr && bias2 == nullptr && n <= layer::kDecodeRows &&
+    if (elem == gemm::kElemBf16 && bias1 == nullptr && bias2 == nullptr && n <= layer::kDecodeRows &&
         (quant_mode == DQMOE_QUANT_NONE || quant_mode == DQMOE_QUANT_FP8_TENSOR) &&
         size_t(H > I ? H : I) * sizeof(float) <= 200 * 1024)
         return decode::forward(a, a_scale, b, b_scale, b1, b1_scale, d, m_indices, fp8 ? act_bf16 : act, amax, T, H, I,
@@ -186,7 +186,7 @@ int dqmoe_moe_forward(const void* a, const float* a_scale, const void* b, const 
                       dqmoe_stream_t stream) {
     (void) fused;
     return moe_forward_impl(a, a_scale, b, b_scale, b1, b1_scale, d, m_indices, workspace, workspace_bytes, T, H, I, E, k,
-                            quant_mode, gemm::kBf16, nullptr, nullptr, static_cast<cudaStream_t>(stream));
+                            quant_mode, gemm::kElemBf16, nullptr, nullptr, static_cast<cudaStream_t>(stream));
 }
 
 int dqmoe_moe_forward_bias(const void* a, const float* a_scale, const void* b, const float* b_scale, const void* b1,
@@ -194,33 +194,33 @@ int dqmoe_moe_forward_bias(const void* a, const float* a_scale, const void* b, c
                            const int32_t* m_indices, void* workspace, size_t workspace_bytes, int T, int H, int I, int E,
                            int k, int quant_mode, dqmoe_stream_t stream) {
     return moe_forward_impl(a, a_scale, b, b_scale, b1, b1_scale, d, m_indices, workspace, workspace_bytes, T, H, I, E, k,
-                            quant_mode, gemm::kBf16, bias1, bias2, static_cast<cudaStream_t>(stream));
+                            quant_mode, gemm::kElemBf16, bias1, bias2, static_cast<cudaStream_t>(stream));
 }
 
 int dqmoe_moe_forward_f16(const void* a, const void* b, const void* b1, void* d, const int32_t* m_indices,
                           void* workspace, size_t workspace_bytes, int T, int H, int I, int E, int k,
                           dqmoe_stream_t stream) {
     return moe_forward_impl(a, nullptr, b, nullptr, b1, nullptr, d, m_indices, workspace, workspace_bytes, T, H, I, E, k,
-                            DQMOE_QUANT_NONE, gemm::kHalf, nullptr, nullptr, static_cast<cudaStream_t>(stream));
+                            DQMOE_QUANT_NONE, gemm::kElemHalf, nullptr, nullptr, static_cast<cudaStream_t>(stream));
 }
 
 size_t dqmoe_moe_workspace_bytes_f32(int T, int H, int I, int E, int k) {
     if (T < 0 || H <= 0 || I <= 0 || E <= 0 || k <= 0) return 0;
-    return layer::make_layout(T, H, I, E, k, DQMOE_QUANT_NONE, gemm::kF32).total;
+    return layer::make_layout(T, H, I, E, k, DQMOE_QUANT_NONE, gemm::kElemF32).total;
 }
 
 int dqmoe_moe_forward_f32(const void* a, const void* b, const void* b1, const float* bias1, const float* bias2, void* d,
                           const int32_t* m_indices, void* workspace, size_t workspace_bytes, int T, int H, int I, int E,
                           int k, dqmoe_stream_t stream) {
     return moe_forward_impl(a, nullptr, b, nullptr, b1, nullptr, d, m_indices, workspace, workspace_bytes, T, H, I, E, k,
-                            DQMOE_QUANT_NONE, gemm::kF32, bias1, bias2, static_cast<cudaStream_t>(stream));
+                            DQMOE_QUANT_NONE, gemm::kElemF32, bias1, bias2, static_cast<cudaStream_t>(stream));
 }
 
 int dqmoe_moe_forward_f16_bias(const void* a, const void* b, const void* b1, const float* bias1, const float* bias2,
                                void* d, const int32_t* m_indices, void* workspace, size_t workspace_bytes, int T, int H,
                                int I, int E, int k, dqmoe_stream_t stream) {
     return moe_forward_impl(a, nullptr, b, nullptr, b1, nullptr, d, m_indices, workspace, workspace_bytes, T, H, I, E, k,
-                            DQMOE_QUANT_NONE, gemm::kHalf, bias1, bias2, static_cast<cudaStream_t>(stream));
+                            DQMOE_QUANT_NONE, gemm::kElemHalf, bias1, bias2, static_cast<cudaStream_t>(stream));
 }
 
 // ---------------------------------------------------------------------------------------------

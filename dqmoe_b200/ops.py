@@ -104,6 +104,24 @@ def moe_forward(a, a_scale, b, b_scale, b1, b1_scale, d, m_indices, workspace, q
                 quant_mode, _stream(a.device)))
 
 
+def moe_forward_f16(a, b, b1, d, m_indices, workspace, bias1=None, bias2=None) -> None:
+    """The unquantised layer on fp16 tensors into d[T, k, H] (fp16); see dqmoe_moe_forward_f16."""
+    lib = _lib.load()
+    for name, t in (("a", a), ("b", b), ("b1", b1), ("d", d), ("m_indices", m_indices), ("workspace", workspace)):
+        _cuda(t, name)
+    for name, t in (("a", a), ("b", b), ("b1", b1), ("d", d)):
+        if t.dtype != torch.float16:
+            raise RuntimeError(f"[ASSERT FAILED] ops.py  Condition: {name}.scalar_type() == at::kHalf")
+    T, H = a.shape
+    E, I, k = b.shape[0], b1.shape[2], d.shape[1]
+    _check_bias(bias1, E, 2 * I, "bias1")
+    _check_bias(bias2, E, H, "bias2")
+    with torch.cuda.device(a.device):
+        _lib.check(lib.dqmoe_moe_forward_f16_bias(_p(a), _p(b), _p(b1), _p(bias1), _p(bias2), _p(d), _p(m_indices),
+                                                  _p(workspace), workspace.numel() * workspace.element_size(), T, H,
+                                                  I, E, k, _stream(a.device)))
+
+
 def moe_workspace_bytes_f32(T: int, H: int, I: int, E: int, k: int) -> int:
     return int(_lib.load().dqmoe_moe_workspace_bytes_f32(T, H, I, E, k))
 

@@ -62,7 +62,7 @@ def test_only_one_bias_given(ops):
 
 @pytest.mark.parametrize("with_bias", [False, True])
 @pytest.mark.parametrize("E,T,H,I,k", [(8, 96, 512, 384, 2), (4, 700, 384, 640, 2), (3, 5, 192, 160, 2), (1, 1, 16, 16, 1),
-                                       (2, 1300, 1000, 520, 3)])
+                                       (4, 1300, 1000, 520, 3)])
 def test_layer_fp32_operands(ops, E, T, H, I, k, with_bias):
     a, b, b1, _, idx = make_inputs(41, T, H, I, E, k, 1.0, 0.05)
     a, b, b1 = a.float(), b.float(), b1.float()
