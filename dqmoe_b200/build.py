@@ -90,6 +90,53 @@ def build(force: bool = False, verbose: bool = False) -> str:
     return LIB_PATH
 
 
+EXT_DIR = os.path.join(PKG_DIR, "dropin_ext")
+EXT_SRC = os.path.join(CSRC, "moe_test_pybind.cpp")
+
+
+def build_extension(force: bool = False) -> str:
+    """Compile the pybind11 `moe_test` extension module (csrc/moe_test_pybind.cpp) into
+    dqmoe_b200/dropin_ext/, linked against libdqmoe_b200.so next door and against torch (host code only: g++,
+    no nvcc). Put dqmoe_b200/dropin_ext on sys.path to import it; dqmoe_b200/dropin holds the ctypes
+    module of the same name for setups without a C++ compiler."""
+    import sysconfig
+
+    import torch
+    from torch.utils import cpp_extension as ce
+
+    build()
+    os.makedirs(EXT_DIR, exist_ok=True)
+    out = os.path.join(EXT_DIR, "moe_test" + sysconfig.get_config_var("EXT_SUFFIX"))
+    stamp_path = os.path.join(OBJ_DIR, "ext_stamp.txt")
+    h = hashlib.sha256()
+    for p in (EXT_SRC, os.path.join(os.path.dirname(PKG_DIR), "include", "dqmoe.h")):
+        with open(p, "rb") as f:
+            h.update(f.read())
+    h.update(torch.__version__.encode())
+    digest = h.hexdigest()
+    if not force and os.path.exists(out) and os.path.exists(stamp_path):
+        with open(stamp_path) as f:
+            if f.read().strip() == digest:
+                return out
+    cuda_home = os.environ.get("CUDA_HOME", "/usr/local/cuda")
+    cmd = ["g++", "-O2", "-std=c++17", "-shared", "-fPIC", "-DTORCH_EXTENSION_NAME=moe_test",
+           "-DTORCH_API_INCLUDE_EXTENSION_H", f"-D_GLIBCXX_USE_CXX11_ABI={int(torch._C._GLIBCXX_USE_CXX11_ABI)}",
+           "-I" + sysconfig.get_paths()["include"], "-I" + os.path.join(cuda_home, "include")]
+    cmd += ["-I" + p for p in ce.include_paths()]
+    cmd += [EXT_SRC, "-o", out, "-L" + PKG_DIR, "-l:libdqmoe_b200.so", "-Wl,-rpath,$ORIGIN/.."]
+    for lp in ce.library_paths():
+        cmd += ["-L" + lp, "-Wl,-rpath," + lp]
+    cmd += ["-lc10", "-lc10_cuda", "-ltorch_cpu", "-ltorch_cuda", "-ltorch", "-ltorch_python"]
+    res = subprocess.run(cmd, capture_output=True, text=True)
+    if res.returncode != 0:
+        raise RuntimeError(f"building the moe_test extension failed:\n{res.stdout[-3000:]}\n{res.stderr[-3000:]}")
+    with open(stamp_path, "w") as f:
+        f.write(digest)
+    return out
+
+
 if __name__ == "__main__":
     path = build(force="--force" in sys.argv, verbose="-v" in sys.argv)
     print(path)
+    if "--ext" in sys.argv:
+        print(build_extension(force="--force" in sys.argv))
