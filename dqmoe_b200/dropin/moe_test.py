@@ -15,7 +15,9 @@ import torch
 
 _ROOT = os.path.dirname(os.path.dirname(os.path.dirname(os.path.abspath(__file__))))
 if _ROOT not in sys.path:
-    sys.path.insert(0, _ROOT)
+    # at the end: the importing script's own modules (the reference's test/bench.py, test/util.py) must keep
+    # winning over same-named files at the root of this repository
+    sys.path.append(_ROOT)
 
 from dqmoe_b200 import ops as _ops  # noqa: E402
 
