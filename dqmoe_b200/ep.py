@@ -172,56 +172,6 @@ class ExpertParallelLayer:
         return be.finalize_weighted(d, route_weights)
 
 
-class ExpertParallelMoE:
-    """Bench/test helper: seeded synthetic weights of one workload, sharded by expert, quantised
-    on this rank's GPU with the library's own quantisers."""
-
-    def __init__(self, wl: dict, device, seed: int, ops, group=None):
-        from . import ops as _ops  # noqa: F401  (the CUDA front end; there is no other backend)
-        self.ops = ops
-        world, rank = dist.get_world_size(group), dist.get_rank(group)
-        E, H, I, mode = wl["E"], wl["H"], wl["I"], wl["mode"]
-        lo, hi = expert_range(rank, world, E)
-        b = torch.empty(hi - lo, 2 * I, H, device=device, dtype=torch.bfloat16)
-        b1 = torch.empty(hi - lo, H, I, device=device, dtype=torch.bfloat16)
-        for e in range(lo, hi):  # one generator per global expert: the model is the same for every world size
-            g = torch.Generator(device=device).manual_seed(seed * 100003 + e)
-            b[e - lo] = (torch.randn(2 * I, H, generator=g, device=device) * 0.02).to(torch.bfloat16)
-            b1[e - lo] = (torch.randn(H, I, generator=g, device=device) * 0.02).to(torch.bfloat16)
-        self.mode = mode
-        if mode == 1024:
-            wq = (*ops.per_block_cast_to_fp8(b), *ops.per_block_cast_to_fp8(b1))
-        elif mode == 512:
-            bq, bs = ops.per_channel_cast_to_fp8(b)
-            b1q, b1s = ops.per_channel_cast_to_fp8(b1)
-            wq = (bq, bs.view(hi - lo, -1), b1q, b1s.view(hi - lo, -1))
-        elif mode == 0:
-            wq = (b, None, b1, None)
-        else:
-            raise RuntimeError("[ASSERT FAILED] ep.py  Condition: mode in (0, 512, 1024)")
-        del b, b1
-        self.wq = wq  # (fc1 weights, scales, fc2 weights, scales) of this rank's experts
-        # exchange over peer memory; DQMOE_EP_IMPL=nccl selects the collectives
-        import os
-        use_peer = os.environ.get("DQMOE_EP_IMPL", "peer") == "peer" and world <= 8
-        if use_peer:
-            self.layer = PeerExpertParallelLayer(wl["T"], H, I, E, wl["k"], mode, wq, ops, group)
-        else:
-            self.layer = ExpertParallelLayer(E, wl["k"], mode, wq, CudaBackend(ops), group)
-        self.impl = "peer" if use_peer else "nccl"
-
-    def quantize_activations(self, x):
-        if self.mode == 1024:
-            return self.ops.per_token_block_cast_to_fp8(x)
-        if self.mode == 512:
-            q, s = self.ops.per_token_cast_to_fp8(x)
-            return q, s.view(-1)
-        return x, None
-
-    def forward(self, aq, a_scale, idx, weights):
-        return self.layer.forward(aq, a_scale, idx, weights)
-
-
 class PeerExpertParallelLayer:
     """Expert-parallel layer whose exchange runs over peer-mapped memory instead of collectives.
 
@@ -234,11 +184,13 @@ class PeerExpertParallelLayer:
     every result row directly into its home rank's d (NVLink stores) -> signal -> wait.
     bf16, block FP8 and channel FP8 modes (channel mode adds the per-row re-quantisation pass between
     the GEMMs, bounded by the received row count read on the device). The returned tensor aliases
-    the symmetric output buffer and is overwritten by the next call.
+    the symmetric output buffer and is overwritten by a later call: by the next one with out_buffers = 1,
+    by the one after it with out_buffers = 2 (calls then alternate between two output buffers, so a caller
+    can still be copying call i's result while call i + 1 runs).
     """
 
     def __init__(self, T: int, H: int, I: int, E: int, k: int, mode: int, weights_q, ops, group=None,
-                 capacity_rows: Optional[int] = None, capacity_factor: float = 2.0):
+                 capacity_rows: Optional[int] = None, capacity_factor: float = 2.0, out_buffers: int = 1):
         import ctypes
         import os
         os.environ.setdefault("TORCH_SYMM_MEM_DISABLE_MULTICAST", "1")  # plain peer loads/stores only
@@ -277,9 +229,12 @@ class PeerExpertParallelLayer:
         def up(x):
             return (x + 255) // 256 * 256
         off, self.off = 0, {}
+        if out_buffers not in (1, 2):
+            raise RuntimeError("[ASSERT FAILED] ep.py  Condition: out_buffers in (1, 2)")
+        self.out_buffers = out_buffers
         for name, nbytes in (("cnt", self.W * E * 4), ("flags", 3 * 8 * 4), ("rx_rows", self.cap * H * self.esz),
                              ("rx_scale", self.cap * max(self.scale_cols, 1) * 4), ("rx_home", self.cap * 4),
-                             ("d_out", self.n * H * 2)):
+                             ("d_out", self.n * H * 2), ("d_out1", self.n * H * 2 if out_buffers == 2 else 0)):
             self.off[name] = off
             off += up(nbytes)
         self.sym = symm_mem.empty(off, dtype=torch.uint8, device=dev)
@@ -301,7 +256,9 @@ class PeerExpertParallelLayer:
         if mode == 512:  # stage 1 writes bf16 and collects the row amax; a second pass quantises
             self.act_bf16 = torch.empty(self.cap * I, dtype=torch.bfloat16, device=dev)
             self.amax = torch.zeros(self.cap, dtype=torch.float32, device=dev)
-        self.d_out = self.sym[self.off["d_out"]:self.off["d_out"] + self.n * H * 2].view(torch.bfloat16).view(T, k, H)
+        self.d_outs = [self.sym[self.off[nm]:self.off[nm] + self.n * H * 2].view(torch.bfloat16).view(T, k, H)
+                       for nm in (("d_out", "d_out1") if out_buffers == 2 else ("d_out",))]
+        self.d_out = self.d_outs[0]
         self.epoch = 0
         torch.cuda.synchronize()
         dist.barrier(self.group)  # every rank's flags are zero before anyone publishes
@@ -317,31 +274,50 @@ class PeerExpertParallelLayer:
                                + (f": more than capacity_rows={self.cap} rows for one rank" if code == 202 else ""))
 
     def forward(self, a: torch.Tensor, a_scale: Optional[torch.Tensor], m_indices: torch.Tensor,
-                route_weights: Optional[torch.Tensor] = None, zero_dropped: bool = False) -> torch.Tensor:
+                route_weights: Optional[torch.Tensor] = None, zero_dropped: bool = False,
+                timeline: Optional[list] = None) -> torch.Tensor:
+        """timeline: a list that receives (phase name, CUDA event recorded after the phase's launches) pairs,
+        for measuring where a call's time goes; None records nothing."""
         ct, lib, ops = self.ct, self.lib, self.ops
         W, me, E, El, H, I, k = self.W, self.me, self.E, self.El, self.H, self.I, self.k
         if tuple(a.shape) != (self.T, H) or tuple(m_indices.shape) != (self.T, k):
             raise RuntimeError("[ASSERT FAILED] ep.py  Condition: a is [T, H] and m_indices is [T, k] of the sizes given at construction")
         self.epoch += 1
         ep_ = self.epoch
-        stream = ct.c_void_p(torch.cuda.current_stream(self.dev).cuda_stream)
+        cur = torch.cuda.current_stream(self.dev)
+        stream = ct.c_void_p(cur.cuda_stream)
         P = self._ptr_arrays
         vp = ct.c_void_p
+        out_name = "d_out1" if (self.out_buffers == 2 and ep_ % 2 == 0) else "d_out"
+        d_out = self.d_outs[1] if out_name == "d_out1" else self.d_outs[0]
+
+        def mark(name):
+            if timeline is not None:
+                ev = torch.cuda.Event(enable_timing=True)
+                ev.record(cur)
+                timeline.append((name, ev))
+        mark("start")
         if zero_dropped:
-            self.d_out.zero_()
+            d_out.zero_()
         counts, offsets, d2s, _ = ops.route_sort(m_indices, E)
+        mark("sort")
         self.check(lib.dqmoe_ep_publish_counts(vp(counts.data_ptr()), E, me, W, P["cnt"], P["flags"], ep_, stream))
+        mark("publish")
         self.check(lib.dqmoe_ep_plan(vp(self.local["cnt"]), vp(self.local["flags"]), E, me, W, ep_, self.cap,
                                      vp(self.send_base.data_ptr()), vp(self.rx_offsets.data_ptr()),
                                      vp(self.rx_mtiles.data_ptr()), stream))
+        mark("plan")
         sc_ptr = vp(a_scale.data_ptr()) if self.scale_cols else None
         self.check(lib.dqmoe_ep_dispatch(vp(a.data_ptr()), sc_ptr, H * self.esz, self.scale_cols, k, self.n,
                                          vp(offsets.data_ptr()), vp(d2s.data_ptr()), vp(self.send_base.data_ptr()),
                                          E, me, W, P["rx_rows"], P["rx_scale"], P["rx_home"], P["flags"],
                                          vp(self.done.data_ptr()), ep_, stream))
+        mark("dispatch")
         self.check(lib.dqmoe_ep_wait(vp(self.local["flags"]), 1, W, ep_, stream))
-        self.check(lib.dqmoe_ep_row_ptrs(vp(self.local["rx_home"]), vp(self.rx_offsets.data_ptr()), El, P["d_out"], W,
+        mark("wait_rows")
+        self.check(lib.dqmoe_ep_row_ptrs(vp(self.local["rx_home"]), vp(self.rx_offsets.data_ptr()), El, P[out_name], W,
                                          H * 2, self.cap, vp(self.row_dst.data_ptr()), stream))
+        mark("row_ptrs")
         b, bs, b1, b1s = self.weights_q
         sp = lambda t: None if t is None else vp(t.data_ptr())
         rx_scale = vp(self.local["rx_scale"]) if self.scale_cols else None
@@ -360,12 +336,15 @@ class PeerExpertParallelLayer:
                                               vp(self.rx_offsets.data_ptr()), vp(self.rx_mtiles.data_ptr()), self.cap, I,
                                               H, El, self.mode, 1, vp(self.act.data_ptr()), vp(self.act_scale.data_ptr()),
                                               None, None, stream))
+        mark("fc1")
         self.check(lib.dqmoe_grouped_gemm_rows(vp(self.act.data_ptr()), vp(self.act_scale.data_ptr()) if self.mode else None,
                                                vp(b1.data_ptr()), sp(b1s), vp(self.rx_offsets.data_ptr()),
                                                vp(self.rx_mtiles.data_ptr()), self.cap, H, I, El, self.mode,
                                                vp(self.row_dst.data_ptr()), stream))
+        mark("fc2")
         self.check(lib.dqmoe_ep_signal(P["flags"], 2, me, W, ep_, stream))
         self.check(lib.dqmoe_ep_wait(vp(self.local["flags"]), 2, W, ep_, stream))
+        mark("wait_results")
         if route_weights is None:
-            return self.d_out
-        return ops.finalize_weighted(self.d_out, route_weights)
+            return d_out
+        return ops.finalize_weighted(d_out, route_weights)
