@@ -577,8 +577,9 @@ def sustained_run(step, steps, local_rank, barrier, flops_step, pk, mode, is_ran
     if clocks and clocks.get("sm_mhz"):
         out["ms_x_mhz_median"] = med * clocks["sm_mhz"]
     peak = pk["bf16_sustained"] * (2.0 if mode else 1.0)
-    out["frac_of_sustained_peak"] = out["value"] / peak
-    out["sustained_peak_note"] = ("2 x " if mode else "") + f"{pk['source']} bf16 sustained ({pk['bf16_sustained']} TFLOP/s)"
+    world = dist.get_world_size() if dist is not None else 1
+    out["frac_of_sustained_peak"] = out["value"] / world / peak
+    out["sustained_peak_note"] = ("2 x " if mode else "") + f"{pk['source']} bf16 sustained ({pk['bf16_sustained']} TFLOP/s) per GPU"
     return out
 
 
