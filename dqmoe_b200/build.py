@@ -19,7 +19,8 @@ CSRC = os.path.join(PKG_DIR, "csrc")
 OBJ_DIR = os.path.join(PKG_DIR, "build")
 LIB_PATH = os.path.join(PKG_DIR, "libdqmoe_b200.so")
 
-SOURCES = ["common.cu", "route.cu", "permute.cu", "quant.cu", "gemm_sm100.cu", "layer.cu", "ep.cu", "decode.cu", "plugin.cu"]
+SOURCES = ["common.cu", "route.cu", "permute.cu", "quant.cu", "quant_mx.cu", "gemm_sm100.cu", "gemm_mx_sm100.cu", "layer.cu",
+           "ep.cu", "decode.cu", "plugin.cu"]
 
 NVCC_FLAGS = [
     "-gencode", "arch=compute_100a,code=sm_100a",

@@ -1,0 +1,510 @@
+// Grouped GEMM for expert-sorted rows in the MXFP8 mode: e4m3 operands with one UE8M0 (power-of-two) scale per
+// row and 32 K elements, for activations and weights alike. The scales ride inside the tensor-core instruction
+// (tcgen05.mma.kind::mxf8f6f4.block_scale reads them from TMEM columns), so the fp32 accumulator stays in TMEM
+// for the whole K loop: no per-128-K promotion through registers as the fp32-scaled block mode of
+// gemm_sm100.cu needs. Same persistent, warp-specialised structure otherwise:
+//   warp 0     TMA producer (activation rows + two weight boxes per 128-byte K stage, no cluster broadcast)
+//   warp 1     MMA issuer: per stage three tcgen05.cp (scale bytes -> TMEM) and four block-scaled MMAs
+//   warp 2     scale loader: 4-byte asynchronous copies that lay the stage's scale bytes out in shared memory
+//              the way tcgen05.cp wants them
+//   warps 4-11 epilogue: stage 1 SwiGLU + MXFP8 re-quantisation (each thread owns whole 32-column scale groups
+//              of its row), stage 2 bf16 rows scattered to d[T, k, H] or to explicit row addresses
+// TMEM budget: two 256-column accumulators and the scale columns do not fit 512 columns side by side, so the
+// two accumulators overlap by 24 columns; the epilogue of a tile drains the chunk holding those columns first
+// and signals it, and only that signal (not the whole epilogue) gates the next tile's first MMA.
+// The reference reserves mode bits for block-scaled formats it does not implement (csrc/quantization.h:30-38)
+// and names DeepGEMM as its road map (README.md:11); this mode has no counterpart kernel there.
+#include "common.cuh"
+#include "gemm_tile.cuh"
+#include "ptx_sm100.cuh"
+
+#include <mutex>
+
+namespace dq {
+namespace gemm_mx {
+
+using gemm::store_rows_staged;
+
+constexpr int kBM = 128;                 // rows per tile = UMMA M
+constexpr int kBox = 128;                // weight rows per TMA box, two boxes per stage
+constexpr int kN = 2 * kBox;             // 256 accumulator columns per tile
+constexpr int kBK = 128;                 // K elements (= bytes) per stage: one 128-byte swizzle row, four scale groups
+constexpr int kUmmaK = 32;               // K elements per tcgen05.mma = one scale group
+constexpr int kStages = 4;
+constexpr int kABytes = kBM * kBK;       // 16 KiB
+constexpr int kBBytes = kN * kBK;        // 32 KiB
+constexpr int kStageBytes = kABytes + kBBytes;
+constexpr int kSfBlock = 512;            // scale bytes of 128 rows x 4 groups, in tcgen05.cp order
+constexpr int kSfStage = 3 * kSfBlock;   // activation rows, first weight box, second weight box
+constexpr int kThreads = 384;
+constexpr int kRegsControl = 56;
+constexpr int kRegsEpilogue = 224;
+constexpr int kEpiWarps = 8;
+constexpr int kMaxExperts = 1024;
+constexpr int kMaxDevices = 64;
+constexpr int kTmemCols = 512;
+constexpr int kAccCol1 = 232;            // second accumulator: columns [232, 488); the first is [0, 256)
+constexpr int kSfCol = 488;              // scale columns: two alternating sets of 4 (A) + 8 (B)
+constexpr int kSfCols = 12;
+constexpr long long kWaitLimit = 1000000000LL;  // clock cycles before a wait gives up (~0.5 s)
+
+struct Params {
+    int n_rows, N, K, E;
+    int n_tiles;         // column tiles per row tile
+    int w_rows;          // weight rows per expert (stage 1: 2I, stage 2: H)
+    int tile_w_rows;     // weight rows advanced per column tile (stage 1: 128, stage 2: 256)
+    int box2_off;        // row offset of the second weight box (stage 1: I, stage 2: 128)
+    int kb_count;        // K / 128
+    const int* offsets;
+    const int* mtile_prefix;
+    const uint8_t* sfa;  // [n_rows, K/32] UE8M0
+    const uint8_t* sfb;  // [E * w_rows, K/32] UE8M0
+    void* out;
+    uint8_t* out_sf;     // stage 1: [n_rows, N/32] UE8M0
+    const float* bias;   // [E, w_rows] fp32 or nullptr
+    const int* dest_to_src;
+    const unsigned long long* row_dst;
+    int* status;
+};
+
+struct Shared {
+    uint64_t full[kStages];
+    uint64_t empty[kStages];
+    uint64_t tmem_full[2];
+    uint64_t tmem_empty[2];
+    uint64_t overlap_free[2];   // the columns a buffer shares with the other one have been drained
+    uint32_t tmem_base;
+    int abort_flag;
+    alignas(128) uint8_t sf[kStages][kSfStage];
+    uint4 stage[kEpiWarps][32 * 4];
+    int mprefix[kMaxExperts + 1];
+    int offsets[kMaxExperts + 1];
+};
+
+constexpr size_t kSmemBytes = 1024 + size_t(kStages) * kStageBytes + sizeof(Shared);
+
+struct Tile {
+    int e, row0, row_end, nt;
+};
+__device__ __forceinline__ Tile decode_tile(int t, int& e_cursor, const Shared& st, int n_tiles) {
+    while (t >= st.mprefix[e_cursor + 1] * n_tiles) ++e_cursor;
+    const int local = t - st.mprefix[e_cursor] * n_tiles;
+    const int mtiles = st.mprefix[e_cursor + 1] - st.mprefix[e_cursor];
+    Tile tl;
+    tl.e = e_cursor;
+    tl.nt = local / mtiles;
+    tl.row0 = st.offsets[e_cursor] + (local % mtiles) * kBM;
+    tl.row_end = st.offsets[e_cursor + 1];
+    return tl;
+}
+
+// UE8M0 scale of a 32-value group from its amax: the smallest power of two s with amax / s <= 448
+// (s = 2^ceil(log2(max(amax, 1e-4) / 448))), returned as the biased exponent byte; *inv = 1 / s exactly.
+__device__ __forceinline__ uint32_t mx_scale_byte(float amax, float* inv) {
+    const float s = __fdiv_rn(fmaxf(amax, 1e-4f), 448.0f);
+    const uint32_t bits = __float_as_uint(s);
+    const uint32_t e = (bits >> 23) + ((bits & 0x7fffffu) != 0u ? 1u : 0u);  // s > 0: no sign bit
+    *inv = __uint_as_float((254u - e) << 23);                               // 2^(127 - e)
+    return e;
+}
+
+template <bool kGated>
+__global__ void __launch_bounds__(kThreads, 1)
+moe_GemmGrouped_GemmUniversal_tcgen05_mx(const __grid_constant__ CUtensorMap tma_a,
+                                         const __grid_constant__ CUtensorMap tma_b, const Params p) {
+    extern __shared__ uint8_t smem_raw[];
+    uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+    Shared& st = *reinterpret_cast<Shared*>(smem + size_t(kStages) * kStageBytes);
+
+    const int warp = threadIdx.x >> 5;
+    const int lane = threadIdx.x & 31;
+
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < kStages; ++s) {
+            ptx::mbar_init(&st.full[s], 2);   // the TMA producer's expect_tx arrival + the scale loader
+            ptx::mbar_init(&st.empty[s], 1);
+        }
+        for (int b = 0; b < 2; ++b) {
+            ptx::mbar_init(&st.tmem_full[b], 1);
+            ptx::mbar_init(&st.tmem_empty[b], kEpiWarps);
+            ptx::mbar_init(&st.overlap_free[b], 4);  // the four warps (one per lane quarter) that own the shared columns
+        }
+        st.abort_flag = 0;
+        ptx::fence_barrier_init();
+        ptx::fence_proxy_async();
+    }
+    if (warp == 1) {
+        ptx::tmem_alloc(&st.tmem_base, kTmemCols);
+        ptx::tmem_relinquish();
+    }
+    for (int i = threadIdx.x; i <= p.E; i += kThreads) {
+        st.mprefix[i] = p.mtile_prefix[i];
+        st.offsets[i] = p.offsets[i];
+    }
+    ptx::tc_fence_before();
+    __syncthreads();
+    ptx::tc_fence_after();
+
+    const uint32_t tmem_base = st.tmem_base;
+    const int total_tiles = st.mprefix[p.E] * p.n_tiles;
+    volatile int* abort_flag = &st.abort_flag;
+    const int kb_count = p.kb_count;
+    const int tile_first = int(blockIdx.x), tile_step = int(gridDim.x);
+
+    if (warp < 4) {
+      ptx::setmaxnreg_dec<kRegsControl>();
+      if (warp == 0) {
+        // ------------------------------------------------------------ TMA producer
+        if (lane == 0) {
+            ptx::prefetch_tensormap(&tma_a);
+            ptx::prefetch_tensormap(&tma_b);
+            uint32_t it = 0;
+            int e_cursor = 0;
+            bool ok = true;
+            for (int t = tile_first; ok && t < total_tiles; t += tile_step) {
+                const Tile tl = decode_tile(t, e_cursor, st, p.n_tiles);
+                const int wrow0 = tl.e * p.w_rows + tl.nt * p.tile_w_rows;
+                const int wrow1 = wrow0 + p.box2_off;
+                for (int kb = 0; kb < kb_count; ++kb, ++it) {
+                    const int s = it % kStages;
+                    if (!ptx::mbar_wait(&st.empty[s], ((it / kStages) & 1u) ^ 1u, abort_flag, kWaitLimit)) {
+                        ok = false;
+                        break;
+                    }
+                    uint8_t* sa = smem + size_t(s) * kStageBytes;
+                    uint8_t* sb = sa + kABytes;
+                    ptx::mbar_arrive_expect_tx(&st.full[s], kStageBytes);
+                    ptx::tma_load_2d(sa, &tma_a, kb * kBK, tl.row0, &st.full[s]);
+                    ptx::tma_load_2d(sb, &tma_b, kb * kBK, wrow0, &st.full[s]);
+                    ptx::tma_load_2d(sb + kBox * kBK, &tma_b, kb * kBK, wrow1, &st.full[s]);
+                }
+            }
+        }
+        __syncwarp();
+      } else if (warp == 1) {
+        // ------------------------------------------------------------ MMA issuer
+        if (lane == 0) {
+            constexpr uint32_t idesc = ptx::make_idesc_mx(kBM, kN);
+            uint32_t it = 0;
+            uint32_t acc_it = 0;
+            bool ok = true;
+            for (int t = tile_first; ok && t < total_tiles; t += tile_step, ++acc_it) {
+                const uint32_t buf = acc_it & 1u;
+                // this buffer's previous tile is drained, and the other buffer's tile (the one just before this)
+                // has given up the columns the two share
+                if (!ptx::mbar_wait(&st.tmem_empty[buf], ((acc_it >> 1) & 1u) ^ 1u, abort_flag, kWaitLimit)) break;
+                if (acc_it > 0 &&
+                    !ptx::mbar_wait(&st.overlap_free[buf ^ 1u], ((acc_it - 1) >> 1) & 1u, abort_flag, kWaitLimit))
+                    break;
+                ptx::tc_fence_after();
+                const uint32_t d_tmem = tmem_base + (buf ? kAccCol1 : 0);
+                for (int kb = 0; kb < kb_count; ++kb, ++it) {
+                    const int s = it % kStages;
+                    if (!ptx::mbar_wait(&st.full[s], (it / kStages) & 1u, abort_flag, kWaitLimit)) {
+                        ok = false;
+                        break;
+                    }
+                    ptx::tc_fence_after();
+                    const uint32_t a_addr = ptx::smem_u32(smem + size_t(s) * kStageBytes);
+                    const uint32_t b_addr = a_addr + kABytes;
+                    const uint32_t sf_addr = ptx::smem_u32(&st.sf[s][0]);
+                    const uint32_t sf_col = tmem_base + kSfCol + (it & 1u) * kSfCols;
+                    // scale bytes of this stage -> TMEM (executed in order with the MMAs around them)
+                    ptx::tmem_cp_sf(sf_col, ptx::smem_desc_sf(sf_addr));
+                    ptx::tmem_cp_sf(sf_col + 4, ptx::smem_desc_sf(sf_addr + kSfBlock));
+                    ptx::tmem_cp_sf(sf_col + 8, ptx::smem_desc_sf(sf_addr + 2 * kSfBlock));
+#pragma unroll
+                    for (int k = 0; k < kBK / kUmmaK; ++k)
+                        ptx::umma_mx(d_tmem, ptx::smem_desc_sw128(a_addr + k * kUmmaK),
+                                     ptx::smem_desc_sw128(b_addr + k * kUmmaK), ptx::idesc_mx_with_sf_id(idesc, k), sf_col,
+                                     sf_col + 4, (kb | k) != 0 ? 1u : 0u);
+                    ptx::umma_commit(&st.empty[s]);
+                }
+                if (!ok) break;
+                ptx::umma_commit(&st.tmem_full[buf]);
+            }
+        }
+        __syncwarp();
+      } else if (warp == 2) {
+        // ------------------------------------------------------------ scale loader
+        // Row r of a 128-row block keeps its four scale bytes of this K stage (one 32-bit word of the row-major
+        // scale matrix) at byte (r % 32) * 16 + (r / 32) * 4 of the block: the order tcgen05.cp.32x128b.warpx4
+        // copies into TMEM. The copies of stage i are signalled when stage i + 1 has been issued, after a
+        // fence that makes them visible to the tensor core's reads of shared memory.
+        const size_t ks = size_t(p.K) / 32;  // scale bytes per row
+        const long long last_w = (long long) p.E * p.w_rows - 1;
+        uint32_t it = 0;
+        int e_cursor = 0;
+        bool ok = true;
+        int prev_s = -1;
+        for (int t = tile_first; ok && t < total_tiles; t += tile_step) {
+            const Tile tl = decode_tile(t, e_cursor, st, p.n_tiles);
+            const long long wrow0 = (long long) tl.e * p.w_rows + (long long) tl.nt * p.tile_w_rows;
+            const uint8_t* src[12];
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+                src[j] = p.sfa + size_t(min(tl.row0 + lane + 32 * j, p.n_rows - 1)) * ks;
+                long long r0 = wrow0 + lane + 32 * j, r1 = wrow0 + p.box2_off + lane + 32 * j;
+                src[4 + j] = p.sfb + size_t(r0 < last_w ? r0 : last_w) * ks;
+                src[8 + j] = p.sfb + size_t(r1 < last_w ? r1 : last_w) * ks;
+            }
+            for (int kb = 0; kb < kb_count; ++kb, ++it) {
+                const int s = it % kStages;
+                if (!ptx::mbar_wait(&st.empty[s], ((it / kStages) & 1u) ^ 1u, abort_flag, kWaitLimit)) {
+                    ok = false;
+                    break;
+                }
+                uint8_t* dst = &st.sf[s][0] + lane * 16;
+#pragma unroll
+                for (int j = 0; j < 12; ++j) ptx::cp_async4(dst + (j >> 2) * kSfBlock + (j & 3) * 4, src[j] + kb * 4);
+                ptx::cp_async_commit_group();
+                if (prev_s >= 0) {
+                    ptx::cp_async_wait_group<1>();  // everything but the group just committed has landed
+                    ptx::fence_proxy_async();
+                    __syncwarp();
+                    if (lane == 0) ptx::mbar_arrive(&st.full[prev_s]);
+                }
+                prev_s = s;
+            }
+        }
+        ptx::cp_async_wait_all();
+        if (ok && prev_s >= 0) {
+            ptx::fence_proxy_async();
+            __syncwarp();
+            if (lane == 0) ptx::mbar_arrive(&st.full[prev_s]);
+        }
+      }
+    } else {
+        ptx::setmaxnreg_inc<kRegsEpilogue>();
+        // ------------------------------------------------------------ epilogue warps
+        const int q = warp & 3;            // TMEM lane quarter this warp may read
+        const int h = (warp - 4) >> 2;     // which 64-column half of each 128-column group
+        const int r_in_tile = q * 32 + lane;
+        const uint32_t t_lane = tmem_base + (static_cast<uint32_t>(q * 32) << 16);
+        uint32_t acc_it = 0;
+        int e_cursor = 0;
+        bool ok = true;
+        const int N = p.N;
+        float* csw = reinterpret_cast<float*>(st.stage[warp - 4]);
+        const float4* cs4 = reinterpret_cast<const float4*>(st.stage[warp - 4]);
+
+        for (int t = tile_first; ok && t < total_tiles; t += tile_step, ++acc_it) {
+            const Tile tl = decode_tile(t, e_cursor, st, p.n_tiles);
+            const int grow = tl.row0 + r_in_tile;
+            const bool row_ok = grow < tl.row_end;
+            const uint32_t buf = acc_it & 1u;
+            if (!ptx::mbar_wait(&st.tmem_full[buf], (acc_it >> 1) & 1u, abort_flag, kWaitLimit)) {
+                ok = false;
+                break;
+            }
+            ptx::tc_fence_after();
+            const uint32_t t_buf = t_lane + (buf ? kAccCol1 : 0);
+            // The columns shared with the other buffer are the last 24 of buffer 0 and the first 24 of buffer 1:
+            // the chunk order starts there, and the warps that own those columns report them drained.
+            const bool owns_overlap = h == (buf == 0u ? 1 : 0);
+            const bool has_bias = p.bias != nullptr;
+            const float* bias_e = has_bias ? p.bias + size_t(tl.e) * p.w_rows : nullptr;
+            auto overlap_drained = [&]() {
+                if (owns_overlap) {
+                    ptx::tc_fence_before();
+                    __syncwarp();
+                    if (lane == 0) ptx::mbar_arrive(&st.overlap_free[buf]);
+                }
+            };
+
+            if constexpr (kGated) {
+                // act columns nt*128 + h*64 + [0, 64): two scale groups of 32
+                uint32_t pk[2][8];   // e4m3 bytes of the two groups in the order they were drained
+                uint32_t sf_bytes = 0;
+#pragma unroll
+                for (int jj = 0; jj < 2; ++jj) {
+                    const int j = buf == 0u ? 1 - jj : jj;
+                    uint32_t g[32], v[32];
+                    const int c0 = h * 64 + j * 32;
+                    ptx::tmem_ld32(t_buf + c0, g);
+                    ptx::tmem_ld32(t_buf + kBox + c0, v);
+                    const int col0 = tl.nt * kBox + c0;
+                    if (has_bias) {
+                        __syncwarp();
+                        const int c = min(col0 + lane, N - 1);
+                        csw[lane] = bias_e[c];
+                        csw[32 + lane] = bias_e[N + c];
+                        __syncwarp();
+                    }
+                    ptx::tmem_wait_ld(g);
+                    ptx::tmem_wait_ld(v);
+                    if (jj == 0) overlap_drained();
+                    float act[32];
+                    float amax = 0.0f;
+#pragma unroll
+                    for (int i = 0; i < 32; i += 4) {
+                        float bg[4] = {0.0f, 0.0f, 0.0f, 0.0f}, bv[4] = {0.0f, 0.0f, 0.0f, 0.0f};
+                        if (has_bias) {
+                            const float4 a = cs4[i >> 2], b = cs4[8 + (i >> 2)];
+                            bg[0] = a.x, bg[1] = a.y, bg[2] = a.z, bg[3] = a.w;
+                            bv[0] = b.x, bv[1] = b.y, bv[2] = b.z, bv[3] = b.w;
+                        }
+#pragma unroll
+                        for (int u = 0; u < 4; ++u) {
+                            // roundings as in the fp32-scaled block mode: product, silu and their product to bf16
+                            const float gate = bf_round_cvt(__uint_as_float(g[i + u]) + bg[u]);
+                            const float val = bf_round_cvt(__uint_as_float(v[i + u]) + bv[u]);
+                            float a = bf_round_cvt(bf_round_cvt(__fdividef(gate, 1.0f + __expf(-gate))) * val);
+                            if (col0 + i + u >= N) a = 0.0f;
+                            act[i + u] = a;
+                            amax = fmaxf(amax, fabsf(a));
+                        }
+                    }
+                    float inv;
+                    const uint32_t e8 = mx_scale_byte(amax, &inv);
+                    sf_bytes |= e8 << (8 * j);
+#pragma unroll
+                    for (int i = 0; i < 32; i += 4)
+                        pk[jj][i >> 2] = f2e4m3x4(act[i] * inv, act[i + 1] * inv, act[i + 2] * inv, act[i + 3] * inv);
+                }
+                uint32_t packed[16];  // back into column order (buffer 0 drains its second group first)
+#pragma unroll
+                for (int i = 0; i < 8; ++i) {
+                    packed[i] = buf == 0u ? pk[1][i] : pk[0][i];
+                    packed[8 + i] = buf == 0u ? pk[0][i] : pk[1][i];
+                }
+                const int colh = tl.nt * kBox + h * 64;
+                store_rows_staged(st.stage[warp - 4], packed,
+                                  row_ok ? static_cast<uint8_t*>(p.out) + size_t(grow) * N + colh : nullptr,
+                                  min(4, max(0, (N - colh + 15) / 16)), lane);
+                if (row_ok && colh < N)
+                    *reinterpret_cast<uint16_t*>(p.out_sf + size_t(grow) * (N / 32) + (colh >> 5)) = uint16_t(sf_bytes);
+            } else {
+                int orow_idx = grow;
+                if (row_ok && p.dest_to_src != nullptr) orow_idx = p.dest_to_src[grow];
+                uint8_t* orow = static_cast<uint8_t*>(p.out) + size_t(orow_idx) * N * 2;
+                if (p.row_dst != nullptr) {  // rows go to explicit addresses (expert parallel: the home rank's output)
+                    orow = row_ok ? reinterpret_cast<uint8_t*>(p.row_dst[grow]) : nullptr;
+                    orow_idx = orow != nullptr ? 0 : -1;
+                }
+#pragma unroll 1
+                for (int cc = 0; cc < 4; ++cc) {
+                    const int c = buf == 0u ? 3 - cc : cc;
+                    uint32_t r[32];
+                    const int tc = (c >> 1) * kBox + h * 64 + (c & 1) * 32;
+                    ptx::tmem_ld32(t_buf + tc, r);
+                    const int col0 = tl.nt * kN + tc;
+                    if (has_bias) {
+                        __syncwarp();
+                        csw[lane] = bias_e[min(col0 + lane, N - 1)];
+                        __syncwarp();
+                    }
+                    ptx::tmem_wait_ld(r);
+                    if (cc == 0) overlap_drained();
+                    uint32_t packed[16];
+#pragma unroll
+                    for (int i = 0; i < 32; i += 4) {
+                        float bb[4] = {0.0f, 0.0f, 0.0f, 0.0f};
+                        if (has_bias) {
+                            const float4 a = cs4[i >> 2];
+                            bb[0] = a.x, bb[1] = a.y, bb[2] = a.z, bb[3] = a.w;
+                        }
+                        packed[i >> 1] = pack_bf16x2(__uint_as_float(r[i]) + bb[0], __uint_as_float(r[i + 1]) + bb[1]);
+                        packed[(i >> 1) + 1] = pack_bf16x2(__uint_as_float(r[i + 2]) + bb[2], __uint_as_float(r[i + 3]) + bb[3]);
+                    }
+                    store_rows_staged(st.stage[warp - 4], packed,
+                                      row_ok && orow_idx >= 0 ? orow + size_t(col0) * 2 : nullptr,
+                                      min(4, max(0, (N - col0 + 7) / 8)), lane);
+                }
+            }
+            ptx::tc_fence_before();
+            __syncwarp();
+            if (lane == 0) ptx::mbar_arrive(&st.tmem_empty[buf]);
+        }
+    }
+
+    // ---------------------------------------------------------------- teardown
+    if (*abort_flag != 0) {
+        // a wait gave up: report instead of trapping, let copies in flight land, then free TMEM
+        if (threadIdx.x == 0 && p.status != nullptr) {
+            *reinterpret_cast<volatile int*>(p.status) = 120 + (kGated ? 0 : 10) + 4;
+            __threadfence_system();
+        }
+        for (int i = 0; i < 2000; ++i) __nanosleep(1000);
+    }
+    ptx::cp_async_wait_all();
+    ptx::tc_fence_before();
+    __syncthreads();
+    if (warp == 1) {
+        ptx::tc_fence_after();
+        ptx::tmem_dealloc(tmem_base, kTmemCols);
+    }
+}
+
+template <bool kGated>
+static int launch(const CUtensorMap& ma, const CUtensorMap& mb, const Params& p, cudaStream_t stream) {
+    auto kern = moe_GemmGrouped_GemmUniversal_tcgen05_mx<kGated>;
+    static std::mutex mu;
+    static bool configured[kMaxDevices] = {};
+    int dev = 0;
+    DQ_CUDA(cudaGetDevice(&dev));
+    DQ_CHECK(dev >= 0 && dev < kMaxDevices);
+    {
+        std::lock_guard<std::mutex> lk(mu);
+        if (!configured[dev]) {
+            DQ_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, int(kSmemBytes)));
+            configured[dev] = true;
+        }
+    }
+    kern<<<sm_count(), kThreads, kSmemBytes, stream>>>(ma, mb, p);
+    DQ_LAUNCH_CHECK();
+    return DQMOE_OK;
+}
+
+int grouped_gemm_mx(const void* a, const uint8_t* a_sf, const void* w, const uint8_t* w_sf, const int* offsets,
+                    const int* mtile_prefix, int n, int N, int K, int E, int gated, void* out, uint8_t* out_sf,
+                    const int* dest_to_src, const void* row_dst, const float* bias, cudaStream_t stream) {
+    DQ_CHECK(n >= 0 && N > 0 && K > 0 && E > 0 && E <= kMaxExperts);
+    if (n == 0) return DQMOE_OK;
+    DQ_CHECK_FMT(K % 128 == 0, "K=%d: the MXFP8 mode needs the reduction length to be a multiple of 128", K);
+    DQ_CHECK_FMT(N % (gated ? 128 : 8) == 0, "N=%d: MXFP8 stage %d needs a multiple of %d output columns", N, gated ? 1 : 2,
+                 gated ? 128 : 8);
+    DQ_CHECK(a != nullptr && w != nullptr && a_sf != nullptr && w_sf != nullptr && offsets != nullptr && mtile_prefix != nullptr);
+    DQ_CHECK((out != nullptr || row_dst != nullptr) && (row_dst == nullptr || !gated));
+    DQ_CHECK(is_aligned(a, 16) && is_aligned(w, 16) && is_aligned(out, 16) && is_aligned(row_dst, 8) && is_aligned(a_sf, 4) &&
+             is_aligned(w_sf, 4));
+    if (gated) DQ_CHECK(out_sf != nullptr && is_aligned(out_sf, 4));
+    Params p;
+    p.n_rows = n;
+    p.N = N;
+    p.K = K;
+    p.E = E;
+    p.w_rows = gated ? 2 * N : N;
+    p.n_tiles = gated ? ceil_div(N, kBox) : ceil_div(N, kN);
+    p.tile_w_rows = gated ? kBox : kN;
+    p.box2_off = gated ? N : kBox;
+    p.kb_count = K / kBK;
+    p.offsets = offsets;
+    p.mtile_prefix = mtile_prefix;
+    p.sfa = a_sf;
+    p.sfb = w_sf;
+    p.out = out;
+    p.out_sf = out_sf;
+    p.bias = bias;
+    p.dest_to_src = dest_to_src;
+    p.row_dst = static_cast<const unsigned long long*>(row_dst);
+    p.status = device_status_word();
+    if (p.status == nullptr) return DQMOE_ERR_CUDA;
+    CUtensorMap ma, mb;
+    int rc = gemm::make_map(&ma, a, 1, uint64_t(n), uint64_t(K), kBM);
+    if (rc != DQMOE_OK) return rc;
+    rc = gemm::make_map(&mb, w, 1, uint64_t(E) * p.w_rows, uint64_t(K), kBox);
+    if (rc != DQMOE_OK) return rc;
+    return gated ? launch<true>(ma, mb, p, stream) : launch<false>(ma, mb, p, stream);
+}
+
+}  // namespace gemm_mx
+}  // namespace dq
+
+extern "C" int dqmoe_grouped_gemm_mx(const void* a, const uint8_t* a_sf, const void* w, const uint8_t* w_sf,
+                                     const int32_t* offsets, const int32_t* mtile_prefix, int n, int N, int K, int E,
+                                     int gated, void* out, uint8_t* out_sf, const int32_t* dest_to_src,
+                                     dqmoe_stream_t stream) {
+    return dq::gemm_mx::grouped_gemm_mx(a, a_sf, w, w_sf, offsets, mtile_prefix, n, N, K, E, gated, out, out_sf,
+                                        dest_to_src, nullptr, nullptr, static_cast<cudaStream_t>(stream));
+}

@@ -24,6 +24,12 @@ int grouped_gemm(const void* a, const float* a_scale, const void* w, const float
 enum Elem : int { kElemBf16 = 0, kElemHalf = 1, kElemF32 = 2 };  // element type of the unquantised path
 }  // namespace gemm
 
+namespace gemm_mx {
+int grouped_gemm_mx(const void* a, const uint8_t* a_sf, const void* w, const uint8_t* w_sf, const int* offsets,
+                    const int* mtile_prefix, int n, int N, int K, int E, int gated, void* out, uint8_t* out_sf,
+                    const int* dest_to_src, const void* row_dst, const float* bias, cudaStream_t stream);
+}  // namespace gemm_mx
+
 namespace decode {
 int forward(const void* a, const float* a_scale, const void* b, const float* b_scale, const void* b1,
             const float* b1_scale, void* d, const int* m_indices, void* act_bf16, float* amax, int T, int H, int I,
@@ -44,7 +50,7 @@ struct Layout {
 
 static bool valid_mode(int q) {
     return q == DQMOE_QUANT_NONE || q == DQMOE_QUANT_FP8_TENSOR || q == DQMOE_QUANT_FP8_CHANNEL ||
-           q == DQMOE_QUANT_FP8_BLOCK;
+           q == DQMOE_QUANT_FP8_BLOCK || q == DQMOE_QUANT_FP8_MX;
 }
 
 static Layout make_layout(int T, int H, int I, int E, int k, int quant_mode, int elem = gemm::kElemBf16) {
@@ -64,11 +70,12 @@ static Layout make_layout(int T, int H, int I, int E, int k, int quant_mode, int
     L.sort_ws = add(L.sort_ws_bytes);
     L.dest_to_src = add(n * sizeof(int));
     L.perm_a = add(n * H * esz);
-    L.perm_scale_cols = quant_mode == DQMOE_QUANT_FP8_BLOCK ? ceil_div(H, 128)
+    // fp32 words of scale per row: block mode one per 128 columns; MX mode H/32 UE8M0 bytes = H/128 words
+    L.perm_scale_cols = quant_mode == DQMOE_QUANT_FP8_BLOCK || quant_mode == DQMOE_QUANT_FP8_MX ? ceil_div(H, 128)
                         : quant_mode == DQMOE_QUANT_FP8_CHANNEL ? 1 : 0;
     L.perm_a_scale = add(n * L.perm_scale_cols * sizeof(float));
     L.act = add(n * I * esz);
-    const size_t act_scale_elems = quant_mode == DQMOE_QUANT_FP8_BLOCK ? n * ceil_div(I, 128)
+    const size_t act_scale_elems = quant_mode == DQMOE_QUANT_FP8_BLOCK || quant_mode == DQMOE_QUANT_FP8_MX ? n * ceil_div(I, 128)
                                    : quant_mode == DQMOE_QUANT_FP8_CHANNEL ? n
                                    : quant_mode == DQMOE_QUANT_FP8_TENSOR ? 1 : 0;
     L.act_scale = add(act_scale_elems * sizeof(float));
@@ -117,7 +124,10 @@ static int moe_forward_impl(const void* a, const float* a_scale, const void* b, 
                             size_t workspace_bytes, int T, int H, int I, int E, int k, int quant_mode, int elem,
                             const float* bias1, const float* bias2, cudaStream_t stream) {
     DQ_CHECK(T >= 0 && H > 0 && I > 0 && E > 0 && k > 0);
-    DQ_CHECK_FMT(layer::valid_mode(quant_mode), "quant_mode_value=%d is not one of 0, 256, 512, 1024", quant_mode);
+    DQ_CHECK_FMT(layer::valid_mode(quant_mode), "quant_mode_value=%d is not one of 0, 256, 512, 1024, 2048", quant_mode);
+    if (quant_mode == DQMOE_QUANT_FP8_MX)
+        DQ_CHECK_FMT(H % 128 == 0 && I % 128 == 0, "hidden_size=%d and inter_size=%d must be multiples of 128 in the MXFP8 mode",
+                     H, I);
     if (T == 0) return DQMOE_OK;  // as csrc/pybind11_register.h:125-126
     DQ_CHECK(a != nullptr && b != nullptr && b1 != nullptr && d != nullptr && m_indices != nullptr);
     DQ_CHECK_FMT(workspace != nullptr && is_aligned(workspace, layer::kAlign), "workspace pointer %p is not aligned!",
@@ -161,6 +171,15 @@ static int moe_forward_impl(const void* a, const float* a_scale, const void* b, 
                             L.perm_scale_cols, L.perm_scale_cols ? perm_a_scale : nullptr, stream);
     if (rc != DQMOE_OK) return rc;
 
+    if (quant_mode == DQMOE_QUANT_FP8_MX) {  // the scale pointers address UE8M0 bytes in this mode
+        rc = gemm_mx::grouped_gemm_mx(perm_a, reinterpret_cast<const uint8_t*>(perm_a_scale), b,
+                                      reinterpret_cast<const uint8_t*>(b_scale), offsets, mtile_prefix, n, I, H, E, 1, act,
+                                      reinterpret_cast<uint8_t*>(act_scale), nullptr, nullptr, bias1, stream);
+        if (rc != DQMOE_OK) return rc;
+        return gemm_mx::grouped_gemm_mx(act, reinterpret_cast<const uint8_t*>(act_scale), b1,
+                                        reinterpret_cast<const uint8_t*>(b1_scale), offsets, mtile_prefix, n, H, I, E, 0, d,
+                                        nullptr, dest_to_src, nullptr, bias2, stream);
+    }
     const float* sa1 = quant_mode == DQMOE_QUANT_FP8_TENSOR ? a_scale : perm_a_scale;
     const bool two_pass = quant_mode == DQMOE_QUANT_FP8_TENSOR || quant_mode == DQMOE_QUANT_FP8_CHANNEL;
     if (two_pass) {
@@ -253,9 +272,7 @@ static BlockLayout block_layout(int T, int H, int I, int E, int k, int quant_mod
 
 size_t dqmoe_moe_block_workspace_bytes(int T, int H, int I, int E, int k, int quant_mode) {
     if (T < 0 || H <= 0 || I <= 0 || E <= 0 || k <= 0) return 0;
-    if (quant_mode != DQMOE_QUANT_NONE && quant_mode != DQMOE_QUANT_FP8_BLOCK &&
-        quant_mode != DQMOE_QUANT_FP8_TENSOR && quant_mode != DQMOE_QUANT_FP8_CHANNEL)
-        return 0;
+    if (!layer::valid_mode(quant_mode)) return 0;
     return block_layout(T, H, I, E, k, quant_mode).total;
 }
 
@@ -269,9 +286,10 @@ static int moe_block_impl(const void* x_bf16, const float* logits, const void* b
     DQ_CHECK(T >= 0 && H > 0 && I > 0 && E_routed > 0 && k_routed > 0 && n_shared >= 0);
     const int E = E_routed + n_shared;
     const int k = k_routed + n_shared;
-    DQ_CHECK_FMT(quant_mode == DQMOE_QUANT_NONE || quant_mode == DQMOE_QUANT_FP8_BLOCK ||
-                     quant_mode == DQMOE_QUANT_FP8_TENSOR || quant_mode == DQMOE_QUANT_FP8_CHANNEL,
-                 "quant_mode=%d: unknown quantisation mode", quant_mode);
+    DQ_CHECK_FMT(layer::valid_mode(quant_mode), "quant_mode=%d: unknown quantisation mode", quant_mode);
+    if (quant_mode == DQMOE_QUANT_FP8_MX)
+        DQ_CHECK_FMT(H % 128 == 0 && I % 128 == 0, "hidden_size=%d and inter_size=%d must be multiples of 128 in the MXFP8 mode",
+                     H, I);
     if (T == 0) return DQMOE_OK;
     DQ_CHECK(x_bf16 != nullptr && logits != nullptr && b != nullptr && b1 != nullptr && out_bf16 != nullptr);
     DQ_CHECK_FMT(workspace != nullptr && is_aligned(workspace, layer::kAlign), "workspace pointer %p is not aligned!",
@@ -318,6 +336,19 @@ static int moe_block_impl(const void* x_bf16, const float* logits, const void* b
     rc = route::route_sort(indices, n, E, counts, offsets, mtile_prefix, dest_to_src, nullptr, lws + L.sort_ws,
                            L.sort_ws_bytes, stream);
     if (rc != DQMOE_OK) return rc;
+    if (quant_mode == DQMOE_QUANT_FP8_MX) {  // the same fusion with 1x32 power-of-two scales
+        rc = dqmoe_permute_quant_mxfp8(x_bf16, H, k, dest_to_src, n, perm_a, reinterpret_cast<uint8_t*>(perm_a_scale), stream);
+        if (rc != DQMOE_OK) return rc;
+        rc = gemm_mx::grouped_gemm_mx(perm_a, reinterpret_cast<const uint8_t*>(perm_a_scale), b,
+                                      reinterpret_cast<const uint8_t*>(b_scale), offsets, mtile_prefix, n, I, H, E, 1, act,
+                                      reinterpret_cast<uint8_t*>(act_scale), nullptr, nullptr, nullptr, stream);
+        if (rc != DQMOE_OK) return rc;
+        rc = gemm_mx::grouped_gemm_mx(act, reinterpret_cast<const uint8_t*>(act_scale), b1,
+                                      reinterpret_cast<const uint8_t*>(b1_scale), offsets, mtile_prefix, n, H, I, E, 0, d,
+                                      nullptr, dest_to_src, nullptr, nullptr, stream);
+        if (rc != DQMOE_OK) return rc;
+        return dqmoe_finalize_weighted(d, weights, out_bf16, T, k, H, stream);
+    }
     if (fp8)  // quantise while gathering: each expanded row is read as bf16 and written as e4m3 + 1x128 scales
         rc = dqmoe_permute_quant_block_1x128(x_bf16, H, k, dest_to_src, n, perm_a, perm_a_scale, stream);
     else

@@ -76,6 +76,13 @@ __device__ __forceinline__ void cp_async_arrive(uint64_t* bar) {
     asm volatile("cp.async.mbarrier.arrive.noinc.shared::cta.b64 [%0];" ::"r"(smem_u32(bar)) : "memory");
 }
 __device__ __forceinline__ void cp_async_wait_all() { asm volatile("cp.async.wait_all;" ::: "memory"); }
+// Groups of cp.async: commit what this thread issued so far as one group; wait until at most kPending of its
+// most recent groups are still in flight.
+__device__ __forceinline__ void cp_async_commit_group() { asm volatile("cp.async.commit_group;" ::: "memory"); }
+template <int kPending>
+__device__ __forceinline__ void cp_async_wait_group() {
+    asm volatile("cp.async.wait_group %0;" ::"n"(kPending) : "memory");
+}
 
 // ---------------------------------------------------------------- register budget
 
@@ -189,6 +196,51 @@ __device__ __forceinline__ void umma(uint32_t tmem_d, uint64_t desc_a, uint64_t 
             "l"(desc_a), "l"(desc_b), "r"(idesc), "r"(accumulate)
             : "memory");
     }
+}
+
+// ---------------------------------------------------------------- block-scaled MMA (MXFP8)
+
+// Instruction descriptor of tcgen05.mma.kind::mxf8f6f4.block_scale: A and B e4m3, both K-major, UE8M0 scale
+// factors, M x N tile; sf_id = which of the four scale bytes of a 32-bit TMEM scale column this instruction
+// uses (the K = 32 step inside a 128-wide K block), for A (bits 29-30) and B (bits 4-5).
+__host__ __device__ constexpr uint32_t make_idesc_mx(uint32_t m, uint32_t n) {
+    return ((n >> 3) << 17)        // N / 8
+           | (1u << 23)            // scale format UE8M0
+           | ((m >> 4) << 24);     // M / 16; A and B format fields 0 = e4m3
+}
+__device__ __forceinline__ uint32_t idesc_mx_with_sf_id(uint32_t idesc, uint32_t sf_id) {
+    return idesc | (sf_id << 4) | (sf_id << 29);
+}
+
+// D[tmem] (+)= (A * 2^(sfa-127)) (B * 2^(sfb-127))^T with one UE8M0 scale per row of A / B and 32 K elements;
+// the scale factors are read from TMEM columns (tmem_sfa: 4 columns for 128 rows of A, tmem_sfb: 4 columns per
+// 128 rows of B).
+__device__ __forceinline__ void umma_mx(uint32_t tmem_d, uint64_t desc_a, uint64_t desc_b, uint32_t idesc,
+                                        uint32_t tmem_sfa, uint32_t tmem_sfb, uint32_t accumulate) {
+    asm volatile(
+        "{\n\t"
+        ".reg .pred p;\n\t"
+        "setp.ne.b32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::1.kind::mxf8f6f4.block_scale [%0], %1, %2, %3, [%5], [%6], p;\n\t"
+        "}" ::"r"(tmem_d),
+        "l"(desc_a), "l"(desc_b), "r"(idesc), "r"(accumulate), "r"(tmem_sfa), "r"(tmem_sfb)
+        : "memory");
+}
+
+// Shared-memory descriptor of one 512-byte scale-factor block for tcgen05.cp: 32 rows of 16 bytes, no swizzle,
+// 8-row groups 128 bytes apart. Row r0 holds the scale bytes of tile rows r0, r0+32, r0+64, r0+96 (4 each, one
+// per 32-wide K step).
+__device__ __forceinline__ uint64_t smem_desc_sf(uint32_t smem_addr) {
+    uint64_t d = 0;
+    d |= static_cast<uint64_t>((smem_addr & 0x3ffffu) >> 4);  // start address
+    d |= static_cast<uint64_t>(128 >> 4) << 32;                // stride byte offset between 8-row groups
+    d |= static_cast<uint64_t>(1) << 46;                       // descriptor version of sm_100
+    return d;                                                  // layout type 0: no swizzle
+}
+// Copy that block into 4 TMEM columns, replicated into all four 32-lane quarters (each quarter's MMA rows
+// find their scales in their own lanes).
+__device__ __forceinline__ void tmem_cp_sf(uint32_t tmem_dst, uint64_t smem_desc) {
+    asm volatile("tcgen05.cp.cta_group::1.32x128b.warpx4 [%0], %1;" ::"r"(tmem_dst), "l"(smem_desc) : "memory");
 }
 
 // Arrive on an mbarrier when all MMAs issued so far by this thread have completed.

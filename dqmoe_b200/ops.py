@@ -19,6 +19,7 @@ QUANT_NONE = 0
 QUANT_FP8_TENSOR = 256
 QUANT_FP8_CHANNEL = 512
 QUANT_FP8_BLOCK = 1024
+QUANT_FP8_MX = 2048
 SCORE_SOFTMAX = 0
 SCORE_SIGMOID = 1
 
@@ -59,11 +60,13 @@ def _check_scales(a_scale, b_scale, b1_scale, T, H, I, E, quant_mode):
     (include/dqmoe.h lists the shapes); a short tensor would be read out of bounds by the kernels."""
     g = lambda x: (x + 127) // 128
     want = {QUANT_FP8_TENSOR: (1, E, E), QUANT_FP8_CHANNEL: (T, E * 2 * I, E * H),
-            QUANT_FP8_BLOCK: (T * g(H), E * g(2 * I) * g(H), E * g(H) * g(I))}[quant_mode]
+            QUANT_FP8_BLOCK: (T * g(H), E * g(2 * I) * g(H), E * g(H) * g(I)),
+            QUANT_FP8_MX: (T * H // 32, E * 2 * I * H // 32, E * H * I // 32)}[quant_mode]
+    dtype = torch.uint8 if quant_mode == QUANT_FP8_MX else torch.float32  # MXFP8 scales are UE8M0 bytes
     for name, t, n in zip(("a_scale", "b_scale", "b1_scale"), (a_scale, b_scale, b1_scale), want):
-        if t is None or not t.is_cuda or t.dtype != torch.float32 or not t.is_contiguous() or t.numel() != n:
+        if t is None or not t.is_cuda or t.dtype != dtype or not t.is_contiguous() or t.numel() != n:
             got = "None" if t is None else f"{t.dtype} {tuple(t.shape)} on {t.device}"
-            raise RuntimeError(f"[ASSERT FAILED] ops.py  Condition: {name} is a contiguous fp32 CUDA tensor of {n} "
+            raise RuntimeError(f"[ASSERT FAILED] ops.py  Condition: {name} is a contiguous {dtype} CUDA tensor of {n} "
                                f"elements for quant mode {quant_mode}  Info: got {got}")
 
 
@@ -87,7 +90,7 @@ def moe_forward(a, a_scale, b, b_scale, b1, b1_scale, d, m_indices, workspace, q
     for name, t in (("a", a), ("b", b), ("b1", b1), ("d", d), ("m_indices", m_indices), ("workspace", workspace)):
         _cuda(t, name)
     quant_mode = int(quant_mode)
-    if quant_mode in (QUANT_FP8_TENSOR, QUANT_FP8_CHANNEL, QUANT_FP8_BLOCK):
+    if quant_mode in (QUANT_FP8_TENSOR, QUANT_FP8_CHANNEL, QUANT_FP8_BLOCK, QUANT_FP8_MX):
         _check_scales(a_scale, b_scale, b1_scale, T, H, I, E, quant_mode)
     _check_bias(bias1, E, 2 * I, "bias1")
     _check_bias(bias2, E, H, "bias2")
@@ -350,7 +353,43 @@ def per_tensor_cast_to_fp8(x: torch.Tensor, per_expert: bool = False):
     return q, s
 
 
+def mx_cast_to_fp8(x: torch.Tensor):
+    """MXFP8: (e4m3 of x's shape, UE8M0 scale bytes [..., n/32]) for bf16 x [..., n]; see dqmoe_quant_mxfp8."""
+    _cuda(x, "x")
+    assert x.dtype == torch.bfloat16 and x.shape[-1] % 32 == 0
+    n = x.shape[-1]
+    rows = x.numel() // n
+    q = torch.empty(x.shape, dtype=FP8, device=x.device)
+    s = torch.empty((*x.shape[:-1], n // 32), dtype=torch.uint8, device=x.device)
+    with torch.cuda.device(x.device):
+        _lib.check(_lib.load().dqmoe_quant_mxfp8(_p(x), rows, n, _p(q), _p(s), _stream(x.device)))
+    return q, s
+
+
+def moe_permute_quant_mx(x: torch.Tensor, dest_to_src: torch.Tensor, k: int):
+    """Gather fused with the MXFP8 quantisation of bf16 activations x [T, H]."""
+    _cuda(x, "x")
+    _cuda(dest_to_src, "dest_to_src")
+    assert x.dtype == torch.bfloat16
+    n, H = dest_to_src.numel(), x.shape[1]
+    q = torch.empty((n, H), dtype=FP8, device=x.device)
+    s = torch.empty((n, H // 32), dtype=torch.uint8, device=x.device)
+    with torch.cuda.device(x.device):
+        _lib.check(_lib.load().dqmoe_permute_quant_mxfp8(_p(x), H, k, _p(dest_to_src), n, _p(q), _p(s), _stream(x.device)))
+    return q, s
+
+
 # ---------------------------------------------------------------------- grouped GEMM
+
+def grouped_gemm_mx(a, a_sf, w, w_sf, offsets, mtile_pref, N: int, gated: bool, out, out_sf=None, dest_to_src=None) -> None:
+    """The grouped GEMM in the MXFP8 mode; see dqmoe_grouped_gemm_mx."""
+    n, K = a.shape
+    E = w.shape[0]
+    with torch.cuda.device(a.device):
+        _lib.check(_lib.load().dqmoe_grouped_gemm_mx(_p(a), _p(a_sf), _p(w), _p(w_sf), _p(offsets), _p(mtile_pref), n, N, K,
+                                                     E, int(bool(gated)), _p(out), _p(out_sf), _p(dest_to_src),
+                                                     _stream(a.device)))
+
 
 def grouped_gemm(a, a_scale, w, w_scale, offsets, mtile_pref, N: int, quant_mode: int, gated: bool,
                  out, out_scale=None, amax=None, dest_to_src=None) -> None:

@@ -25,6 +25,8 @@
  *   channel (512):  a_scale [T],             b_scale [E, 2I],                b1_scale [E, H]
  *   block   (1024): a_scale [T, ceil(H/128)], b_scale [E, ceil(2I/128), ceil(H/128)],
  *                   b1_scale [E, ceil(H/128), ceil(I/128)]
+ *   MXFP8   (2048): the scale pointers address UE8M0 bytes (value 2^(byte - 127)), not floats:
+ *                   a_scale [T, H/32], b_scale [E, 2I, H/32], b1_scale [E, H, I/32]
  */
 #ifndef DQMOE_H_
 #define DQMOE_H_
@@ -50,6 +52,10 @@ extern "C" {
 #define DQMOE_QUANT_FP8_TENSOR 256  /* FP8_QDQ      : per-tensor act scale, per-expert weight scale */
 #define DQMOE_QUANT_FP8_CHANNEL 512 /* FP8_ROWWISE  : per-token act scale, per-output-channel weight scale */
 #define DQMOE_QUANT_FP8_BLOCK 1024  /* FP8_BLOCKWISE: 1x128 act scales, 128x128 weight scales */
+/* MXFP8: e4m3 with one UE8M0 (power-of-two) scale byte per row and 32 K elements, activations and weights
+ * alike; the bit between FP8_BLOCKWISE (1 << 10) and FP4 (1 << 12), which the reference leaves unused
+ * (csrc/quantization.h:25-38). Needs H and I to be multiples of 128. */
+#define DQMOE_QUANT_FP8_MX 2048
 
 /* router scoring functions */
 #define DQMOE_SCORE_SOFTMAX 0 /* softmax over experts, top-k, renormalised to sum 1 */
@@ -344,6 +350,16 @@ int dqmoe_quant_fp8_tensor(const void* x_bf16, int e, int64_t numel_per, void* q
 int dqmoe_quant_fp8_tensor_static(const void* x_bf16, int e, int64_t numel_per, void* q, float* scale,
                                   dqmoe_stream_t stream);
 
+/*
+ * MXFP8 quantisers over bf16 input: q e4m3 [rows, cols], scale UE8M0 bytes [rows, cols/32] with
+ * s = 2^ceil(log2(max(amax, 1e-4) / 448)) per 32-element group (cols a multiple of 32). The second form
+ * gathers while it quantises: row r of the output is x[dest_to_src[r] / k] (negative entries are skipped).
+ * No counterpart in the reference (see DQMOE_QUANT_FP8_MX).
+ */
+int dqmoe_quant_mxfp8(const void* x_bf16, int64_t rows, int cols, void* q, uint8_t* scale, dqmoe_stream_t stream);
+int dqmoe_permute_quant_mxfp8(const void* x_bf16, int H, int k, const int32_t* dest_to_src, int n, void* q,
+                              uint8_t* scale, dqmoe_stream_t stream);
+
 /* ------------------------------------------------------------------ grouped GEMM */
 
 /*
@@ -372,6 +388,17 @@ int dqmoe_grouped_gemm(const void* a, const float* a_scale, const void* w, const
 int dqmoe_grouped_gemm_rows(const void* a, const float* a_scale, const void* w, const float* w_scale,
                             const int32_t* offsets, const int32_t* mtile_prefix, int n, int N, int K,
                             int E, int quant_mode, const void* row_dst, dqmoe_stream_t stream);
+
+/*
+ * The grouped GEMM in the MXFP8 mode (block-scaled tensor-core instruction, scales in TMEM): a [n, K] e4m3
+ * with a_sf [n, K/32], w [E, gated ? 2N : N, K] e4m3 with w_sf of the same rows and K/32 columns. Stage 1
+ * writes e4m3 [n, N] and out_sf [n, N/32]; stage 2 writes bf16 rows through dest_to_src (identity when NULL).
+ * K a multiple of 128; N a multiple of 128 in stage 1, of 8 in stage 2. No counterpart in the reference.
+ */
+int dqmoe_grouped_gemm_mx(const void* a, const uint8_t* a_sf, const void* w, const uint8_t* w_sf,
+                          const int32_t* offsets, const int32_t* mtile_prefix, int n, int N, int K, int E,
+                          int gated, void* out, uint8_t* out_sf, const int32_t* dest_to_src,
+                          dqmoe_stream_t stream);
 
 /* cumulative 128-row tile counts per expert from offsets[E+1] (device to device) */
 int dqmoe_mtile_prefix(const int32_t* offsets, int E, int32_t* mtile_prefix, dqmoe_stream_t stream);

@@ -34,6 +34,8 @@ AMAX_FLOOR = 1e-4
 GROUP = 128
 
 QUANT_NONE, QUANT_TENSOR, QUANT_CHANNEL, QUANT_BLOCK = 0, 256, 512, 1024
+QUANT_MX = 2048   # MXFP8: e4m3 with one UE8M0 scale per 32 elements (no counterpart in the reference)
+MX_GROUP = 32
 
 
 # ---------------------------------------------------------------------- quantisers
@@ -94,6 +96,29 @@ def quant_tensor(x: torch.Tensor, per_expert: bool = False) -> Tuple[torch.Tenso
     amax = x.abs().float().amax().view(*([1] * x.dim()))
     q, sf = _scale_and_cast(x, amax)
     return q.contiguous(), sf.reshape(1)
+
+
+def quant_mx(x: torch.Tensor) -> Tuple[torch.Tensor, torch.Tensor]:
+    """MXFP8 quantiser, parity unpinned (the reference reserves mode bits for block-scaled formats,
+    csrc/quantization.h:30-38, but has no code for them). Per 32 consecutive elements of the last dimension:
+    s = 2^ceil(log2(max(amax, 1e-4) / 448)), the smallest power of two that brings the group inside the e4m3
+    range (the rule of DeepGEMM's UE8M0 path, which the reference's README.md:11 names as its road map);
+    bytes = e4m3(x / s); the scale is stored as the biased exponent byte log2(s) + 127."""
+    n = x.shape[-1]
+    assert n % MX_GROUP == 0
+    g = x.float().reshape(*x.shape[:-1], n // MX_GROUP, MX_GROUP)
+    s = g.abs().amax(dim=-1, keepdim=True).clamp(min=AMAX_FLOOR) / FP8_MAX
+    bits = s.contiguous().view(torch.int32)
+    e = (bits >> 23) + ((bits & 0x7FFFFF) != 0).to(torch.int32)   # ceil(log2(s)) + 127
+    inv = ((254 - e) << 23).view(torch.float32)                   # 1 / s, exact
+    q = (g * inv).to(FP8)
+    return q.reshape(x.shape).contiguous(), e.to(torch.uint8).reshape(*x.shape[:-1], n // MX_GROUP)
+
+
+def dequant_mx(q: torch.Tensor, sf: torch.Tensor) -> torch.Tensor:
+    n = q.shape[-1]
+    scale = (sf.to(torch.int32) << 23).view(torch.float32)        # 2^(byte - 127)
+    return (q.float().reshape(*q.shape[:-1], n // MX_GROUP, MX_GROUP) * scale.unsqueeze(-1)).reshape(q.shape)
 
 
 # ---------------------------------------------------------------------- routing
@@ -197,7 +222,8 @@ def moe_layer_fp8(a_q, a_s, b_q, b_s, b1_q, b1_s, m_indices, E: int, quant_mode:
     (test/util.py:95-158): dequantise, fp32 linear, round to bf16, SwiGLU in bf16,
     re-quantise the intermediate, dequantise, fp32 linear, round to bf16. Channel and
     tensor modes apply the same steps with their scale shapes (parity unpinned: the
-    reference has no torch model of them). bias1 [E, 2I] / bias2 [E, H] (fp32, parity unpinned)
+    reference has no torch model of them), and so does the MXFP8 mode with its 1x32 power-of-two
+    scales (parity unpinned: the format is not in the reference). bias1 [E, 2I] / bias2 [E, H] (fp32, parity unpinned)
     are added to the fp32 products before the rounding to bf16."""
     T, k = m_indices.shape
     H = a_q.shape[1]
@@ -220,6 +246,9 @@ def moe_layer_fp8(a_q, a_s, b_q, b_s, b1_q, b1_s, m_indices, E: int, quant_mode:
         elif quant_mode == QUANT_TENSOR:
             dq_a = a_f[tok] * a_s.view(())
             dq_b = b_q[e].float() * b_s[e]
+        elif quant_mode == QUANT_MX:
+            dq_a = dequant_mx(a_q[tok], a_s[tok])
+            dq_b = dequant_mx(b_q[e], b_s[e])
         else:
             raise ValueError(quant_mode)
         inter = F.linear(dq_a, dq_b)
@@ -242,6 +271,10 @@ def moe_layer_fp8(a_q, a_s, b_q, b_s, b1_q, b1_s, m_indices, E: int, quant_mode:
             q, s = quant_rowwise(act)
             dq_act = q.float() * s
             dq_b1 = b1_q[e].float() * b1_s[e].view(-1, 1)
+        elif quant_mode == QUANT_MX:
+            q, s = quant_mx(act)
+            dq_act = dequant_mx(q, s)
+            dq_b1 = dequant_mx(b1_q[e], b1_s[e])
         else:
             q = (act * (1.0 / sf_all)).to(FP8)
             s = sf_all
@@ -285,6 +318,8 @@ def quantize_inputs(a, b, b1, quant_mode: int):
         return (*quant_rowwise(a), *quant_rowwise(b), *quant_rowwise(b1))
     if quant_mode == QUANT_TENSOR:
         return (*quant_tensor(a), *quant_tensor(b, per_expert=True), *quant_tensor(b1, per_expert=True))
+    if quant_mode == QUANT_MX:
+        return (*quant_mx(a), *quant_mx(b), *quant_mx(b1))
     raise ValueError(quant_mode)
 
 
