@@ -42,12 +42,17 @@ WORKLOADS = {
                desc="DeepSeek-V3-shape routed-expert layer, block FP8"),
     "c4": dict(T=16384, H=2048, I=768, E=128, k=8, mode=512, scoring="softmax",
                desc="Qwen-MoE-shape channel-wise layer, Zipf(1.1) expert bias"),
+    # the Mixtral shape of c2 in the added MXFP8 mode (1x32 UE8M0 scales on the block-scaled tensor-core instruction)
+    "c2-mx": dict(T=4096, H=4096, I=14336, E=8, k=2, mode=2048, scoring="softmax",
+                  desc="Mixtral-8x7B-shape prefill layer, MXFP8 (1x32 power-of-two scales)"),
+    "c3-mx": dict(T=8192, H=7168, I=2048, E=256, k=8, mode=2048, scoring="sigmoid",
+                  desc="DeepSeek-V3-shape routed-expert layer, MXFP8 (1x32 power-of-two scales)"),
 }
 # dram__bytes_read.sum + dram__bytes_write.sum of one fc1 launch divided by the launch's algorithmic bytes, from
 # ncu captures of the same kernel (ncu cannot run inside a timed bench; the ratio scales the algorithmic bytes
 # that are computed here for the workload at hand)
-NCU_FC1_TRAFFIC_RATIO = {1024: 1.004, 512: 1.0, 256: 1.0, 0: 1.0}
-MODE_NAME = {0: "bf16", 256: "fp8-tensor", 512: "fp8-channel", 1024: "fp8-block"}
+NCU_FC1_TRAFFIC_RATIO = {1024: 1.004, 512: 1.0, 256: 1.0, 0: 1.0, 2048: 1.0}
+MODE_NAME = {0: "bf16", 256: "fp8-tensor", 512: "fp8-channel", 1024: "fp8-block", 2048: "mxfp8"}
 COS_MIN, REL_MAX = 0.999, 2e-2  # layer tolerance against the oracle: cosine and max|x - ref| / max|ref|
 
 
@@ -241,6 +246,8 @@ def quantize_weights_gpu(ops, b, b1, mode):
         return bq, bs.view(E, -1), b1q, b1s.view(E, -1)
     if mode == 256:
         return (*ops.per_tensor_cast_to_fp8(b, per_expert=True), *ops.per_tensor_cast_to_fp8(b1, per_expert=True))
+    if mode == 2048:
+        return (*ops.mx_cast_weights_to_fp8(b), *ops.mx_cast_weights_to_fp8(b1))
     return b, None, b1, None
 
 
@@ -266,6 +273,8 @@ def quantize_activations_gpu(ops, x, mode):
         return q, s.view(-1)
     if mode == 256:
         return ops.per_tensor_cast_to_fp8(x)
+    if mode == 2048:
+        return ops.mx_cast_to_fp8(x)
     return x, None
 
 
@@ -294,6 +303,9 @@ def fc1_algorithmic_bytes(n, H, I, E, mode):
         scales = n * g(H) * 4 + E * g(2 * I) * g(H) * 4 + n * g(I) * 4
     elif mode == 512:
         scales = n * 4 * 2 + E * 2 * I * 4
+    elif mode == 2048:
+        out = n * I
+        scales = n * H // 32 + E * 2 * I * H // 32 + n * I // 32
     return w + a + out + scales
 
 
@@ -334,6 +346,8 @@ def cpu_baseline(wl, sample_tokens, seed=0, steps=1, warmup=0, ops=None, device=
     parity = None
     if ops is not None:
         dev_in = [t.to(device).contiguous() for t in qs] if mode else [x.to(device), None, b.to(device), None, b1.to(device), None]
+        if mode == 2048:  # the layer takes the weights' scale bytes in the tiled layout
+            dev_in[3], dev_in[5] = ops.mx_tile_scales(dev_in[3], H), ops.mx_tile_scales(dev_in[5], I)
         if mode == 512:
             dev_in[1], dev_in[3], dev_in[5] = dev_in[1].view(-1), dev_in[3].view(E, -1), dev_in[5].view(E, -1)
         ws = torch.empty(ops.moe_workspace_bytes(T, H, I, E, k, mode) + 256, dtype=torch.uint8, device=device)
@@ -700,7 +714,13 @@ def run_prefill(args, name, wl, ops, dev, rank, world, local_rank, dist=None, ep
         gated_out = torch.empty(n * I * 2, dtype=torch.uint8, device=dev)
         sa1 = as_.data_ptr() if mode == 256 else p_perm_s
 
+        def fc1_mx():
+            _lib.check(lib.dqmoe_grouped_gemm_mx(p_perm, p_perm_s, bq.data_ptr(), bs.data_ptr(), p_off, p_mt, n, I, H, E, 1,
+                                                 gated_out.data_ptr(), p_act_s, None, stream))
+
         def fc1():  # on the step's own expert-sorted (ragged) rows, as left in the workspace by the last step
+            if mode == 2048:
+                return fc1_mx()
             _lib.check(lib.dqmoe_grouped_gemm(p_perm, sa1, bq.data_ptr(), bs.data_ptr() if bs is not None else None,
                                               p_off, p_mt, n, I, H, E, mode, 1, gated_out.data_ptr(), p_act_s,
                                               scratch_amax.data_ptr(), None, stream))
@@ -940,7 +960,8 @@ def main():
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=20)
     ap.add_argument("--warmup", type=int, default=5)
-    ap.add_argument("--workload", default="c2", choices=sorted(WORKLOADS) + ["c5"])
+    ap.add_argument("--workload", default="c2", choices=sorted(WORKLOADS) + ["c5"],
+                    help="c2 (default, the headline), c3, c4, c5 (decode sweep), c1 (CPU-size), c2-mx / c3-mx (added MXFP8 mode)")
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-extras", action="store_true", help="headline workload only: no c3/c4/c5/moe_block records")

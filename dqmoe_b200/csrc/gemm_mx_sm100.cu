@@ -3,12 +3,18 @@
 // (tcgen05.mma.kind::mxf8f6f4.block_scale reads them from TMEM columns), so the fp32 accumulator stays in TMEM
 // for the whole K loop: no per-128-K promotion through registers as the fp32-scaled block mode of
 // gemm_sm100.cu needs. Same persistent, warp-specialised structure otherwise:
-//   warp 0     TMA producer (activation rows + two weight boxes per 128-byte K stage, no cluster broadcast)
+//   warp 0     TMA producer: activation rows + two weight boxes per 128-byte K stage, and the stage's three
+//              512-byte scale blocks by untiled bulk copies (no cluster broadcast anywhere)
 //   warp 1     MMA issuer: per stage three tcgen05.cp (scale bytes -> TMEM) and four block-scaled MMAs
-//   warp 2     scale loader: 4-byte asynchronous copies that lay the stage's scale bytes out in shared memory
-//              the way tcgen05.cp wants them
 //   warps 4-11 epilogue: stage 1 SwiGLU + MXFP8 re-quantisation (each thread owns whole 32-column scale groups
 //              of its row), stage 2 bf16 rows scattered to d[T, k, H] or to explicit row addresses
+// Scale layout in global memory ("tiled"): one 512-byte block per 128 rows and 128 K elements, holding the
+// block's 128 x 4 scale bytes in the order tcgen05.cp.32x128b.warpx4 wants them in shared memory - row r of the
+// block at byte (r % 32) * 16 + (r / 32) * 4, its four bytes in K order. Blocks are indexed [row block][K block].
+// Weight rows form blocks by their row index; activation rows by their tile (cumulative 128-row tile of the
+// expert sort + row within the expert), so that tiles of ragged experts still find their scales in whole blocks.
+// (4-byte copies that built this layout in shared memory from row-major scales were measured first: they cost
+// 45 % of the kernel's throughput.)
 // TMEM budget: two 256-column accumulators and the scale columns do not fit 512 columns side by side, so the
 // two accumulators overlap by 24 columns; the epilogue of a tile drains the chunk holding those columns first
 // and signals it, and only that signal (not the whole epilogue) gates the next tile's first MMA.
@@ -57,10 +63,11 @@ struct Params {
     int kb_count;        // K / 128
     const int* offsets;
     const int* mtile_prefix;
-    const uint8_t* sfa;  // [n_rows, K/32] UE8M0
-    const uint8_t* sfb;  // [E * w_rows, K/32] UE8M0
+    int w_blocks;        // E * w_rows / 128: 128-row blocks of the weight scales
+    const uint8_t* sfa;  // tiled UE8M0 scales of the activations: [row tiles][K/128][512]
+    const uint8_t* sfb;  // tiled UE8M0 scales of the weights: [E * w_rows / 128][K/128][512]
     void* out;
-    uint8_t* out_sf;     // stage 1: [n_rows, N/32] UE8M0
+    uint8_t* out_sf;     // stage 1: tiled scales of the output, [row tiles][N/128][512]
     const float* bias;   // [E, w_rows] fp32 or nullptr
     const int* dest_to_src;
     const unsigned long long* row_dst;
@@ -68,7 +75,7 @@ struct Params {
 };
 
 struct Shared {
-    uint64_t full[kStages];
+    uint64_t full[kStages];     // operands and scale blocks of a stage have landed
     uint64_t empty[kStages];
     uint64_t tmem_full[2];
     uint64_t tmem_empty[2];
@@ -85,6 +92,7 @@ constexpr size_t kSmemBytes = 1024 + size_t(kStages) * kStageBytes + sizeof(Shar
 
 struct Tile {
     int e, row0, row_end, nt;
+    int mtile;  // index of the row tile among all row tiles of the expert sort
 };
 __device__ __forceinline__ Tile decode_tile(int t, int& e_cursor, const Shared& st, int n_tiles) {
     while (t >= st.mprefix[e_cursor + 1] * n_tiles) ++e_cursor;
@@ -93,6 +101,7 @@ __device__ __forceinline__ Tile decode_tile(int t, int& e_cursor, const Shared& 
     Tile tl;
     tl.e = e_cursor;
     tl.nt = local / mtiles;
+    tl.mtile = st.mprefix[e_cursor] + local % mtiles;
     tl.row0 = st.offsets[e_cursor] + (local % mtiles) * kBM;
     tl.row_end = st.offsets[e_cursor + 1];
     return tl;
@@ -121,7 +130,7 @@ moe_GemmGrouped_GemmUniversal_tcgen05_mx(const __grid_constant__ CUtensorMap tma
 
     if (threadIdx.x == 0) {
         for (int s = 0; s < kStages; ++s) {
-            ptx::mbar_init(&st.full[s], 2);   // the TMA producer's expect_tx arrival + the scale loader
+            ptx::mbar_init(&st.full[s], 1);
             ptx::mbar_init(&st.empty[s], 1);
         }
         for (int b = 0; b < 2; ++b) {
@@ -165,6 +174,9 @@ moe_GemmGrouped_GemmUniversal_tcgen05_mx(const __grid_constant__ CUtensorMap tma
                 const Tile tl = decode_tile(t, e_cursor, st, p.n_tiles);
                 const int wrow0 = tl.e * p.w_rows + tl.nt * p.tile_w_rows;
                 const int wrow1 = wrow0 + p.box2_off;
+                const uint8_t* sf_a = p.sfa + size_t(tl.mtile) * kb_count * kSfBlock;
+                const uint8_t* sf_b0 = p.sfb + size_t(min(wrow0 >> 7, p.w_blocks - 1)) * kb_count * kSfBlock;
+                const uint8_t* sf_b1 = p.sfb + size_t(min(wrow1 >> 7, p.w_blocks - 1)) * kb_count * kSfBlock;
                 for (int kb = 0; kb < kb_count; ++kb, ++it) {
                     const int s = it % kStages;
                     if (!ptx::mbar_wait(&st.empty[s], ((it / kStages) & 1u) ^ 1u, abort_flag, kWaitLimit)) {
@@ -173,10 +185,13 @@ moe_GemmGrouped_GemmUniversal_tcgen05_mx(const __grid_constant__ CUtensorMap tma
                     }
                     uint8_t* sa = smem + size_t(s) * kStageBytes;
                     uint8_t* sb = sa + kABytes;
-                    ptx::mbar_arrive_expect_tx(&st.full[s], kStageBytes);
+                    ptx::mbar_arrive_expect_tx(&st.full[s], kStageBytes + kSfStage);
                     ptx::tma_load_2d(sa, &tma_a, kb * kBK, tl.row0, &st.full[s]);
                     ptx::tma_load_2d(sb, &tma_b, kb * kBK, wrow0, &st.full[s]);
                     ptx::tma_load_2d(sb + kBox * kBK, &tma_b, kb * kBK, wrow1, &st.full[s]);
+                    ptx::bulk_load(&st.sf[s][0], sf_a + size_t(kb) * kSfBlock, kSfBlock, &st.full[s]);
+                    ptx::bulk_load(&st.sf[s][kSfBlock], sf_b0 + size_t(kb) * kSfBlock, kSfBlock, &st.full[s]);
+                    ptx::bulk_load(&st.sf[s][2 * kSfBlock], sf_b1 + size_t(kb) * kSfBlock, kSfBlock, &st.full[s]);
                 }
             }
         }
@@ -225,54 +240,6 @@ moe_GemmGrouped_GemmUniversal_tcgen05_mx(const __grid_constant__ CUtensorMap tma
             }
         }
         __syncwarp();
-      } else if (warp == 2) {
-        // ------------------------------------------------------------ scale loader
-        // Row r of a 128-row block keeps its four scale bytes of this K stage (one 32-bit word of the row-major
-        // scale matrix) at byte (r % 32) * 16 + (r / 32) * 4 of the block: the order tcgen05.cp.32x128b.warpx4
-        // copies into TMEM. The copies of stage i are signalled when stage i + 1 has been issued, after a
-        // fence that makes them visible to the tensor core's reads of shared memory.
-        const size_t ks = size_t(p.K) / 32;  // scale bytes per row
-        const long long last_w = (long long) p.E * p.w_rows - 1;
-        uint32_t it = 0;
-        int e_cursor = 0;
-        bool ok = true;
-        int prev_s = -1;
-        for (int t = tile_first; ok && t < total_tiles; t += tile_step) {
-            const Tile tl = decode_tile(t, e_cursor, st, p.n_tiles);
-            const long long wrow0 = (long long) tl.e * p.w_rows + (long long) tl.nt * p.tile_w_rows;
-            const uint8_t* src[12];
-#pragma unroll
-            for (int j = 0; j < 4; ++j) {
-                src[j] = p.sfa + size_t(min(tl.row0 + lane + 32 * j, p.n_rows - 1)) * ks;
-                long long r0 = wrow0 + lane + 32 * j, r1 = wrow0 + p.box2_off + lane + 32 * j;
-                src[4 + j] = p.sfb + size_t(r0 < last_w ? r0 : last_w) * ks;
-                src[8 + j] = p.sfb + size_t(r1 < last_w ? r1 : last_w) * ks;
-            }
-            for (int kb = 0; kb < kb_count; ++kb, ++it) {
-                const int s = it % kStages;
-                if (!ptx::mbar_wait(&st.empty[s], ((it / kStages) & 1u) ^ 1u, abort_flag, kWaitLimit)) {
-                    ok = false;
-                    break;
-                }
-                uint8_t* dst = &st.sf[s][0] + lane * 16;
-#pragma unroll
-                for (int j = 0; j < 12; ++j) ptx::cp_async4(dst + (j >> 2) * kSfBlock + (j & 3) * 4, src[j] + kb * 4);
-                ptx::cp_async_commit_group();
-                if (prev_s >= 0) {
-                    ptx::cp_async_wait_group<1>();  // everything but the group just committed has landed
-                    ptx::fence_proxy_async();
-                    __syncwarp();
-                    if (lane == 0) ptx::mbar_arrive(&st.full[prev_s]);
-                }
-                prev_s = s;
-            }
-        }
-        ptx::cp_async_wait_all();
-        if (ok && prev_s >= 0) {
-            ptx::fence_proxy_async();
-            __syncwarp();
-            if (lane == 0) ptx::mbar_arrive(&st.full[prev_s]);
-        }
       }
     } else {
         ptx::setmaxnreg_inc<kRegsEpilogue>();
@@ -372,8 +339,10 @@ moe_GemmGrouped_GemmUniversal_tcgen05_mx(const __grid_constant__ CUtensorMap tma
                 store_rows_staged(st.stage[warp - 4], packed,
                                   row_ok ? static_cast<uint8_t*>(p.out) + size_t(grow) * N + colh : nullptr,
                                   min(4, max(0, (N - colh + 15) / 16)), lane);
-                if (row_ok && colh < N)
-                    *reinterpret_cast<uint16_t*>(p.out_sf + size_t(grow) * (N / 32) + (colh >> 5)) = uint16_t(sf_bytes);
+                // scale bytes of this row's two groups into the tile's block of the next GEMM's K block nt (written for
+                // all 128 rows of the tile: the block belongs to this tile alone)
+                *reinterpret_cast<uint16_t*>(p.out_sf + (size_t(tl.mtile) * (N / 128) + tl.nt) * kSfBlock + (r_in_tile & 31) * 16 +
+                                             (r_in_tile >> 5) * 4 + h * 2) = uint16_t(sf_bytes);
             } else {
                 int orow_idx = grow;
                 if (row_ok && p.dest_to_src != nullptr) orow_idx = p.dest_to_src[grow];
@@ -427,7 +396,6 @@ moe_GemmGrouped_GemmUniversal_tcgen05_mx(const __grid_constant__ CUtensorMap tma
         }
         for (int i = 0; i < 2000; ++i) __nanosleep(1000);
     }
-    ptx::cp_async_wait_all();
     ptx::tc_fence_before();
     __syncthreads();
     if (warp == 1) {
@@ -462,13 +430,12 @@ int grouped_gemm_mx(const void* a, const uint8_t* a_sf, const void* w, const uin
     DQ_CHECK(n >= 0 && N > 0 && K > 0 && E > 0 && E <= kMaxExperts);
     if (n == 0) return DQMOE_OK;
     DQ_CHECK_FMT(K % 128 == 0, "K=%d: the MXFP8 mode needs the reduction length to be a multiple of 128", K);
-    DQ_CHECK_FMT(N % (gated ? 128 : 8) == 0, "N=%d: MXFP8 stage %d needs a multiple of %d output columns", N, gated ? 1 : 2,
-                 gated ? 128 : 8);
+    DQ_CHECK_FMT(N % 128 == 0, "N=%d: the MXFP8 mode needs a multiple of 128 output columns", N);
     DQ_CHECK(a != nullptr && w != nullptr && a_sf != nullptr && w_sf != nullptr && offsets != nullptr && mtile_prefix != nullptr);
     DQ_CHECK((out != nullptr || row_dst != nullptr) && (row_dst == nullptr || !gated));
-    DQ_CHECK(is_aligned(a, 16) && is_aligned(w, 16) && is_aligned(out, 16) && is_aligned(row_dst, 8) && is_aligned(a_sf, 4) &&
-             is_aligned(w_sf, 4));
-    if (gated) DQ_CHECK(out_sf != nullptr && is_aligned(out_sf, 4));
+    DQ_CHECK(is_aligned(a, 16) && is_aligned(w, 16) && is_aligned(out, 16) && is_aligned(row_dst, 8) && is_aligned(a_sf, 16) &&
+             is_aligned(w_sf, 16));
+    if (gated) DQ_CHECK(out_sf != nullptr && is_aligned(out_sf, 16));
     Params p;
     p.n_rows = n;
     p.N = N;
@@ -479,6 +446,8 @@ int grouped_gemm_mx(const void* a, const uint8_t* a_sf, const void* w, const uin
     p.tile_w_rows = gated ? kBox : kN;
     p.box2_off = gated ? N : kBox;
     p.kb_count = K / kBK;
+    DQ_CHECK_FMT(p.w_rows % 128 == 0, "N=%d: weight rows per expert must be a multiple of 128 in the MXFP8 mode", N);
+    p.w_blocks = int(int64_t(E) * p.w_rows / 128);
     p.offsets = offsets;
     p.mtile_prefix = mtile_prefix;
     p.sfa = a_sf;

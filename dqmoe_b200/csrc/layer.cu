@@ -70,12 +70,14 @@ static Layout make_layout(int T, int H, int I, int E, int k, int quant_mode, int
     L.sort_ws = add(L.sort_ws_bytes);
     L.dest_to_src = add(n * sizeof(int));
     L.perm_a = add(n * H * esz);
-    // fp32 words of scale per row: block mode one per 128 columns; MX mode H/32 UE8M0 bytes = H/128 words
-    L.perm_scale_cols = quant_mode == DQMOE_QUANT_FP8_BLOCK || quant_mode == DQMOE_QUANT_FP8_MX ? ceil_div(H, 128)
+    L.perm_scale_cols = quant_mode == DQMOE_QUANT_FP8_BLOCK ? ceil_div(H, 128)
                         : quant_mode == DQMOE_QUANT_FP8_CHANNEL ? 1 : 0;
-    L.perm_a_scale = add(n * L.perm_scale_cols * sizeof(float));
+    // MX mode: UE8M0 scale bytes in the tiled layout, whole 512-byte blocks per 128-row tile of the expert sort
+    const bool mx = quant_mode == DQMOE_QUANT_FP8_MX;
+    L.perm_a_scale = add(mx ? dqmoe_mx_tiled_scale_bytes(int64_t(n), E, align_up(H, 128)) : n * L.perm_scale_cols * sizeof(float));
     L.act = add(n * I * esz);
-    const size_t act_scale_elems = quant_mode == DQMOE_QUANT_FP8_BLOCK || quant_mode == DQMOE_QUANT_FP8_MX ? n * ceil_div(I, 128)
+    const size_t act_scale_elems = mx ? dqmoe_mx_tiled_scale_bytes(int64_t(n), E, align_up(I, 128)) / sizeof(float)
+                                   : quant_mode == DQMOE_QUANT_FP8_BLOCK ? n * ceil_div(I, 128)
                                    : quant_mode == DQMOE_QUANT_FP8_CHANNEL ? n
                                    : quant_mode == DQMOE_QUANT_FP8_TENSOR ? 1 : 0;
     L.act_scale = add(act_scale_elems * sizeof(float));
@@ -171,7 +173,12 @@ static int moe_forward_impl(const void* a, const float* a_scale, const void* b, 
                             L.perm_scale_cols, L.perm_scale_cols ? perm_a_scale : nullptr, stream);
     if (rc != DQMOE_OK) return rc;
 
-    if (quant_mode == DQMOE_QUANT_FP8_MX) {  // the scale pointers address UE8M0 bytes in this mode
+    if (quant_mode == DQMOE_QUANT_FP8_MX) {
+        // the scale pointers address UE8M0 bytes in this mode: the activations' row-major [T, H/32], gathered here
+        // into the tiled layout of the expert sort; the weights' already tiled
+        rc = dqmoe_mx_tile_scales(reinterpret_cast<const uint8_t*>(a_scale), n, H, dest_to_src, k, offsets, mtile_prefix, E,
+                                  reinterpret_cast<uint8_t*>(perm_a_scale), stream);
+        if (rc != DQMOE_OK) return rc;
         rc = gemm_mx::grouped_gemm_mx(perm_a, reinterpret_cast<const uint8_t*>(perm_a_scale), b,
                                       reinterpret_cast<const uint8_t*>(b_scale), offsets, mtile_prefix, n, I, H, E, 1, act,
                                       reinterpret_cast<uint8_t*>(act_scale), nullptr, nullptr, bias1, stream);
@@ -337,7 +344,8 @@ static int moe_block_impl(const void* x_bf16, const float* logits, const void* b
                            L.sort_ws_bytes, stream);
     if (rc != DQMOE_OK) return rc;
     if (quant_mode == DQMOE_QUANT_FP8_MX) {  // the same fusion with 1x32 power-of-two scales
-        rc = dqmoe_permute_quant_mxfp8(x_bf16, H, k, dest_to_src, n, perm_a, reinterpret_cast<uint8_t*>(perm_a_scale), stream);
+        rc = dqmoe_permute_quant_mxfp8(x_bf16, H, k, dest_to_src, n, offsets, mtile_prefix, E, perm_a,
+                                       reinterpret_cast<uint8_t*>(perm_a_scale), stream);
         if (rc != DQMOE_OK) return rc;
         rc = gemm_mx::grouped_gemm_mx(perm_a, reinterpret_cast<const uint8_t*>(perm_a_scale), b,
                                       reinterpret_cast<const uint8_t*>(b_scale), offsets, mtile_prefix, n, I, H, E, 1, act,

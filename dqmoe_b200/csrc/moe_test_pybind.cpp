@@ -64,14 +64,16 @@ void run(const TensorPair& a, const TensorPair& b, const TensorPair& b1, const t
     const float* sfb1 = nullptr;
     int mode = 0;
     if (fp8) {
-        MT_CHECK(quant_mode_value == 256 || quant_mode_value == 512 || quant_mode_value == 1024,
+        MT_CHECK(quant_mode_value == 256 || quant_mode_value == 512 || quant_mode_value == 1024 || quant_mode_value == 2048,
                  "got " + std::to_string(quant_mode_value));
+        // 2048 = MXFP8, an added mode (include/dqmoe.h): its scale tensors hold UE8M0 bytes
+        const auto want_s = quant_mode_value == 2048 ? torch::kByte : torch::kFloat;
         for (const torch::Tensor* s : {&a.second, &b.second, &b1.second})
-            MT_CHECK(s->scalar_type() == torch::kFloat && s->is_contiguous() && s->is_cuda(),
-                     "scale tensors are contiguous fp32 CUDA tensors");
-        sfa = a.second.data_ptr<float>();
-        sfb = b.second.data_ptr<float>();
-        sfb1 = b1.second.data_ptr<float>();
+            MT_CHECK(s->scalar_type() == want_s && s->is_contiguous() && s->is_cuda(),
+                     "scale tensors are contiguous CUDA tensors, fp32 (UE8M0 bytes in the MXFP8 mode)");
+        sfa = static_cast<const float*>(a.second.data_ptr());
+        sfb = static_cast<const float*>(b.second.data_ptr());
+        sfb1 = static_cast<const float*>(b1.second.data_ptr());
         mode = quant_mode_value;
     }
     // bf16: the scale halves are dummy tensors (test/util.py:232-234) and are not read

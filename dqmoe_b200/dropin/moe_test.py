@@ -56,11 +56,13 @@ def _run(a, b, b1, d, m_indices, workspace, quant_mode_value, fused, fp8):
     if d.dtype != torch.bfloat16:
         _fail("d.scalar_type() == torch::kBFloat16")
     if fp8:
-        if quant_mode_value not in (256, 512, 1024):
-            _fail("quant_mode_value in (256, 512, 1024)", f"got {quant_mode_value}")
+        if quant_mode_value not in (256, 512, 1024, 2048):
+            _fail("quant_mode_value in (256, 512, 1024, 2048)", f"got {quant_mode_value}")
+        # 2048 = MXFP8, an added mode (include/dqmoe.h): its scale tensors hold UE8M0 bytes
+        want_s = torch.uint8 if quant_mode_value == 2048 else torch.float32
         for name, s in (("sfa", sfa), ("sfb", sfb), ("sfb1", sfb1)):
-            if s.dtype != torch.float32 or not s.is_contiguous() or not s.is_cuda:
-                _fail(f"{name} is a contiguous fp32 CUDA tensor")
+            if s.dtype != want_s or not s.is_contiguous() or not s.is_cuda:
+                _fail(f"{name} is a contiguous {want_s} CUDA tensor")
         mode = quant_mode_value
     else:
         # the scale halves are dummy tensors in this mode (test/util.py:232-234) and are not read

@@ -61,7 +61,7 @@ def _check_scales(a_scale, b_scale, b1_scale, T, H, I, E, quant_mode):
     g = lambda x: (x + 127) // 128
     want = {QUANT_FP8_TENSOR: (1, E, E), QUANT_FP8_CHANNEL: (T, E * 2 * I, E * H),
             QUANT_FP8_BLOCK: (T * g(H), E * g(2 * I) * g(H), E * g(H) * g(I)),
-            QUANT_FP8_MX: (T * H // 32, E * 2 * I * H // 32, E * H * I // 32)}[quant_mode]
+            QUANT_FP8_MX: (T * H // 32, E * 2 * I * H // 32, E * H * I // 32)}[quant_mode]  # weights' tiled: same size
     dtype = torch.uint8 if quant_mode == QUANT_FP8_MX else torch.float32  # MXFP8 scales are UE8M0 bytes
     for name, t, n in zip(("a_scale", "b_scale", "b1_scale"), (a_scale, b_scale, b1_scale), want):
         if t is None or not t.is_cuda or t.dtype != dtype or not t.is_contiguous() or t.numel() != n:
@@ -366,16 +366,43 @@ def mx_cast_to_fp8(x: torch.Tensor):
     return q, s
 
 
-def moe_permute_quant_mx(x: torch.Tensor, dest_to_src: torch.Tensor, k: int):
-    """Gather fused with the MXFP8 quantisation of bf16 activations x [T, H]."""
+def mx_tile_scales(sf: torch.Tensor, cols: int, offsets=None, mtile_pref=None, dest_to_src=None, k: int = 1) -> torch.Tensor:
+    """Row-major UE8M0 scale bytes [..., cols/32] -> the tiled layout the MXFP8 grouped GEMM reads (see
+    dqmoe_mx_tile_scales). Without offsets the rows form 128-row blocks by their index (weights); with offsets /
+    mtile_pref [E+1] they are expert-sorted activation rows; dest_to_src gathers rows of `sf` first."""
+    _cuda(sf, "sf")
+    assert sf.dtype == torch.uint8 and sf.shape[-1] == cols // 32
+    lib = _lib.load()
+    rows = dest_to_src.numel() if dest_to_src is not None else sf.numel() // (cols // 32)
+    E = offsets.numel() - 1 if offsets is not None else 0
+    nbytes = int(lib.dqmoe_mx_tiled_scale_bytes(rows, E, cols))
+    out = torch.zeros(max(nbytes, 16), dtype=torch.uint8, device=sf.device)
+    with torch.cuda.device(sf.device):
+        _lib.check(lib.dqmoe_mx_tile_scales(_p(sf), rows, cols, _p(dest_to_src), k, _p(offsets), _p(mtile_pref), E, _p(out),
+                                            _stream(sf.device)))
+    return out
+
+
+def mx_cast_weights_to_fp8(w: torch.Tensor):
+    """MXFP8 weights [E, rows, cols] (rows a multiple of 128): (e4m3 bytes, scale bytes in the tiled layout)."""
+    q, s = mx_cast_to_fp8(w)
+    return q, mx_tile_scales(s, w.shape[-1])
+
+
+def moe_permute_quant_mx(x: torch.Tensor, dest_to_src: torch.Tensor, k: int, offsets: torch.Tensor,
+                         mtile_pref: torch.Tensor):
+    """Gather fused with the MXFP8 quantisation of bf16 activations x [T, H]; scales come out tiled."""
     _cuda(x, "x")
     _cuda(dest_to_src, "dest_to_src")
     assert x.dtype == torch.bfloat16
+    lib = _lib.load()
     n, H = dest_to_src.numel(), x.shape[1]
+    E = offsets.numel() - 1
     q = torch.empty((n, H), dtype=FP8, device=x.device)
-    s = torch.empty((n, H // 32), dtype=torch.uint8, device=x.device)
+    s = torch.zeros(max(int(lib.dqmoe_mx_tiled_scale_bytes(n, E, H)), 16), dtype=torch.uint8, device=x.device)
     with torch.cuda.device(x.device):
-        _lib.check(_lib.load().dqmoe_permute_quant_mxfp8(_p(x), H, k, _p(dest_to_src), n, _p(q), _p(s), _stream(x.device)))
+        _lib.check(lib.dqmoe_permute_quant_mxfp8(_p(x), H, k, _p(dest_to_src), n, _p(offsets), _p(mtile_pref), E, _p(q),
+                                                 _p(s), _stream(x.device)))
     return q, s
 
 

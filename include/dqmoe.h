@@ -26,7 +26,8 @@
  *   block   (1024): a_scale [T, ceil(H/128)], b_scale [E, ceil(2I/128), ceil(H/128)],
  *                   b1_scale [E, ceil(H/128), ceil(I/128)]
  *   MXFP8   (2048): the scale pointers address UE8M0 bytes (value 2^(byte - 127)), not floats:
- *                   a_scale [T, H/32], b_scale [E, 2I, H/32], b1_scale [E, H, I/32]
+ *                   a_scale [T, H/32] row-major; b_scale (E * 2I rows, H columns) and b1_scale (E * H rows,
+ *                   I columns) in the tiled layout of dqmoe_mx_tile_scales (same byte count as row-major)
  */
 #ifndef DQMOE_H_
 #define DQMOE_H_
@@ -351,14 +352,31 @@ int dqmoe_quant_fp8_tensor_static(const void* x_bf16, int e, int64_t numel_per, 
                                   dqmoe_stream_t stream);
 
 /*
- * MXFP8 quantisers over bf16 input: q e4m3 [rows, cols], scale UE8M0 bytes [rows, cols/32] with
- * s = 2^ceil(log2(max(amax, 1e-4) / 448)) per 32-element group (cols a multiple of 32). The second form
- * gathers while it quantises: row r of the output is x[dest_to_src[r] / k] (negative entries are skipped).
- * No counterpart in the reference (see DQMOE_QUANT_FP8_MX).
+ * MXFP8 (see DQMOE_QUANT_FP8_MX; no counterpart in the reference). Quantiser over bf16 input: q e4m3
+ * [rows, cols], scale UE8M0 bytes [rows, cols/32] row-major, s = 2^ceil(log2(max(amax, 1e-4) / 448)) per
+ * 32-element group (cols a multiple of 32).
  */
 int dqmoe_quant_mxfp8(const void* x_bf16, int64_t rows, int cols, void* q, uint8_t* scale, dqmoe_stream_t stream);
-int dqmoe_permute_quant_mxfp8(const void* x_bf16, int H, int k, const int32_t* dest_to_src, int n, void* q,
-                              uint8_t* scale, dqmoe_stream_t stream);
+/*
+ * The grouped GEMM reads scales in a tiled layout: one 512-byte block per 128 rows and 128 columns, row r of
+ * the block at byte (r % 32) * 16 + (r / 32) * 4 with its four scale bytes in column order (the order the
+ * tensor core's scale copy wants in shared memory), blocks indexed [row block][column block]. Rows form row
+ * blocks by their index (weights: offsets == NULL, rows a multiple of 128) or, for expert-sorted activation
+ * rows, by tile: block mtile_prefix[e] + (r - offsets[e]) / 128, row (r - offsets[e]) % 128 (offsets and
+ * mtile_prefix [E+1] as dqmoe_route_sort / dqmoe_mtile_prefix give them), so that every 128-row tile of a
+ * ragged expert owns whole blocks. dqmoe_mx_tile_scales converts row-major scales [*, cols/32] (cols a multiple
+ * of 128); with dest_to_src != NULL output row r takes the scales of input row dest_to_src[r] / k (the
+ * expert-sort gather; negative entries are skipped). dqmoe_mx_tiled_scale_bytes: size of the tiled buffer for
+ * `rows` rows (E_sorted = number of experts for expert-sorted rows, 0 for rows that form blocks by index).
+ */
+size_t dqmoe_mx_tiled_scale_bytes(int64_t rows, int E_sorted, int cols);
+int dqmoe_mx_tile_scales(const uint8_t* scale_rows, int64_t rows, int cols, const int32_t* dest_to_src, int k,
+                         const int32_t* offsets, const int32_t* mtile_prefix, int E, uint8_t* scale_tiled,
+                         dqmoe_stream_t stream);
+/* Gather fused with the quantiser: q[r] = quant(x[dest_to_src[r] / k]), scales written tiled (H a multiple of 128). */
+int dqmoe_permute_quant_mxfp8(const void* x_bf16, int H, int k, const int32_t* dest_to_src, int n,
+                              const int32_t* offsets, const int32_t* mtile_prefix, int E, void* q,
+                              uint8_t* scale_tiled, dqmoe_stream_t stream);
 
 /* ------------------------------------------------------------------ grouped GEMM */
 
@@ -391,9 +409,10 @@ int dqmoe_grouped_gemm_rows(const void* a, const float* a_scale, const void* w, 
 
 /*
  * The grouped GEMM in the MXFP8 mode (block-scaled tensor-core instruction, scales in TMEM): a [n, K] e4m3
- * with a_sf [n, K/32], w [E, gated ? 2N : N, K] e4m3 with w_sf of the same rows and K/32 columns. Stage 1
- * writes e4m3 [n, N] and out_sf [n, N/32]; stage 2 writes bf16 rows through dest_to_src (identity when NULL).
- * K a multiple of 128; N a multiple of 128 in stage 1, of 8 in stage 2. No counterpart in the reference.
+ * expert-sorted rows, w [E, gated ? 2N : N, K] e4m3; a_sf and w_sf in the tiled layout above (a_sf by tiles of
+ * the expert sort, w_sf by row index). Stage 1 writes e4m3 [n, N] and out_sf, tiled like a_sf, ready to be the
+ * next GEMM's a_sf; stage 2 writes bf16 rows through dest_to_src (identity when NULL). K and N multiples of
+ * 128. No counterpart in the reference.
  */
 int dqmoe_grouped_gemm_mx(const void* a, const uint8_t* a_sf, const void* w, const uint8_t* w_sf,
                           const int32_t* offsets, const int32_t* mtile_prefix, int n, int N, int K, int E,
