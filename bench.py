@@ -526,7 +526,7 @@ class EPModel:
         lo, hi = ep.expert_range(rank, world, wl["E"])
         self.lo, self.hi = lo, hi
         self.wq = build_model(ops, wl, seed, device, range(lo, hi))
-        use_peer = os.environ.get("DQMOE_EP_IMPL", "peer") == "peer" and world <= 8 and wl["mode"] in (0, 512, 1024)
+        use_peer = os.environ.get("DQMOE_EP_IMPL", "peer") == "peer" and world <= 8 and wl["mode"] in (0, 512, 1024, 2048)
         if use_peer:
             self.layer = ep.PeerExpertParallelLayer(T, wl["H"], wl["I"], wl["E"], wl["k"], wl["mode"], self.wq, ops,
                                                     out_buffers=out_buffers)
@@ -725,7 +725,7 @@ def run_prefill(args, name, wl, ops, dev, rank, world, local_rank, dist=None, ep
                                               p_off, p_mt, n, I, H, E, mode, 1, gated_out.data_ptr(), p_act_s,
                                               scratch_amax.data_ptr(), None, stream))
         fc1_n, fc1_e, fc1_what = n, E, "the step's own expert-sorted rows"
-    elif mode in (0, 1024) and layer.impl == "peer":
+    elif mode in (0, 1024, 2048) and layer.impl == "peer":
         # Expert parallel: the same kernel alone on this rank's expert shard, with this rank's rows repeated k
         # times and split evenly over its experts (the received rows of a step have this size on average).
         e_loc = layer.wq[0].shape[0]
@@ -737,7 +737,13 @@ def run_prefill(args, name, wl, ops, dev, rank, world, local_rank, dist=None, ep
         out1 = torch.empty((n, I), dtype=torch.uint8 if mode else torch.bfloat16, device=dev)
         out1_s = torch.empty((n, (I + 127) // 128), dtype=torch.float32, device=dev)
 
+        if mode == 2048:
+            rows_s = ops.mx_tile_scales(rows_s, H, offsets=offs, mtile_pref=mt)
+            out1_t = torch.empty(rows_s.numel() // H * I + 512, dtype=torch.uint8, device=dev)
+
         def fc1():
+            if mode == 2048:
+                return ops.grouped_gemm_mx(rows_, rows_s, layer.wq[0], layer.wq[1], offs, mt, I, True, out1, out1_t)
             ops.grouped_gemm(rows_, rows_s, layer.wq[0], layer.wq[1], offs, mt, I, mode, True, out1, out_scale=out1_s)
         fc1_n, fc1_e, fc1_what = n, e_loc, "rank 0's expert shard, its rows split evenly"
     if fc1 is not None:

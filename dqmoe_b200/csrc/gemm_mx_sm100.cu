@@ -477,3 +477,10 @@ extern "C" int dqmoe_grouped_gemm_mx(const void* a, const uint8_t* a_sf, const v
     return dq::gemm_mx::grouped_gemm_mx(a, a_sf, w, w_sf, offsets, mtile_prefix, n, N, K, E, gated, out, out_sf,
                                         dest_to_src, nullptr, nullptr, static_cast<cudaStream_t>(stream));
 }
+
+extern "C" int dqmoe_grouped_gemm_mx_rows(const void* a, const uint8_t* a_sf, const void* w, const uint8_t* w_sf,
+                                          const int32_t* offsets, const int32_t* mtile_prefix, int n, int N, int K, int E,
+                                          const void* row_dst, dqmoe_stream_t stream) {
+    return dq::gemm_mx::grouped_gemm_mx(a, a_sf, w, w_sf, offsets, mtile_prefix, n, N, K, E, 0, nullptr, nullptr, nullptr,
+                                        row_dst, nullptr, static_cast<cudaStream_t>(stream));
+}

@@ -135,6 +135,7 @@ __global__ void __launch_bounds__(kThreads) tile_scales_kernel(const uint32_t* _
     for (int64_t i = int64_t(blockIdx.x) * kThreads + threadIdx.x; i < total; i += int64_t(gridDim.x) * kThreads) {
         const int64_t r = i / kblocks;
         const int kb = int(i - r * kblocks);
+        if (sorted && r >= s_tab[E]) continue;  // beyond the experts' rows (dropped rows, or an over-long row count)
         int64_t src = r;
         if (dest_to_src != nullptr) {
             const int slot = dest_to_src[r];

@@ -182,7 +182,9 @@ class PeerExpertParallelLayer:
     sort -> publish counts -> plan -> dispatch (rows written straight into the owners' receive
     buffers, already grouped by expert) -> wait -> grouped fc1 -> grouped fc2 whose epilogue stores
     every result row directly into its home rank's d (NVLink stores) -> signal -> wait.
-    bf16, block FP8 and channel FP8 modes (channel mode adds the per-row re-quantisation pass between
+    bf16, block FP8, MXFP8 and channel FP8 modes (MXFP8: a_scale is the row-major UE8M0 bytes [T, H/32], the weight
+    scales are tiled by row index over this rank's experts; the received scale rows are tiled locally before fc1;
+    channel mode adds the per-row re-quantisation pass between
     the GEMMs, bounded by the received row count read on the device). The returned tensor aliases
     the symmetric output buffer and is overwritten by a later call: by the next one with out_buffers = 1,
     by the one after it with out_buffers = 2 (calls then alternate between two output buffers, so a caller
@@ -196,8 +198,10 @@ class PeerExpertParallelLayer:
         os.environ.setdefault("TORCH_SYMM_MEM_DISABLE_MULTICAST", "1")  # plain peer loads/stores only
         import torch.distributed._symmetric_memory as symm_mem
         from . import _lib
-        if mode not in (0, 512, 1024):
-            raise RuntimeError("[ASSERT FAILED] ep.py  Condition: mode in (0, 512, 1024)  Info: peer exchange supports bf16, channel and block FP8")
+        if mode not in (0, 512, 1024, 2048):
+            raise RuntimeError("[ASSERT FAILED] ep.py  Condition: mode in (0, 512, 1024, 2048)  Info: peer exchange supports bf16, channel, block FP8 and MXFP8")
+        if mode == 2048 and (H % 128 or I % 128):
+            raise RuntimeError("[ASSERT FAILED] ep.py  Condition: H % 128 == 0 and I % 128 == 0 in the MXFP8 mode")
         self.ops, self.lib, self.check, self.ct = ops, _lib.load(), _lib.check, ctypes
         self.group = group if group is not None else dist.group.WORLD
         self.W, self.me = dist.get_world_size(self.group), dist.get_rank(self.group)
@@ -222,7 +226,8 @@ class PeerExpertParallelLayer:
         if capacity_rows < 0:
             raise RuntimeError("[ASSERT FAILED] ep.py  Condition: capacity_rows >= 0")
         self.cap = min(capacity_rows, worst)
-        self.scale_cols = (H + 127) // 128 if mode == 1024 else (1 if mode == 512 else 0)
+        # fp32 words of scale that travel with a row: block mode one per 128 columns; MXFP8 H/32 bytes = H/128 words
+        self.scale_cols = (H + 127) // 128 if mode in (1024, 2048) else (1 if mode == 512 else 0)
         dev = torch.device("cuda", torch.cuda.current_device())
         self.dev = dev
 
@@ -253,6 +258,11 @@ class PeerExpertParallelLayer:
         self.row_dst = torch.zeros(self.cap, dtype=torch.int64, device=dev)
         self.act = torch.empty(self.cap * I * self.esz, dtype=torch.uint8, device=dev)
         self.act_scale = torch.empty(self.cap * ((I + 127) // 128), dtype=torch.float32, device=dev)
+        if mode == 2048:  # scale bytes in the tiled layout of this rank's receive buffer (see dqmoe_mx_tile_scales)
+            self.rx_sf_tiled = torch.zeros(int(self.lib.dqmoe_mx_tiled_scale_bytes(self.cap, self.El, H)), dtype=torch.uint8,
+                                           device=dev)
+            self.act_sf_tiled = torch.zeros(int(self.lib.dqmoe_mx_tiled_scale_bytes(self.cap, self.El, I)), dtype=torch.uint8,
+                                            device=dev)
         if mode == 512:  # stage 1 writes bf16 and collects the row amax; a second pass quantises
             self.act_bf16 = torch.empty(self.cap * I, dtype=torch.bfloat16, device=dev)
             self.amax = torch.zeros(self.cap, dtype=torch.float32, device=dev)
@@ -321,7 +331,20 @@ class PeerExpertParallelLayer:
         b, bs, b1, b1s = self.weights_q
         sp = lambda t: None if t is None else vp(t.data_ptr())
         rx_scale = vp(self.local["rx_scale"]) if self.scale_cols else None
-        if self.mode == 512:
+        if self.mode == 2048:
+            # received scale rows (row-major, in receive order) -> tiled by this rank's tiles; then the two MXFP8 GEMMs
+            self.check(lib.dqmoe_mx_tile_scales(rx_scale, self.cap, H, None, 1, vp(self.rx_offsets.data_ptr()),
+                                                vp(self.rx_mtiles.data_ptr()), El, vp(self.rx_sf_tiled.data_ptr()), stream))
+            self.check(lib.dqmoe_grouped_gemm_mx(vp(self.local["rx_rows"]), vp(self.rx_sf_tiled.data_ptr()), vp(b.data_ptr()),
+                                                 sp(bs), vp(self.rx_offsets.data_ptr()), vp(self.rx_mtiles.data_ptr()),
+                                                 self.cap, I, H, El, 1, vp(self.act.data_ptr()),
+                                                 vp(self.act_sf_tiled.data_ptr()), None, stream))
+            mark("fc1")
+            self.check(lib.dqmoe_grouped_gemm_mx_rows(vp(self.act.data_ptr()), vp(self.act_sf_tiled.data_ptr()),
+                                                      vp(b1.data_ptr()), sp(b1s), vp(self.rx_offsets.data_ptr()),
+                                                      vp(self.rx_mtiles.data_ptr()), self.cap, H, I, El,
+                                                      vp(self.row_dst.data_ptr()), stream))
+        elif self.mode == 512:
             self.amax.zero_()
             self.check(lib.dqmoe_grouped_gemm(vp(self.local["rx_rows"]), rx_scale, vp(b.data_ptr()), sp(bs),
                                               vp(self.rx_offsets.data_ptr()), vp(self.rx_mtiles.data_ptr()), self.cap, I,
@@ -336,11 +359,12 @@ class PeerExpertParallelLayer:
                                               vp(self.rx_offsets.data_ptr()), vp(self.rx_mtiles.data_ptr()), self.cap, I,
                                               H, El, self.mode, 1, vp(self.act.data_ptr()), vp(self.act_scale.data_ptr()),
                                               None, None, stream))
-        mark("fc1")
-        self.check(lib.dqmoe_grouped_gemm_rows(vp(self.act.data_ptr()), vp(self.act_scale.data_ptr()) if self.mode else None,
-                                               vp(b1.data_ptr()), sp(b1s), vp(self.rx_offsets.data_ptr()),
-                                               vp(self.rx_mtiles.data_ptr()), self.cap, H, I, El, self.mode,
-                                               vp(self.row_dst.data_ptr()), stream))
+        if self.mode != 2048:
+            mark("fc1")
+            self.check(lib.dqmoe_grouped_gemm_rows(vp(self.act.data_ptr()), vp(self.act_scale.data_ptr()) if self.mode else None,
+                                                   vp(b1.data_ptr()), sp(b1s), vp(self.rx_offsets.data_ptr()),
+                                                   vp(self.rx_mtiles.data_ptr()), self.cap, H, I, El, self.mode,
+                                                   vp(self.row_dst.data_ptr()), stream))
         mark("fc2")
         self.check(lib.dqmoe_ep_signal(P["flags"], 2, me, W, ep_, stream))
         self.check(lib.dqmoe_ep_wait(vp(self.local["flags"]), 2, W, ep_, stream))

@@ -366,7 +366,8 @@ int dqmoe_quant_mxfp8(const void* x_bf16, int64_t rows, int cols, void* q, uint8
  * mtile_prefix [E+1] as dqmoe_route_sort / dqmoe_mtile_prefix give them), so that every 128-row tile of a
  * ragged expert owns whole blocks. dqmoe_mx_tile_scales converts row-major scales [*, cols/32] (cols a multiple
  * of 128); with dest_to_src != NULL output row r takes the scales of input row dest_to_src[r] / k (the
- * expert-sort gather; negative entries are skipped). dqmoe_mx_tiled_scale_bytes: size of the tiled buffer for
+ * expert-sort gather; negative entries are skipped). With offsets, rows at or beyond offsets[E] are skipped, so
+ * `rows` may be an upper bound of a row count that exists only on the device. dqmoe_mx_tiled_scale_bytes: size of the tiled buffer for
  * `rows` rows (E_sorted = number of experts for expert-sorted rows, 0 for rows that form blocks by index).
  */
 size_t dqmoe_mx_tiled_scale_bytes(int64_t rows, int E_sorted, int cols);
@@ -418,6 +419,11 @@ int dqmoe_grouped_gemm_mx(const void* a, const uint8_t* a_sf, const void* w, con
                           const int32_t* offsets, const int32_t* mtile_prefix, int n, int N, int K, int E,
                           int gated, void* out, uint8_t* out_sf, const int32_t* dest_to_src,
                           dqmoe_stream_t stream);
+
+/* Stage 2 of the MXFP8 grouped GEMM with explicit row addresses, as dqmoe_grouped_gemm_rows. */
+int dqmoe_grouped_gemm_mx_rows(const void* a, const uint8_t* a_sf, const void* w, const uint8_t* w_sf,
+                               const int32_t* offsets, const int32_t* mtile_prefix, int n, int N, int K, int E,
+                               const void* row_dst, dqmoe_stream_t stream);
 
 /* cumulative 128-row tile counts per expert from offsets[E+1] (device to device) */
 int dqmoe_mtile_prefix(const int32_t* offsets, int E, int32_t* mtile_prefix, dqmoe_stream_t stream);

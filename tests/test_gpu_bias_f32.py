@@ -140,7 +140,7 @@ def test_scale_tensors_are_validated(ops):
     ws = torch.empty(ops.moe_workspace_bytes(T, H, I, E, k, 1024) + 256, dtype=torch.uint8, device=DEV)
     d = torch.zeros(T, k, H, dtype=torch.bfloat16, device=DEV)
     short = torch.ones(T, 1, device=DEV)  # a per-token scale passed in block mode
-    with pytest.raises(RuntimeError, match="a_scale is a contiguous fp32 CUDA tensor of"):
+    with pytest.raises(RuntimeError, match="a_scale is a contiguous torch.float32 CUDA tensor of 64 elements"):
         ops.moe_forward(q[0], short, q[2], q[3], q[4], q[5], d, idx.to(DEV), ws, 1024)
     with pytest.raises(RuntimeError, match="b1_scale"):
         ops.moe_forward(q[0], q[1], q[2], q[3], q[4], q[5].double(), d, idx.to(DEV), ws, 1024)

@@ -37,6 +37,9 @@ def _worker(rank, world, init_file, mode, impl, results):
         elif mode == 1024:
             full = (*ops.per_block_cast_to_fp8(b.to(dev)), *ops.per_block_cast_to_fp8(b1.to(dev)))
             aq, asc = ops.per_token_block_cast_to_fp8(a.to(dev))
+        elif mode == 2048:
+            full = (*ops.mx_cast_weights_to_fp8(b.to(dev)), *ops.mx_cast_weights_to_fp8(b1.to(dev)))
+            aq, asc = ops.mx_cast_to_fp8(a.to(dev))
         else:
             bq, bs = ops.per_channel_cast_to_fp8(b.to(dev))
             b1q, b1s = ops.per_channel_cast_to_fp8(b1.to(dev))
@@ -48,7 +51,12 @@ def _worker(rank, world, init_file, mode, impl, results):
         ref = torch.zeros(T, k, H, dtype=torch.bfloat16, device=dev)
         idx = m_indices.to(dev)
         ops.moe_forward(aq, asc, full[0], full[1], full[2], full[3], ref, idx, ws, mode)
-        shard = tuple(None if t is None else t[lo:hi].contiguous() for t in full)
+        if mode == 2048:  # tiled scale bytes: an expert's 128-row blocks are contiguous, so a range of experts is a byte range
+            per_b, per_b1 = full[1].numel() // E, full[3].numel() // E
+            shard = (full[0][lo:hi].contiguous(), full[1][lo * per_b:hi * per_b].contiguous(), full[2][lo:hi].contiguous(),
+                     full[3][lo * per_b1:hi * per_b1].contiguous())
+        else:
+            shard = tuple(None if t is None else t[lo:hi].contiguous() for t in full)
         if impl == "peer":  # exchange through peer-mapped memory, three calls in a row (flag epochs)
             layer = ep.PeerExpertParallelLayer(T, H, I, E, k, mode, shard, ops)
             layer.forward(aq, asc, idx, zero_dropped=True)
@@ -68,7 +76,8 @@ def _worker(rank, world, init_file, mode, impl, results):
 
 
 @pytest.mark.parametrize("world", [1, 2])
-@pytest.mark.parametrize("mode,impl", [(0, "nccl"), (512, "nccl"), (1024, "nccl"), (0, "peer"), (512, "peer"), (1024, "peer")])
+@pytest.mark.parametrize("mode,impl", [(0, "nccl"), (512, "nccl"), (1024, "nccl"), (0, "peer"), (512, "peer"), (1024, "peer"),
+                                       (2048, "peer")])
 def test_expert_parallel_matches_single_gpu(mode, impl, world):
     """world = 1 runs the whole exchange (count matrix, plan, dispatch, row-address epilogue, flags) on one
     GPU, so the kernels of csrc/ep.cu are exercised where only one device is available."""
