@@ -7,7 +7,7 @@ scatter) over one batch of synthetic, seeded inputs. Prints ONE JSON line: whole
 same through the drop-in `moe_test` call with host buffers (`e2e`), the roofline of the dominant kernel (the fc1
 grouped GEMM), a parity figure for the very buffers that were timed, a sustained figure over at least a second
 of back-to-back steps, and the CPU oracle timed on a bounded sample (`cpu_baseline`). The default workload (c2)
-also carries short records of the other configurations (`c3`, `c4`, `c5`, `moe_block`).
+also carries short records of the other configurations (`c3`, `c4`, `c5`, `c2_mx`, `moe_block`).
 
 With --gpus N > 1 (launched by torch.distributed.run) the layer runs expert-parallel: every rank keeps T tokens
 (weak scaling) and E/N experts, rows travel through peer memory; the line then also has the per-phase times of
@@ -1016,6 +1016,11 @@ def main():
             r4, full4 = run_prefill(args, "c4", WORKLOADS["c4"], ops, dev, rank, world, local_rank, headline=False)
             rec["c4"] = short(r4)
             del full4
+            torch.cuda.empty_cache()
+            # the headline shape in the added MXFP8 mode (scales applied inside the tensor-core instruction)
+            rmx, fullmx = run_prefill(args, "c2-mx", WORKLOADS["c2-mx"], ops, dev, rank, world, local_rank, headline=False)
+            rec["c2_mx"] = short(rmx)
+            del fullmx
             torch.cuda.empty_cache()
             r5 = decode_sweep(args, dev, ops, with_cpu=False)
             rec["c5"] = {k_: r5[k_] for k_ in ("metric", "value", "unit", "sweep", "roofline", "e2e", "config")}

@@ -32,20 +32,25 @@ struct Peers {
     void* p[kMaxRanks];
 };
 
-__device__ __forceinline__ int ld_acquire_sys(const int* p) {
+// Flags cross GPUs, so their loads and stores are system scope. System-scope fences and acquire / release accesses
+// are the expensive part (measured: an exchange whose flag traffic overlaps large host copies over PCIe gets 0.3-0.4 ms
+// slower per call, a device-to-device copy of the same size does nothing), so each hand-over uses exactly one fence:
+// writers fence once and then store the flags relaxed, readers poll relaxed and fence once after the last flag.
+__device__ __forceinline__ int ld_relaxed_sys(const int* p) {
     int v;
-    asm volatile("ld.acquire.sys.global.s32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+    asm volatile("ld.relaxed.sys.global.s32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
     return v;
 }
-__device__ __forceinline__ void st_release_sys(int* p, int v) {
-    asm volatile("st.release.sys.global.s32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
+__device__ __forceinline__ void st_relaxed_sys(int* p, int v) {
+    asm volatile("st.relaxed.sys.global.s32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
 }
 
-// bounded wait until flag == epoch; false (and status written) when it gives up
+// bounded wait until flag == epoch; false (and status written) when it gives up. The caller fences
+// (__threadfence_system) after all its flags have arrived, before it reads what the flags announce.
 __device__ bool wait_flag(const int* flag, int epoch, int* status, int code, long long limit) {
     const long long t0 = clock64();
     unsigned spins = 0;
-    while (ld_acquire_sys(flag) != epoch) {
+    while (ld_relaxed_sys(flag) != epoch) {
         if (((++spins) & 0x3f) == 0) {
             __nanosleep(200);
             if (clock64() - t0 > limit) {
@@ -67,9 +72,12 @@ __global__ void __launch_bounds__(256) publish_counts_kernel(const int* __restri
         int* dst = static_cast<int*>(cnt.p[p]) + size_t(me) * E;
         for (int e = threadIdx.x; e < E; e += blockDim.x) dst[e] = counts[e];
     }
-    __threadfence_system();
+    __threadfence();   // every thread's count stores, visible on this GPU ...
     __syncthreads();
-    if (threadIdx.x < W) st_release_sys(static_cast<int*>(flags.p[threadIdx.x]) + 0 * kMaxRanks + me, epoch);
+    if (threadIdx.x < W) {
+        __threadfence_system();  // ... and ordered before the flag at system scope by the flag's writer
+        st_relaxed_sys(static_cast<int*>(flags.p[threadIdx.x]) + 0 * kMaxRanks + me, epoch);
+    }
 }
 
 // One block. cnt: my copy of the count matrix [W][E]. Outputs (all local):
@@ -96,6 +104,7 @@ __global__ void __launch_bounds__(256) plan_kernel(const int* __restrict__ cnt, 
     __syncthreads();
     if (threadIdx.x < W) {
         if (!wait_flag(my_flags + 0 * kMaxRanks + threadIdx.x, epoch, status, 201, limit)) s_ok = 0;
+        __threadfence_system();  // acquire: the counts announced by the flags
     }
     __syncthreads();
     const int El = E / W;
@@ -200,27 +209,34 @@ __global__ void __launch_bounds__(256) dispatch_kernel(const uint8_t* __restrict
         // home of the result: (source rank, slot t*k+j) packed as rank * 2^27 + slot (slot < 2^27)
         if (lane == 0) static_cast<int*>(rx_home.p[owner])[dst_row] = (me << 27) | slot;
     }
-    // all blocks done -> tell every owner that my rows have landed
-    __threadfence_system();
+    // all blocks done -> tell every owner that my rows have landed. The blocks order their row stores before the
+    // counter at GPU scope; the last block, which has observed every other block's arrival, fences once at system
+    // scope before it stores the flags (causality composes across the two scopes).
+    __threadfence();
     __syncthreads();
     if (threadIdx.x == 0) {
         const int prev = atomicAdd(done_counter, 1);
         if (prev == int(gridDim.x) - 1) {
             *done_counter = 0;
             __threadfence_system();
-            for (int p = 0; p < W; ++p) st_release_sys(static_cast<int*>(flags.p[p]) + 1 * kMaxRanks + me, epoch);
+            for (int p = 0; p < W; ++p) st_relaxed_sys(static_cast<int*>(flags.p[p]) + 1 * kMaxRanks + me, epoch);
         }
     }
 }
 
 __global__ void wait_kernel(const int* __restrict__ my_flags, int phase, int W, int epoch, int* status,
                             long long limit) {
-    if (threadIdx.x < W) wait_flag(my_flags + phase * kMaxRanks + threadIdx.x, epoch, status, 210 + phase, limit);
+    if (threadIdx.x < W) {
+        wait_flag(my_flags + phase * kMaxRanks + threadIdx.x, epoch, status, 210 + phase, limit);
+        __threadfence_system();  // acquire: what the flags announce (rows, results) is visible to the kernels that follow
+    }
 }
 
 __global__ void signal_kernel(Peers flags, int phase, int me, int W, int epoch) {
-    __threadfence_system();
-    if (threadIdx.x < W) st_release_sys(static_cast<int*>(flags.p[threadIdx.x]) + phase * kMaxRanks + me, epoch);
+    if (threadIdx.x < W) {
+        __threadfence_system();  // release: the preceding kernels' stores (the fc2 epilogue's result rows)
+        st_relaxed_sys(static_cast<int*>(flags.p[threadIdx.x]) + phase * kMaxRanks + me, epoch);
+    }
 }
 
 // row_dst[r] = address of the home output row of received row r (0 beyond the received rows)
