@@ -280,7 +280,8 @@ def quantize_activations_gpu(ops, x, mode):
 
 def launches_per_step(n, mode):
     sort = 1 if n <= 2048 else 3
-    return sort + 1 + 1 + (1 if mode in (256, 512) else 0) + 1
+    # sort, gather, fc1, [re-quantisation pass | scale tiling of the MXFP8 mode], fc2
+    return sort + 1 + 1 + (1 if mode in (256, 512, 2048) else 0) + 1
 
 
 def config_of(name, wl, world, T=None):
@@ -633,9 +634,9 @@ def run_prefill(args, name, wl, ops, dev, rank, world, local_rank, dist=None, ep
     else:
         layer = EPModel(wl, T, dev, 0, ops, ep, dist, out_buffers=2 if headline else 1)
         sort_l = 1 if n <= 2048 else 3
-        # peer exchange per rank and step: sort + publish, plan, dispatch, wait, row_ptrs, fc1, [requant], fc2, signal, wait;
-        # collective exchange: sort, gather, segment ids, then the layer on the received rows, then scatter
-        per_step_launches = (sort_l + 9 + (1 if mode == 512 else 0)) * world if layer.impl == "peer" else \
+        # peer exchange per rank and step: sort + publish/plan, dispatch, wait, row_ptrs, fc1, [requant | scale tiling],
+        # fc2, signal/wait; collective exchange: sort, gather, segment ids, the layer on the received rows, scatter
+        per_step_launches = (sort_l + 7 + (1 if mode in (512, 2048) else 0)) * world if layer.impl == "peer" else \
             (sort_l + 2 + (3 + 3 + (1 if mode in (256, 512) else 0)) + 1) * world
 
         def step():

@@ -59,6 +59,8 @@ SIGNATURES = {
     "dqmoe_ep_publish_counts": (_c_int, [_ptr, _c_int, _c_int, _c_int, _ptr, _ptr, _c_int, _ptr]),
     "dqmoe_ep_plan": (_c_int, [_ptr, _ptr, _c_int, _c_int, _c_int, _c_int, _c_int, _ptr, _ptr, _ptr, _ptr]),
     "dqmoe_ep_set_wait_limit": (_c_int, [_c_i64]),
+    "dqmoe_ep_publish_plan": (_c_int, [_ptr, _c_int, _c_int, _c_int, _ptr, _ptr, _c_int, _c_int, _ptr, _ptr, _ptr, _ptr]),
+    "dqmoe_ep_signal_wait": (_c_int, [_ptr, _c_int, _c_int, _c_int, _c_int, _ptr]),
     "dqmoe_ep_dispatch": (_c_int, [_ptr, _ptr, _c_size, _c_int, _c_int, _c_int, _ptr, _ptr, _ptr, _c_int, _c_int,
                                    _c_int, _ptr, _ptr, _ptr, _ptr, _ptr, _c_int, _ptr]),
     "dqmoe_ep_wait": (_c_int, [_ptr, _c_int, _c_int, _c_int, _ptr]),

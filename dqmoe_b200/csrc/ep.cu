@@ -89,7 +89,7 @@ __global__ void __launch_bounds__(256) publish_counts_kernel(const int* __restri
 // Every rank sees the same count matrix and so reaches the same verdict on the capacity: on overflow
 // all ranks report status 202, dispatch sends nothing and the GEMMs see zero rows, so nothing is
 // written past a receive buffer.
-__global__ void __launch_bounds__(256) plan_kernel(const int* __restrict__ cnt, const int* __restrict__ my_flags,
+__device__ void plan_body(const int* __restrict__ cnt, const int* __restrict__ my_flags,
                                                    int E, int me, int W, int epoch, int cap,
                                                    int* __restrict__ send_base, int* __restrict__ rx_offsets,
                                                    int* __restrict__ rx_mtiles, int* status, long long limit) {
@@ -158,6 +158,44 @@ __global__ void __launch_bounds__(256) plan_kernel(const int* __restrict__ cnt, 
             rx_offsets[El] = over ? 0 : run;
             rx_mtiles[El] = over ? 0 : tiles;
         }
+    }
+}
+
+__global__ void __launch_bounds__(256) plan_kernel(const int* __restrict__ cnt, const int* __restrict__ my_flags,
+                                                   int E, int me, int W, int epoch, int cap,
+                                                   int* __restrict__ send_base, int* __restrict__ rx_offsets,
+                                                   int* __restrict__ rx_mtiles, int* status, long long limit) {
+    plan_body(cnt, my_flags, E, me, W, epoch, cap, send_base, rx_offsets, rx_mtiles, status, limit);
+}
+
+// publish_counts and plan in one launch (one block): store my counts and flag to every rank, then wait for
+// everybody's and compute the plan. Saves a launch on the path every call waits on.
+__global__ void __launch_bounds__(256) publish_plan_kernel(const int* __restrict__ counts, int E, int me, int W, Peers cnt_all,
+                                                           Peers flags_all, int epoch, int cap,
+                                                           int* __restrict__ send_base, int* __restrict__ rx_offsets,
+                                                           int* __restrict__ rx_mtiles, int* status, long long limit) {
+    for (int p = 0; p < W; ++p) {
+        int* dst = static_cast<int*>(cnt_all.p[p]) + size_t(me) * E;
+        for (int e = threadIdx.x; e < E; e += blockDim.x) dst[e] = counts[e];
+    }
+    __threadfence();
+    __syncthreads();
+    if (threadIdx.x < W) {
+        __threadfence_system();
+        st_relaxed_sys(static_cast<int*>(flags_all.p[threadIdx.x]) + 0 * kMaxRanks + me, epoch);
+    }
+    plan_body(static_cast<const int*>(cnt_all.p[me]), static_cast<const int*>(flags_all.p[me]), E, me, W, epoch, cap, send_base,
+              rx_offsets, rx_mtiles, status, limit);
+}
+
+// signal(phase) and wait(phase) in one launch: announce that the preceding kernels' stores are done, then wait for
+// the same announcement from every rank.
+__global__ void signal_wait_kernel(Peers flags, int phase, int me, int W, int epoch, int* status, long long limit) {
+    if (threadIdx.x < W) {
+        __threadfence_system();
+        st_relaxed_sys(static_cast<int*>(flags.p[threadIdx.x]) + phase * kMaxRanks + me, epoch);
+        wait_flag(static_cast<const int*>(flags.p[me]) + phase * kMaxRanks + threadIdx.x, epoch, status, 210 + phase, limit);
+        __threadfence_system();
     }
 }
 
@@ -297,6 +335,33 @@ int dqmoe_ep_plan(const int32_t* cnt, const int32_t* my_flags, int E, int me, in
     ep::plan_kernel<<<1, 256, 0, static_cast<cudaStream_t>(stream)>>>(cnt, my_flags, E, me, W, epoch, cap, send_base,
                                                                       rx_offsets, rx_mtiles, device_status_word(),
                                                                       ep::wait_limit());
+    DQ_LAUNCH_CHECK();
+    return DQMOE_OK;
+}
+
+int dqmoe_ep_publish_plan(const int32_t* counts, int E, int me, int W, const void* const* cnt_ptrs,
+                          const void* const* flag_ptrs, int epoch, int cap, int32_t* send_base, int32_t* rx_offsets,
+                          int32_t* rx_mtiles, dqmoe_stream_t stream) {
+    DQ_CHECK(counts != nullptr && send_base != nullptr && rx_offsets != nullptr && rx_mtiles != nullptr);
+    DQ_CHECK(E > 0 && E <= ep::kMaxExperts && W >= 1 && W <= ep::kMaxRanks && me >= 0 && me < W && E % W == 0 && cap >= 0);
+    ep::Peers cnt, flags;
+    int rc = ep::make_peers(&cnt, cnt_ptrs, W);
+    if (rc == DQMOE_OK) rc = ep::make_peers(&flags, flag_ptrs, W);
+    if (rc != DQMOE_OK) return rc;
+    ep::publish_plan_kernel<<<1, 256, 0, static_cast<cudaStream_t>(stream)>>>(counts, E, me, W, cnt, flags, epoch, cap, send_base,
+                                                                              rx_offsets, rx_mtiles, device_status_word(),
+                                                                              ep::wait_limit());
+    DQ_LAUNCH_CHECK();
+    return DQMOE_OK;
+}
+
+int dqmoe_ep_signal_wait(const void* const* flag_ptrs, int phase, int me, int W, int epoch, dqmoe_stream_t stream) {
+    DQ_CHECK(phase >= 0 && phase < 3 && me >= 0 && me < W);
+    ep::Peers flags;
+    const int rc = ep::make_peers(&flags, flag_ptrs, W);
+    if (rc != DQMOE_OK) return rc;
+    ep::signal_wait_kernel<<<1, 32, 0, static_cast<cudaStream_t>(stream)>>>(flags, phase, me, W, epoch, device_status_word(),
+                                                                            ep::wait_limit());
     DQ_LAUNCH_CHECK();
     return DQMOE_OK;
 }

@@ -179,7 +179,7 @@ class PeerExpertParallelLayer:
     (torch.distributed._symmetric_memory: the same allocation mapped into every rank of the node)
     holding the count matrix, flags, the receive buffers and the output d[T, k, H]. A call then is
     a fixed sequence of kernels on one stream with no host synchronisation and no collective:
-    sort -> publish counts -> plan -> dispatch (rows written straight into the owners' receive
+    sort -> publish counts + plan (one launch) -> dispatch (rows written straight into the owners' receive
     buffers, already grouped by expert) -> wait -> grouped fc1 -> grouped fc2 whose epilogue stores
     every result row directly into its home rank's d (NVLink stores) -> signal -> wait.
     bf16, block FP8, MXFP8 and channel FP8 modes (MXFP8: a_scale is the row-major UE8M0 bytes [T, H/32], the weight
@@ -311,11 +311,9 @@ class PeerExpertParallelLayer:
             d_out.zero_()
         counts, offsets, d2s, _ = ops.route_sort(m_indices, E)
         mark("sort")
-        self.check(lib.dqmoe_ep_publish_counts(vp(counts.data_ptr()), E, me, W, P["cnt"], P["flags"], ep_, stream))
-        mark("publish")
-        self.check(lib.dqmoe_ep_plan(vp(self.local["cnt"]), vp(self.local["flags"]), E, me, W, ep_, self.cap,
-                                     vp(self.send_base.data_ptr()), vp(self.rx_offsets.data_ptr()),
-                                     vp(self.rx_mtiles.data_ptr()), stream))
+        self.check(lib.dqmoe_ep_publish_plan(vp(counts.data_ptr()), E, me, W, P["cnt"], P["flags"], ep_, self.cap,
+                                             vp(self.send_base.data_ptr()), vp(self.rx_offsets.data_ptr()),
+                                             vp(self.rx_mtiles.data_ptr()), stream))
         mark("plan")
         sc_ptr = vp(a_scale.data_ptr()) if self.scale_cols else None
         self.check(lib.dqmoe_ep_dispatch(vp(a.data_ptr()), sc_ptr, H * self.esz, self.scale_cols, k, self.n,
@@ -366,8 +364,7 @@ class PeerExpertParallelLayer:
                                                    vp(self.rx_mtiles.data_ptr()), self.cap, H, I, El, self.mode,
                                                    vp(self.row_dst.data_ptr()), stream))
         mark("fc2")
-        self.check(lib.dqmoe_ep_signal(P["flags"], 2, me, W, ep_, stream))
-        self.check(lib.dqmoe_ep_wait(vp(self.local["flags"]), 2, W, ep_, stream))
+        self.check(lib.dqmoe_ep_signal_wait(P["flags"], 2, me, W, ep_, stream))
         mark("wait_results")
         if route_weights is None:
             return d_out

@@ -476,6 +476,12 @@ int dqmoe_ep_plan(const int32_t* cnt, const int32_t* my_flags, int E, int me, in
 /* Clock cycles a flag wait of the kernels above may spin before it gives up (process-wide, applies to
  * launches made afterwards); 0 restores the default of about 10 s. */
 int dqmoe_ep_set_wait_limit(int64_t cycles);
+/* publish_counts followed by plan, and signal followed by wait, each as one launch (a launch less on the path
+ * every call waits on); same arguments and status codes as the separate calls. */
+int dqmoe_ep_publish_plan(const int32_t* counts, int E, int me, int W, const void* const* cnt_ptrs,
+                          const void* const* flag_ptrs, int epoch, int cap, int32_t* send_base,
+                          int32_t* rx_offsets, int32_t* rx_mtiles, dqmoe_stream_t stream);
+int dqmoe_ep_signal_wait(const void* const* flag_ptrs, int phase, int me, int W, int epoch, dqmoe_stream_t stream);
 int dqmoe_ep_dispatch(const void* a, const float* a_scale, size_t row_bytes, int scale_cols, int k, int n,
                       const int32_t* offsets, const int32_t* dest_to_src, const int32_t* send_base,
                       int E, int me, int W, const void* const* rx_rows, const void* const* rx_scale,
