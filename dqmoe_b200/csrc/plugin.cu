@@ -70,8 +70,12 @@ static int validate(const dqmoe_plugin_fields& f) {
         DQ_CHECK_FMT(f.quant_mode == DQMOE_QUANT_NONE, "quant_mode=%d with unquantised operands", f.quant_mode);
     else
         DQ_CHECK_FMT(f.quant_mode == DQMOE_QUANT_FP8_TENSOR || f.quant_mode == DQMOE_QUANT_FP8_CHANNEL ||
-                         f.quant_mode == DQMOE_QUANT_FP8_BLOCK,
+                         f.quant_mode == DQMOE_QUANT_FP8_BLOCK || f.quant_mode == DQMOE_QUANT_FP8_MX,
                      "quant_mode=%d with FP8 operands", f.quant_mode);
+    if (f.quant_mode == DQMOE_QUANT_FP8_MX)
+        DQ_CHECK_FMT(f.expert_hidden_size % 128 == 0 && f.expert_inter_size % 128 == 0,
+                     "expert_hidden_size=%d and expert_inter_size=%d must be multiples of 128 in the MXFP8 mode",
+                     f.expert_hidden_size, f.expert_inter_size);
     return DQMOE_OK;
 }
 

@@ -199,7 +199,8 @@ int dqmoe_moe_block_shared(const void* x_bf16, const float* logits, const void* 
  * reference; its kernels are the ones dqmoe_moe_forward replaces.
  *
  * type / output_type use the nvinfer1::DataType codes below. Built: FP8 operands with
- * quant_mode 256 / 512 / 1024 and BF16 operands with quant_mode 0, with outputs BF16
+ * quant_mode 256 / 512 / 1024 (and the added 2048, whose scale inputs hold UE8M0 bytes: actscale row-major,
+ * scale_a / scale_b tiled, see DQMOE_QUANT_FP8_MX) and BF16 operands with quant_mode 0, with outputs BF16
  * (written directly), HALF or FLOAT (converted from the layer's bf16 result through
  * workspace); HALF operands with quant_mode 0 and HALF output (dqmoe_moe_forward_f16);
  * FLOAT operands with quant_mode 0 and FLOAT output (dqmoe_moe_forward_f32).

@@ -218,6 +218,32 @@ def test_moe_block_mx(ops):
     assert orc.cosine(out.cpu(), ref) >= COS_MIN and orc.max_rel_err(out.cpu(), ref) <= REL_MAX
 
 
+def test_mx_through_the_drop_in_module_and_the_plugin_front_end(ops):
+    """quant_mode_value 2048 through moe_test.m_grouped_moe_nt_contiguous_fp8_bf16 (scale halves of the tuples hold
+    UE8M0 bytes) and through the plugin-shaped entry points with HALF output."""
+    import moe_test
+    from dqmoe_b200 import plugin
+    E, T, H, I, k = 8, 96, 512, 384, 2
+    a, b, b1, _, idx = make_inputs(21, T, H, I, E, k, 1.0, 0.05)
+    q = orc.quantize_inputs(a, b, b1, MX)
+    ref = orc.moe_layer_fp8(*q, idx, E, MX)
+    aq, as_, bq, bs, b1q, b1s = _device_inputs(ops, q, H, I)
+    ws = torch.empty(ops.moe_workspace_bytes(T, H, I, E, k, MX) + 256, dtype=torch.uint8, device=DEV)
+    d = torch.zeros(T, k, H, dtype=torch.bfloat16, device=DEV)
+    moe_test.m_grouped_moe_nt_contiguous_fp8_bf16((aq, as_), (bq, bs), (b1q, b1s), d, idx.to(DEV), ws, MX)
+    torch.cuda.synchronize()
+    assert ops.device_status() == 0
+    assert orc.cosine(d.cpu(), ref) >= COS_MIN and orc.max_rel_err(d.cpu(), ref) <= REL_MAX
+    with pytest.raises(RuntimeError, match="ASSERT FAILED"):  # fp32 scale tensors in the byte-scaled mode
+        moe_test.m_grouped_moe_nt_contiguous_fp8_bf16((aq, as_.float()), (bq, bs), (b1q, b1s), d, idx.to(DEV), ws, MX)
+    p = plugin.MoePlugin(E, k, H, I, max_num_tokens=128, type=plugin.DT_FP8, output_type=plugin.DT_HALF, quant_mode=MX)
+    out = p.enqueue([aq, bq, b1q, idx.to(DEV), None, None, as_, bs, b1s])
+    torch.cuda.synchronize()
+    assert out.dtype == torch.float16 and torch.equal(out.float(), d.float())
+    with pytest.raises(RuntimeError, match="multiples of 128 in the MXFP8 mode"):
+        plugin.MoePlugin(E, k, 160, I, 128, type=plugin.DT_FP8, quant_mode=MX)
+
+
 def test_mx_mode_rejects_shapes_it_cannot_tile(ops):
     E, T, H, I, k = 2, 8, 160, 128, 1
     a, b, b1, _, idx = make_inputs(15, T, H, I, E, k)
