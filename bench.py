@@ -424,6 +424,19 @@ def decode_sweep(args, dev, ops, with_cpu=True):
                 if i >= warm:
                     times.append(e0.elapsed_time(e1))
             p50 = statistics.median(times)
+            # the same with L2 flushed by READING the buffer: the flush by writing leaves 126 MB of dirty lines whose
+            # write-back shares HBM with the timed call's reads
+            ctimes = []
+            for i in range(steps + 3):
+                flush.sum()
+                e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                e0.record()
+                ops.moe_forward(*call, d, idx, ws, mode)
+                e1.record()
+                torch.cuda.synchronize()
+                if i >= 3:
+                    ctimes.append(e0.elapsed_time(e1))
+            p50c = statistics.median(ctimes)
             # the same call replayed from a CUDA graph (what a decode loop does): launch gaps removed
             side = torch.cuda.Stream()
             with torch.cuda.stream(side):
@@ -448,6 +461,8 @@ def decode_sweep(args, dev, ops, with_cpu=True):
             nbytes = active * 3 * H * I * (1 if mode else 2) + T * H * (1 if mode else 2) + T * k * H * 2
             rows.append({"quant": MODE_NAME[mode], "T": T, "active_experts": active, "p50_us": p50 * 1e3,
                          "p50_us_cuda_graph": p50g * 1e3, "gbs_cuda_graph": nbytes / (p50g * 1e-3) / 1e9,
+                         "p50_us_l2_flushed_by_read": p50c * 1e3,
+                         "frac_of_measured_hbm_l2_flushed_by_read": nbytes / (p50c * 1e-3) / 1e9 / pk["hbm_gbs"],
                          "bytes": nbytes, "gbs": nbytes / (p50 * 1e-3) / 1e9,
                          "frac_of_measured_hbm": nbytes / (p50 * 1e-3) / 1e9 / pk["hbm_gbs"],
                          "frac_of_8000_gbs": nbytes / (p50 * 1e-3) / 1e9 / 8000.0})

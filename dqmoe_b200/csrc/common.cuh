@@ -54,6 +54,10 @@ volatile int* host_status_word();
 
 int sm_count();
 
+namespace decode {
+constexpr int kAmaxParts = 4096;  // floats the layer workspace holds for the per-block amax values of the decode path's fc1
+}
+
 static inline size_t align_up(size_t x, size_t a) { return (x + a - 1) / a * a; }
 static inline int ceil_div(int a, int b) { return (a + b - 1) / b; }
 static inline bool is_aligned(const void* p, size_t a) { return (reinterpret_cast<uintptr_t>(p) % a) == 0; }

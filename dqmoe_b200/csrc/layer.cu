@@ -34,6 +34,7 @@ namespace decode {
 int forward(const void* a, const float* a_scale, const void* b, const float* b_scale, const void* b1,
             const float* b1_scale, void* d, const int* m_indices, void* act_bf16, float* amax, int T, int H, int I,
             int E, int k, bool fp8, cudaStream_t stream);
+bool eligible(int H, int I, bool fp8);  // row sizes the decode path serves (16-byte rows, activation row + ring fit shared memory)
 }  // namespace decode
 
 namespace layer {
@@ -84,7 +85,7 @@ static Layout make_layout(int T, int H, int I, int E, int k, int quant_mode, int
     const bool two_pass = quant_mode == DQMOE_QUANT_FP8_TENSOR || quant_mode == DQMOE_QUANT_FP8_CHANNEL;
     L.act_bf16 = add(two_pass ? n * I * 2 : 0);
     L.amax = add(quant_mode == DQMOE_QUANT_FP8_CHANNEL ? n * sizeof(float)
-                 : quant_mode == DQMOE_QUANT_FP8_TENSOR ? sizeof(float) : 0);
+                 : quant_mode == DQMOE_QUANT_FP8_TENSOR ? decode::kAmaxParts * sizeof(float) : 0);
     L.total = off;
     return L;
 }
@@ -160,8 +161,7 @@ static int moe_forward_impl(const void* a, const float* a_scale, const void* b, 
     float* amax = reinterpret_cast<float*>(ws + L.amax);
 
     if (elem == gemm::kElemBf16 && bias1 == nullptr && bias2 == nullptr && n <= layer::kDecodeRows &&
-        (quant_mode == DQMOE_QUANT_NONE || quant_mode == DQMOE_QUANT_FP8_TENSOR) &&
-        size_t(H > I ? H : I) * sizeof(float) <= 200 * 1024)
+        (quant_mode == DQMOE_QUANT_NONE || quant_mode == DQMOE_QUANT_FP8_TENSOR) && decode::eligible(H, I, fp8))
         return decode::forward(a, a_scale, b, b_scale, b1, b1_scale, d, m_indices, fp8 ? act_bf16 : act, amax, T, H, I,
                                E, k, fp8, stream);
 
