@@ -973,6 +973,93 @@ def _block_ws(ops, T, H, I, E, k, mode):
     return max(int(_lib.load().dqmoe_moe_block_workspace_bytes(T, H, I, E, k, mode)), 256)
 
 
+def run_nvfp4(args, ops, dev, name="c2"):
+    """The added NVFP4 mode on a prefill shape, single GPU: layer time with inputs resident in HBM, the fc1 grouped
+    GEMM timed alone on the step's own expert-sorted rows, and parity of a sample of tokens against the CPU oracle
+    (same packed bytes in). Fractions are of 4 x the measured bf16 peak (no FP4 peak was measured; nominal dense
+    FP4 is 9 000 TFLOP/s)."""
+    from dqmoe_b200 import _lib
+    wl = dict(WORKLOADS[name])
+    T, H, I, E, k = wl["T"], wl["H"], wl["I"], wl["E"], wl["k"]
+    x, logits = synth_inputs(wl, 1, dev)
+    idx, _ = ops.route_topk(logits, k, wl["scoring"])
+    parts = []
+    for i in range(0, E, 16):
+        b, b1 = synth_weights(wl, 0, dev, range(i, min(E, i + 16)))
+        parts.append((*ops.nvfp4_cast_weights(b), *ops.nvfp4_cast_weights(b1), b.shape[0]))
+        del b, b1
+    bq, b1q = torch.cat([p_[0] for p_ in parts]), torch.cat([p_[3] for p_ in parts])
+    bg, b1g = torch.cat([p_[2] for p_ in parts]), torch.cat([p_[5] for p_ in parts])
+    bs, b1s = torch.cat([p_[1] for p_ in parts]), torch.cat([p_[4] for p_ in parts])  # whole 128-row blocks per expert
+    del parts
+    a_g = ops.nvfp4_global_scale(x)
+    aq, a_sf = ops.nvfp4_cast(x, a_g)
+    # the global scale of the intermediate is a calibration constant of the layer: here amax 64, above what
+    # silu(gate) * value reaches on these inputs
+    act_g = torch.tensor([64.0 / (448.0 * 6.0)], dtype=torch.float32, device=dev)
+    ws = torch.empty(ops.moe_workspace_bytes(T, H, I, E, k, 4096), dtype=torch.uint8, device=dev)
+    d = torch.empty(T, k, H, dtype=torch.bfloat16, device=dev)
+    call = (aq, a_sf, a_g, bq, bs, bg, b1q, b1s, b1g, act_g)
+    step = lambda: ops.moe_forward_nvfp4(*call, d, idx, ws)
+    barrier = torch.cuda.synchronize
+    sampler = ClockSampler(dev.index or 0)
+    for _ in range(max(args.warmup, 3)):
+        step()
+    sampler.start()
+    ms = time_steps(step, args.steps, barrier) / args.steps
+    clocks = sampler.stop()
+    if ops.device_status() != 0:
+        raise SystemExit("device status non-zero: a kernel's bounded wait gave up; no number reported")
+    flops = 6.0 * T * k * H * I
+    pk = peaks()
+    peak = 4.0 * pk["bf16_tflops"]
+    # fc1 alone on the step's own sorted rows (the workspace still holds them)
+    lib = _lib.load()
+    n = T * k
+    wp = lambda which: lib.dqmoe_moe_workspace_ptr(ws.data_ptr(), which, T, H, I, E, k, 4096)
+    stream = torch.cuda.current_stream().cuda_stream
+    def fc1():
+        _lib.check(lib.dqmoe_grouped_gemm_nvfp4(wp(2), wp(3), a_g.data_ptr(), bq.data_ptr(), bs.data_ptr(), bg.data_ptr(), wp(0),
+                                                wp(7), n, I, H, E, 1, wp(4), wp(5), act_g.data_ptr(), None, stream))
+    for _ in range(3):
+        fc1()
+    ms1 = time_steps(fc1, args.steps, barrier) / args.steps
+    step()  # leave the workspace as a layer call leaves it
+    fl1 = 4.0 * n * I * H
+    # parity on a sample of tokens: the oracle on the same packed bytes
+    par = None
+    if not args.no_cpu_baseline:
+        from oracle import moe_oracle as orc
+        sample = 64
+        c = lambda t: t.cpu()
+        untile = lambda tiled, rows, cols: tiled.cpu().numpy().reshape(-1, rows // 128, cols // 64, 32, 4, 4).transpose(
+            0, 1, 4, 3, 2, 5).reshape(-1, rows, cols // 16)
+        bs_rm = torch.from_numpy(untile(bs, 2 * I, H).copy())
+        b1s_rm = torch.from_numpy(untile(b1s, H, I).copy())
+        ref = orc.moe_layer_nvfp4(c(aq[:sample]), c(a_sf[:sample]), c(a_g), c(bq), bs_rm, c(bg), c(b1q), b1s_rm, c(b1g), c(act_g),
+                                  c(idx[:sample]), E)
+        ds = torch.empty(sample, k, H, dtype=torch.bfloat16, device=dev)
+        wss = torch.empty(ops.moe_workspace_bytes(sample, H, I, E, k, 4096), dtype=torch.uint8, device=dev)
+        ops.moe_forward_nvfp4(aq[:sample].contiguous(), a_sf[:sample].contiguous(), a_g, bq, bs, bg, b1q, b1s, b1g, act_g, ds,
+                              idx[:sample].contiguous(), wss)
+        torch.cuda.synchronize()
+        par = {"against": "cpu oracle (same packed bytes in)", "tokens": sample, "cosine": orc.cosine(ds.cpu(), ref),
+               "max_rel_err": orc.max_rel_err(ds.cpu(), ref)}
+        par["ok"] = par["cosine"] >= 0.999 and par["max_rel_err"] <= 2e-2
+        if not par["ok"]:
+            raise SystemExit(f"parity of the NVFP4 layer against the CPU oracle failed: {par}; no number reported")
+    return {"metric": "moe_layer_tflops", "value": flops / (ms * 1e-3) / 1e12, "unit": "TFLOP/s", "n_gpus": 1,
+            "steps": args.steps, "warmup": max(args.warmup, 3), "ms_per_step": ms, "tokens_per_s": T / (ms * 1e-3),
+            "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "e2m1 x e2m1 -> f32 (ue4m3 scales per 16)",
+            "data": "synthetic", "parity": par, "clocks": clocks, "gpu_launches": args.steps * (launches_per_step(n, 2048)),
+            "roofline": {"bound": "tensor", "kernel": "fc1 grouped GEMM (gated, NVFP4 re-quantisation)", "achieved": fl1 / (ms1 * 1e-3) / 1e12,
+                         "peak": peak, "unit": "TFLOP/s", "frac": fl1 / (ms1 * 1e-3) / 1e12 / peak,
+                         "peak_note": "4 x measured bf16 burst (no FP4 peak measured; nominal dense FP4 9 000)",
+                         "ms_per_launch": ms1, "traffic": None},
+            "config": {"workload": f"{name} shape in the added NVFP4 mode", "T_per_gpu": T, "H": H, "I": I, "E": E, "k": k,
+                       "quant": "nvfp4", "parallelism": "single", "l2": "operands larger than L2; no flush"}}
+
+
 def short(rec, keys=("value", "unit", "ms_per_step", "tokens_per_s", "scaling", "parity", "roofline", "config", "n_gpus")):
     return {k_: rec.get(k_) for k_ in keys}
 
@@ -982,7 +1069,7 @@ def main():
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=20)
     ap.add_argument("--warmup", type=int, default=5)
-    ap.add_argument("--workload", default="c2", choices=sorted(WORKLOADS) + ["c5"],
+    ap.add_argument("--workload", default="c2", choices=sorted(WORKLOADS) + ["c5", "c2-nvfp4", "c3-nvfp4"],
                     help="c2 (default, the headline), c3, c4, c5 (decode sweep), c1 (CPU-size), c2-mx / c3-mx (added MXFP8 mode)")
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
@@ -993,7 +1080,8 @@ def main():
     local_rank = int(os.environ.get("LOCAL_RANK", "0"))
 
     if args.impl == "reference":
-        name = "c1" if args.workload == "c5" else args.workload  # the CPU path is timed on the CPU-size layer for the decode sweep
+        # the CPU path is timed on the CPU-size layer for the decode sweep, and on the fp32-scaled shape for the NVFP4 records
+        name = "c1" if args.workload == "c5" else args.workload.replace("-nvfp4", "")
         args.workload = name
         run_reference(args, WORKLOADS[name], rank)
         return
@@ -1007,6 +1095,10 @@ def main():
     if args.workload == "c5":
         if rank == 0:
             print(json.dumps(decode_sweep(args, dev, ops, with_cpu=not args.no_cpu_baseline)))
+        return
+    if args.workload.endswith("-nvfp4"):  # single-GPU record of the added NVFP4 mode
+        if rank == 0:
+            print(json.dumps(run_nvfp4(args, ops, dev, args.workload.split("-")[0])))
         return
     dist = ep = None
     if world > 1:
@@ -1037,6 +1129,8 @@ def main():
             rmx, fullmx = run_prefill(args, "c2-mx", WORKLOADS["c2-mx"], ops, dev, rank, world, local_rank, headline=False)
             rec["c2_mx"] = short(rmx)
             del fullmx
+            torch.cuda.empty_cache()
+            rec["c2_nvfp4"] = short(run_nvfp4(args, ops, dev))
             torch.cuda.empty_cache()
             r5 = decode_sweep(args, dev, ops, with_cpu=False)
             rec["c5"] = {k_: r5[k_] for k_ in ("metric", "value", "unit", "sweep", "roofline", "e2e", "config")}

@@ -54,6 +54,9 @@ SIGNATURES = {
     "dqmoe_mx_tile_scales": (_c_int, [_ptr, _c_i64, _c_int, _ptr, _c_int, _ptr, _ptr, _c_int, _ptr, _ptr]),
     "dqmoe_grouped_gemm_mx": (_c_int, [_ptr] * 6 + [_c_int] * 5 + [_ptr] * 4),
     "dqmoe_grouped_gemm_mx_rows": (_c_int, [_ptr] * 6 + [_c_int] * 4 + [_ptr, _ptr]),
+    "dqmoe_quant_nvfp4": (_c_int, [_ptr, _c_i64, _c_int, _ptr, _c_i64, _ptr, _ptr, _ptr]),
+    "dqmoe_grouped_gemm_nvfp4": (_c_int, [_ptr] * 8 + [_c_int] * 5 + [_ptr] * 5),
+    "dqmoe_moe_forward_nvfp4": (_c_int, [_ptr] * 15 + [_c_size] + [_c_int] * 5 + [_ptr]),
     "dqmoe_grouped_gemm": (_c_int, [_ptr] * 6 + [_c_int] * 6 + [_ptr] * 5),
     "dqmoe_grouped_gemm_rows": (_c_int, [_ptr] * 6 + [_c_int] * 5 + [_ptr, _ptr]),
     "dqmoe_ep_publish_counts": (_c_int, [_ptr, _c_int, _c_int, _c_int, _ptr, _ptr, _c_int, _ptr]),

@@ -125,6 +125,36 @@ __device__ __forceinline__ uint32_t f2e4m3x4(float a, float b, float c, float d)
 __device__ __forceinline__ float scale_from_amax(float amax) { return __fdiv_rn(fmaxf(amax, 1e-4f), 448.0f); }
 __device__ __forceinline__ float inv_scale(float sf) { return __fdiv_rn(1.0f, sf); }
 
+// one e4m3 byte -> fp32 (exact)
+__device__ __forceinline__ float e4m3_to_float(uint32_t byte) {
+    const __half_raw h = __nv_cvt_fp8_to_halfraw(static_cast<__nv_fp8_storage_t>(byte & 0xffu), __NV_E4M3);
+    return __half2float(*reinterpret_cast<const __half*>(&h));
+}
+// eight floats -> eight e2m1 nibbles (round to nearest even, saturating at 6), element i in nibble i
+__device__ __forceinline__ uint32_t f2e2m1x8(const float (&x)[8]) {
+    uint32_t out;
+    asm("{\n\t"
+        ".reg .b8 b0, b1, b2, b3;\n\t"
+        "cvt.rn.satfinite.e2m1x2.f32 b0, %2, %1;\n\t"
+        "cvt.rn.satfinite.e2m1x2.f32 b1, %4, %3;\n\t"
+        "cvt.rn.satfinite.e2m1x2.f32 b2, %6, %5;\n\t"
+        "cvt.rn.satfinite.e2m1x2.f32 b3, %8, %7;\n\t"
+        "mov.b32 %0, {b0, b1, b2, b3};\n\t"
+        "}"
+        : "=r"(out)
+        : "f"(x[0]), "f"(x[1]), "f"(x[2]), "f"(x[3]), "f"(x[4]), "f"(x[5]), "f"(x[6]), "f"(x[7]));
+    return out;
+}
+// NVFP4 scale of a 16-value block: the e4m3 byte nearest to (amax / 6) / g (saturating at 448), g = the tensor's
+// global scale; *inv = 1 / (value of that byte * g), or 0 for an all-zero block. A value x of the block is stored
+// as e2m1(x * inv).
+__device__ __forceinline__ uint32_t nvfp4_scale_byte(float amax, float g, float* inv) {
+    const uint32_t byte = f2e4m3x2(__fdiv_rn(__fdiv_rn(amax, 6.0f), g), 0.0f) & 0xffu;
+    const float d = e4m3_to_float(byte) * g;
+    *inv = d > 0.0f ? __fdiv_rn(1.0f, d) : 0.0f;
+    return byte;
+}
+
 __device__ __forceinline__ float warp_max(float v) {
 #pragma unroll
     for (int o = 16; o > 0; o >>= 1) v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, o));

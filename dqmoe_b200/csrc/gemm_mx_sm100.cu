@@ -18,6 +18,14 @@
 // TMEM budget: two 256-column accumulators and the scale columns do not fit 512 columns side by side, so the
 // two accumulators overlap by 24 columns; the epilogue of a tile drains the chunk holding those columns first
 // and signals it, and only that signal (not the whole epilogue) gates the next tile's first MMA.
+// The same kernel serves the NVFP4 mode (kFp4): e2m1 operands, two per byte, with one UE4M3 scale per row and 16 K
+// elements plus an fp32 global scale per tensor (per expert for the weights), on
+// tcgen05.mma.kind::mxf4nvf4.block_scale.scale_vec::4X. A 128-byte K stage then holds 256 elements, an instruction
+// covers K = 64 and reads four scale bytes per row, so a stage carries four 512-byte scale blocks per 128 rows (one
+// per 64 K elements, same byte order) and 48 TMEM scale columns; the accumulators overlap by 96 columns, the
+// epilogue multiplies by the product of the global scales and, in stage 1, re-quantises to NVFP4 with the
+// caller's global scale of the intermediate. Its four stages leave no room for the per-warp store staging
+// buffers, so rows are stored with 16-byte stores straight from registers.
 // The reference reserves mode bits for block-scaled formats it does not implement (csrc/quantization.h:30-38)
 // and names DeepGEMM as its road map (README.md:11); this mode has no counterpart kernel there.
 #include "common.cuh"
@@ -41,7 +49,6 @@ constexpr int kABytes = kBM * kBK;       // 16 KiB
 constexpr int kBBytes = kN * kBK;        // 32 KiB
 constexpr int kStageBytes = kABytes + kBBytes;
 constexpr int kSfBlock = 512;            // scale bytes of 128 rows x 4 groups, in tcgen05.cp order
-constexpr int kSfStage = 3 * kSfBlock;   // activation rows, first weight box, second weight box
 constexpr int kThreads = 384;
 constexpr int kRegsControl = 56;
 constexpr int kRegsEpilogue = 224;
@@ -49,9 +56,19 @@ constexpr int kEpiWarps = 8;
 constexpr int kMaxExperts = 1024;
 constexpr int kMaxDevices = 64;
 constexpr int kTmemCols = 512;
-constexpr int kAccCol1 = 232;            // second accumulator: columns [232, 488); the first is [0, 256)
-constexpr int kSfCol = 488;              // scale columns: two alternating sets of 4 (A) + 8 (B)
-constexpr int kSfCols = 12;
+
+// What differs between the two formats
+template <bool kFp4>
+struct Fmt {
+    static constexpr int kSfAtoms = kFp4 ? 4 : 1;                 // 512-byte scale blocks per 128 rows and stage
+    static constexpr int kSfStage = 3 * kSfAtoms * kSfBlock;      // activation rows, first weight box, second weight box
+    static constexpr int kSfCols = 12 * kSfAtoms;                 // TMEM columns of a stage's scales: (4 (A) + 8 (B)) per block
+    static constexpr int kSfCol = kTmemCols - 2 * kSfCols;        // two alternating sets at the top: 488 / 416
+    static constexpr int kAccCol1 = kSfCol - kN;                  // second accumulator [232, 488) / [160, 416); the first is [0, 256)
+    static constexpr int kStageElems = kFp4 ? 2 * kBK : kBK;      // K elements per 128-byte stage
+    static constexpr bool kStaged = !kFp4;                        // rows leave through the per-warp staging buffers
+    static constexpr int kOverlapWarps = kFp4 ? kEpiWarps : 4;    // epilogue warps that own columns the accumulators share
+};
 constexpr long long kWaitLimit = 1000000000LL;  // clock cycles before a wait gives up (~0.5 s)
 
 struct Params {
@@ -60,7 +77,7 @@ struct Params {
     int w_rows;          // weight rows per expert (stage 1: 2I, stage 2: H)
     int tile_w_rows;     // weight rows advanced per column tile (stage 1: 128, stage 2: 256)
     int box2_off;        // row offset of the second weight box (stage 1: I, stage 2: 128)
-    int kb_count;        // K / 128
+    int kb_count;        // K stages: K / 128 (MXFP8), K / 256 (NVFP4)
     const int* offsets;
     const int* mtile_prefix;
     int w_blocks;        // E * w_rows / 128: 128-row blocks of the weight scales
@@ -69,11 +86,15 @@ struct Params {
     void* out;
     uint8_t* out_sf;     // stage 1: tiled scales of the output, [row tiles][N/128][512]
     const float* bias;   // [E, w_rows] fp32 or nullptr
+    const float* ga;     // NVFP4: global scale of the activations (1 float)
+    const float* gw;     // NVFP4: global scale of every expert's weights [E]
+    const float* gout;   // NVFP4 stage 1: global scale of the re-quantised intermediate (1 float)
     const int* dest_to_src;
     const unsigned long long* row_dst;
     int* status;
 };
 
+template <bool kFp4>
 struct Shared {
     uint64_t full[kStages];     // operands and scale blocks of a stage have landed
     uint64_t empty[kStages];
@@ -82,19 +103,22 @@ struct Shared {
     uint64_t overlap_free[2];   // the columns a buffer shares with the other one have been drained
     uint32_t tmem_base;
     int abort_flag;
-    alignas(128) uint8_t sf[kStages][kSfStage];
-    uint4 stage[kEpiWarps][32 * 4];
+    alignas(128) uint8_t sf[kStages][Fmt<kFp4>::kSfStage];
+    uint4 stage[Fmt<kFp4>::kStaged ? kEpiWarps : 1][Fmt<kFp4>::kStaged ? 32 * 4 : 1];  // per-warp store staging (MXFP8)
     int mprefix[kMaxExperts + 1];
     int offsets[kMaxExperts + 1];
 };
 
-constexpr size_t kSmemBytes = 1024 + size_t(kStages) * kStageBytes + sizeof(Shared);
+template <bool kFp4>
+constexpr size_t smem_bytes() { return 1024 + size_t(kStages) * kStageBytes + sizeof(Shared<kFp4>); }
+static_assert(smem_bytes<false>() <= 227 * 1024 && smem_bytes<true>() <= 227 * 1024, "shared memory of a block");
 
 struct Tile {
     int e, row0, row_end, nt;
     int mtile;  // index of the row tile among all row tiles of the expert sort
 };
-__device__ __forceinline__ Tile decode_tile(int t, int& e_cursor, const Shared& st, int n_tiles) {
+template <class SharedT>
+__device__ __forceinline__ Tile decode_tile(int t, int& e_cursor, const SharedT& st, int n_tiles) {
     while (t >= st.mprefix[e_cursor + 1] * n_tiles) ++e_cursor;
     const int local = t - st.mprefix[e_cursor] * n_tiles;
     const int mtiles = st.mprefix[e_cursor + 1] - st.mprefix[e_cursor];
@@ -117,13 +141,17 @@ __device__ __forceinline__ uint32_t mx_scale_byte(float amax, float* inv) {
     return e;
 }
 
-template <bool kGated>
+template <bool kGated, bool kFp4>
 __global__ void __launch_bounds__(kThreads, 1)
 moe_GemmGrouped_GemmUniversal_tcgen05_mx(const __grid_constant__ CUtensorMap tma_a,
                                          const __grid_constant__ CUtensorMap tma_b, const Params p) {
+    using F = Fmt<kFp4>;
+    constexpr int kSfAtoms = F::kSfAtoms, kSfStage = F::kSfStage, kSfCols = F::kSfCols, kSfCol = F::kSfCol,
+                  kAccCol1 = F::kAccCol1;
+    constexpr int kSfPart = kSfAtoms * kSfBlock;  // scale bytes of 128 rows and one stage
     extern __shared__ uint8_t smem_raw[];
     uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
-    Shared& st = *reinterpret_cast<Shared*>(smem + size_t(kStages) * kStageBytes);
+    Shared<kFp4>& st = *reinterpret_cast<Shared<kFp4>*>(smem + size_t(kStages) * kStageBytes);
 
     const int warp = threadIdx.x >> 5;
     const int lane = threadIdx.x & 31;
@@ -136,7 +164,7 @@ moe_GemmGrouped_GemmUniversal_tcgen05_mx(const __grid_constant__ CUtensorMap tma
         for (int b = 0; b < 2; ++b) {
             ptx::mbar_init(&st.tmem_full[b], 1);
             ptx::mbar_init(&st.tmem_empty[b], kEpiWarps);
-            ptx::mbar_init(&st.overlap_free[b], 4);  // the four warps (one per lane quarter) that own the shared columns
+            ptx::mbar_init(&st.overlap_free[b], F::kOverlapWarps);  // the warps that own the shared columns
         }
         st.abort_flag = 0;
         ptx::fence_barrier_init();
@@ -174,9 +202,9 @@ moe_GemmGrouped_GemmUniversal_tcgen05_mx(const __grid_constant__ CUtensorMap tma
                 const Tile tl = decode_tile(t, e_cursor, st, p.n_tiles);
                 const int wrow0 = tl.e * p.w_rows + tl.nt * p.tile_w_rows;
                 const int wrow1 = wrow0 + p.box2_off;
-                const uint8_t* sf_a = p.sfa + size_t(tl.mtile) * kb_count * kSfBlock;
-                const uint8_t* sf_b0 = p.sfb + size_t(min(wrow0 >> 7, p.w_blocks - 1)) * kb_count * kSfBlock;
-                const uint8_t* sf_b1 = p.sfb + size_t(min(wrow1 >> 7, p.w_blocks - 1)) * kb_count * kSfBlock;
+                const uint8_t* sf_a = p.sfa + size_t(tl.mtile) * kb_count * kSfPart;
+                const uint8_t* sf_b0 = p.sfb + size_t(min(wrow0 >> 7, p.w_blocks - 1)) * kb_count * kSfPart;
+                const uint8_t* sf_b1 = p.sfb + size_t(min(wrow1 >> 7, p.w_blocks - 1)) * kb_count * kSfPart;
                 for (int kb = 0; kb < kb_count; ++kb, ++it) {
                     const int s = it % kStages;
                     if (!ptx::mbar_wait(&st.empty[s], ((it / kStages) & 1u) ^ 1u, abort_flag, kWaitLimit)) {
@@ -189,9 +217,9 @@ moe_GemmGrouped_GemmUniversal_tcgen05_mx(const __grid_constant__ CUtensorMap tma
                     ptx::tma_load_2d(sa, &tma_a, kb * kBK, tl.row0, &st.full[s]);
                     ptx::tma_load_2d(sb, &tma_b, kb * kBK, wrow0, &st.full[s]);
                     ptx::tma_load_2d(sb + kBox * kBK, &tma_b, kb * kBK, wrow1, &st.full[s]);
-                    ptx::bulk_load(&st.sf[s][0], sf_a + size_t(kb) * kSfBlock, kSfBlock, &st.full[s]);
-                    ptx::bulk_load(&st.sf[s][kSfBlock], sf_b0 + size_t(kb) * kSfBlock, kSfBlock, &st.full[s]);
-                    ptx::bulk_load(&st.sf[s][2 * kSfBlock], sf_b1 + size_t(kb) * kSfBlock, kSfBlock, &st.full[s]);
+                    ptx::bulk_load(&st.sf[s][0], sf_a + size_t(kb) * kSfPart, kSfPart, &st.full[s]);
+                    ptx::bulk_load(&st.sf[s][kSfPart], sf_b0 + size_t(kb) * kSfPart, kSfPart, &st.full[s]);
+                    ptx::bulk_load(&st.sf[s][2 * kSfPart], sf_b1 + size_t(kb) * kSfPart, kSfPart, &st.full[s]);
                 }
             }
         }
@@ -199,7 +227,7 @@ moe_GemmGrouped_GemmUniversal_tcgen05_mx(const __grid_constant__ CUtensorMap tma
       } else if (warp == 1) {
         // ------------------------------------------------------------ MMA issuer
         if (lane == 0) {
-            constexpr uint32_t idesc = ptx::make_idesc_mx(kBM, kN);
+            constexpr uint32_t idesc = kFp4 ? ptx::make_idesc_nvf4(kBM, kN) : ptx::make_idesc_mx(kBM, kN);
             uint32_t it = 0;
             uint32_t acc_it = 0;
             bool ok = true;
@@ -224,15 +252,25 @@ moe_GemmGrouped_GemmUniversal_tcgen05_mx(const __grid_constant__ CUtensorMap tma
                     const uint32_t b_addr = a_addr + kABytes;
                     const uint32_t sf_addr = ptx::smem_u32(&st.sf[s][0]);
                     const uint32_t sf_col = tmem_base + kSfCol + (it & 1u) * kSfCols;
-                    // scale bytes of this stage -> TMEM (executed in order with the MMAs around them)
-                    ptx::tmem_cp_sf(sf_col, ptx::smem_desc_sf(sf_addr));
-                    ptx::tmem_cp_sf(sf_col + 4, ptx::smem_desc_sf(sf_addr + kSfBlock));
-                    ptx::tmem_cp_sf(sf_col + 8, ptx::smem_desc_sf(sf_addr + 2 * kSfBlock));
+                    // scale bytes of this stage -> TMEM (executed in order with the MMAs around them). MXFP8: one block
+                    // per 128 rows serves the stage's four instructions (byte k of a column each); NVFP4: block k
+                    // serves instruction k, the weights' two 128-row blocks side by side in 8 columns.
 #pragma unroll
-                    for (int k = 0; k < kBK / kUmmaK; ++k)
-                        ptx::umma_mx(d_tmem, ptx::smem_desc_sw128(a_addr + k * kUmmaK),
-                                     ptx::smem_desc_sw128(b_addr + k * kUmmaK), ptx::idesc_mx_with_sf_id(idesc, k), sf_col,
-                                     sf_col + 4, (kb | k) != 0 ? 1u : 0u);
+                    for (int k = 0; k < kSfAtoms; ++k) {
+                        const uint32_t col_b = sf_col + (kFp4 ? 16 + 8 * k : 4);
+                        ptx::tmem_cp_sf(sf_col + 4 * k, ptx::smem_desc_sf(sf_addr + k * kSfBlock));
+                        ptx::tmem_cp_sf(col_b, ptx::smem_desc_sf(sf_addr + kSfPart + k * kSfBlock));
+                        ptx::tmem_cp_sf(col_b + 4, ptx::smem_desc_sf(sf_addr + 2 * kSfPart + k * kSfBlock));
+                    }
+#pragma unroll
+                    for (int k = 0; k < kBK / kUmmaK; ++k) {
+                        const uint64_t da = ptx::smem_desc_sw128(a_addr + k * kUmmaK), db = ptx::smem_desc_sw128(b_addr + k * kUmmaK);
+                        if constexpr (kFp4)
+                            ptx::umma_nvf4(d_tmem, da, db, idesc, sf_col + 4 * k, sf_col + 16 + 8 * k, (kb | k) != 0 ? 1u : 0u);
+                        else
+                            ptx::umma_mx(d_tmem, da, db, ptx::idesc_mx_with_sf_id(idesc, k), sf_col, sf_col + 4,
+                                         (kb | k) != 0 ? 1u : 0u);
+                    }
                     ptx::umma_commit(&st.empty[s]);
                 }
                 if (!ok) break;
@@ -252,8 +290,9 @@ moe_GemmGrouped_GemmUniversal_tcgen05_mx(const __grid_constant__ CUtensorMap tma
         int e_cursor = 0;
         bool ok = true;
         const int N = p.N;
-        float* csw = reinterpret_cast<float*>(st.stage[warp - 4]);
-        const float4* cs4 = reinterpret_cast<const float4*>(st.stage[warp - 4]);
+        uint4* stage_buf = st.stage[F::kStaged ? warp - 4 : 0];  // MXFP8 only
+        float* csw = reinterpret_cast<float*>(stage_buf);
+        const float4* cs4 = reinterpret_cast<const float4*>(stage_buf);
 
         for (int t = tile_first; ok && t < total_tiles; t += tile_step, ++acc_it) {
             const Tile tl = decode_tile(t, e_cursor, st, p.n_tiles);
@@ -266,20 +305,100 @@ moe_GemmGrouped_GemmUniversal_tcgen05_mx(const __grid_constant__ CUtensorMap tma
             }
             ptx::tc_fence_after();
             const uint32_t t_buf = t_lane + (buf ? kAccCol1 : 0);
-            // The columns shared with the other buffer are the last 24 of buffer 0 and the first 24 of buffer 1:
-            // the chunk order starts there, and the warps that own those columns report them drained.
-            const bool owns_overlap = h == (buf == 0u ? 1 : 0);
+            // The columns shared with the other buffer are the last ones of buffer 0 and the first ones of buffer 1:
+            // the chunk order starts there, and a warp reports once the shared chunks it owns are drained.
+            //   MXFP8, 24 columns: one chunk of the warps with h = 1 (buffer 0) / h = 0 (buffer 1)
+            //   NVFP4, 96 columns: buffer 0: one chunk of h = 0, two of h = 1; buffer 1: two of h = 0, one of h = 1
+            const int at_shared_end = buf == 0u ? h : 1 - h;
+            const int overlap_chunks = kFp4 ? 1 + at_shared_end : at_shared_end;
             const bool has_bias = p.bias != nullptr;
             const float* bias_e = has_bias ? p.bias + size_t(tl.e) * p.w_rows : nullptr;
-            auto overlap_drained = [&]() {
-                if (owns_overlap) {
+            auto overlap_drained = [&](int chunks_done) {
+                if (chunks_done == overlap_chunks) {
                     ptx::tc_fence_before();
                     __syncwarp();
                     if (lane == 0) ptx::mbar_arrive(&st.overlap_free[buf]);
                 }
             };
 
-            if constexpr (kGated) {
+            if constexpr (kGated && kFp4) {
+                // act columns nt*128 + h*64 + [0, 64): four scale groups of 16, packed two values per byte
+                const float alpha = p.ga[0] * p.gw[tl.e], gout = p.gout[0];
+                uint32_t sf_bytes = 0;
+#pragma unroll
+                for (int jj = 0; jj < 2; ++jj) {
+                    const int j = buf == 0u ? 1 - jj : jj;
+                    uint32_t g[32], v[32];
+                    const int c0 = h * 64 + j * 32;
+                    ptx::tmem_ld32(t_buf + c0, g);
+                    ptx::tmem_ld32(t_buf + kBox + c0, v);
+                    const int col0 = tl.nt * kBox + c0;
+                    ptx::tmem_wait_ld(g);
+                    ptx::tmem_wait_ld(v);
+                    overlap_drained(jj + 1);
+                    float act[32];
+                    float amax[2] = {0.0f, 0.0f};
+#pragma unroll
+                    for (int i = 0; i < 32; ++i) {
+                        const float bg = has_bias ? __ldg(bias_e + col0 + i) : 0.0f;
+                        const float bv = has_bias ? __ldg(bias_e + N + col0 + i) : 0.0f;
+                        const float gate = bf_round_cvt(__uint_as_float(g[i]) * alpha + bg);
+                        const float val = bf_round_cvt(__uint_as_float(v[i]) * alpha + bv);
+                        act[i] = bf_round_cvt(bf_round_cvt(__fdividef(gate, 1.0f + __expf(-gate))) * val);
+                        amax[i >> 4] = fmaxf(amax[i >> 4], fabsf(act[i]));
+                    }
+                    uint32_t w4[4];
+#pragma unroll
+                    for (int b = 0; b < 2; ++b) {
+                        float inv;
+                        sf_bytes |= nvfp4_scale_byte(amax[b], gout, &inv) << (16 * j + 8 * b);
+#pragma unroll
+                        for (int hf = 0; hf < 2; ++hf) {
+                            float x8[8];
+#pragma unroll
+                            for (int i = 0; i < 8; ++i) x8[i] = act[16 * b + 8 * hf + i] * inv;
+                            w4[2 * b + hf] = f2e2m1x8(x8);
+                        }
+                    }
+                    if (row_ok)
+                        st16(static_cast<uint8_t*>(p.out) + (size_t(grow) * N + col0) / 2, Vec16{w4[0], w4[1], w4[2], w4[3]});
+                }
+                // scale bytes of this row's four groups into the tile's block of the next GEMM's 64-wide K block
+                *reinterpret_cast<uint32_t*>(p.out_sf + (size_t(tl.mtile) * (N / 64) + tl.nt * 2 + h) * kSfBlock +
+                                             (r_in_tile & 31) * 16 + (r_in_tile >> 5) * 4) = sf_bytes;
+            } else if constexpr (kFp4) {
+                const float alpha = p.ga[0] * p.gw[tl.e];
+                int orow_idx = grow;
+                if (row_ok && p.dest_to_src != nullptr) orow_idx = p.dest_to_src[grow];
+                uint8_t* orow = static_cast<uint8_t*>(p.out) + size_t(orow_idx) * N * 2;
+                if (p.row_dst != nullptr) {
+                    orow = row_ok ? reinterpret_cast<uint8_t*>(p.row_dst[grow]) : nullptr;
+                    orow_idx = orow != nullptr ? 0 : -1;
+                }
+#pragma unroll 1
+                for (int cc = 0; cc < 4; ++cc) {
+                    const int c = buf == 0u ? 3 - cc : cc;
+                    uint32_t r[32];
+                    const int tc = (c >> 1) * kBox + h * 64 + (c & 1) * 32;
+                    ptx::tmem_ld32(t_buf + tc, r);
+                    const int col0 = tl.nt * kN + tc;
+                    ptx::tmem_wait_ld(r);
+                    overlap_drained(cc + 1);
+                    if (row_ok && orow_idx >= 0) {
+#pragma unroll
+                        for (int i = 0; i < 32; i += 8) {
+                            if (col0 + i < N) {
+                                float y[8];
+#pragma unroll
+                                for (int u = 0; u < 8; ++u)
+                                    y[u] = __uint_as_float(r[i + u]) * alpha + (has_bias ? __ldg(bias_e + min(col0 + i + u, N - 1)) : 0.0f);
+                                st16(orow + size_t(col0 + i) * 2, Vec16{pack_bf16x2(y[0], y[1]), pack_bf16x2(y[2], y[3]),
+                                                                      pack_bf16x2(y[4], y[5]), pack_bf16x2(y[6], y[7])});
+                            }
+                        }
+                    }
+                }
+            } else if constexpr (kGated) {
                 // act columns nt*128 + h*64 + [0, 64): two scale groups of 32
                 uint32_t pk[2][8];   // e4m3 bytes of the two groups in the order they were drained
                 uint32_t sf_bytes = 0;
@@ -300,7 +419,7 @@ moe_GemmGrouped_GemmUniversal_tcgen05_mx(const __grid_constant__ CUtensorMap tma
                     }
                     ptx::tmem_wait_ld(g);
                     ptx::tmem_wait_ld(v);
-                    if (jj == 0) overlap_drained();
+                    overlap_drained(jj + 1);
                     float act[32];
                     float amax = 0.0f;
 #pragma unroll
@@ -336,7 +455,7 @@ moe_GemmGrouped_GemmUniversal_tcgen05_mx(const __grid_constant__ CUtensorMap tma
                     packed[8 + i] = buf == 0u ? pk[0][i] : pk[1][i];
                 }
                 const int colh = tl.nt * kBox + h * 64;
-                store_rows_staged(st.stage[warp - 4], packed,
+                store_rows_staged(stage_buf, packed,
                                   row_ok ? static_cast<uint8_t*>(p.out) + size_t(grow) * N + colh : nullptr,
                                   min(4, max(0, (N - colh + 15) / 16)), lane);
                 // scale bytes of this row's two groups into the tile's block of the next GEMM's K block nt (written for
@@ -364,7 +483,7 @@ moe_GemmGrouped_GemmUniversal_tcgen05_mx(const __grid_constant__ CUtensorMap tma
                         __syncwarp();
                     }
                     ptx::tmem_wait_ld(r);
-                    if (cc == 0) overlap_drained();
+                    overlap_drained(cc + 1);
                     uint32_t packed[16];
 #pragma unroll
                     for (int i = 0; i < 32; i += 4) {
@@ -376,7 +495,7 @@ moe_GemmGrouped_GemmUniversal_tcgen05_mx(const __grid_constant__ CUtensorMap tma
                         packed[i >> 1] = pack_bf16x2(__uint_as_float(r[i]) + bb[0], __uint_as_float(r[i + 1]) + bb[1]);
                         packed[(i >> 1) + 1] = pack_bf16x2(__uint_as_float(r[i + 2]) + bb[2], __uint_as_float(r[i + 3]) + bb[3]);
                     }
-                    store_rows_staged(st.stage[warp - 4], packed,
+                    store_rows_staged(stage_buf, packed,
                                       row_ok && orow_idx >= 0 ? orow + size_t(col0) * 2 : nullptr,
                                       min(4, max(0, (N - col0 + 7) / 8)), lane);
                 }
@@ -404,9 +523,9 @@ moe_GemmGrouped_GemmUniversal_tcgen05_mx(const __grid_constant__ CUtensorMap tma
     }
 }
 
-template <bool kGated>
+template <bool kGated, bool kFp4>
 static int launch(const CUtensorMap& ma, const CUtensorMap& mb, const Params& p, cudaStream_t stream) {
-    auto kern = moe_GemmGrouped_GemmUniversal_tcgen05_mx<kGated>;
+    auto kern = moe_GemmGrouped_GemmUniversal_tcgen05_mx<kGated, kFp4>;
     static std::mutex mu;
     static bool configured[kMaxDevices] = {};
     int dev = 0;
@@ -415,27 +534,33 @@ static int launch(const CUtensorMap& ma, const CUtensorMap& mb, const Params& p,
     {
         std::lock_guard<std::mutex> lk(mu);
         if (!configured[dev]) {
-            DQ_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, int(kSmemBytes)));
+            DQ_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, int(smem_bytes<kFp4>())));
             configured[dev] = true;
         }
     }
-    kern<<<sm_count(), kThreads, kSmemBytes, stream>>>(ma, mb, p);
+    kern<<<sm_count(), kThreads, smem_bytes<kFp4>(), stream>>>(ma, mb, p);
     DQ_LAUNCH_CHECK();
     return DQMOE_OK;
 }
 
+// fp4 = false: MXFP8 (a, w e4m3; scales UE8M0 per 32). fp4 = true: NVFP4 (a, w e2m1 pairs; scales UE4M3 per 16;
+// ga / gw / gout the global scales). K and N count elements.
 int grouped_gemm_mx(const void* a, const uint8_t* a_sf, const void* w, const uint8_t* w_sf, const int* offsets,
                     const int* mtile_prefix, int n, int N, int K, int E, int gated, void* out, uint8_t* out_sf,
-                    const int* dest_to_src, const void* row_dst, const float* bias, cudaStream_t stream) {
+                    const int* dest_to_src, const void* row_dst, const float* bias, bool fp4, const float* ga,
+                    const float* gw, const float* gout, cudaStream_t stream) {
     DQ_CHECK(n >= 0 && N > 0 && K > 0 && E > 0 && E <= kMaxExperts);
     if (n == 0) return DQMOE_OK;
-    DQ_CHECK_FMT(K % 128 == 0, "K=%d: the MXFP8 mode needs the reduction length to be a multiple of 128", K);
-    DQ_CHECK_FMT(N % 128 == 0, "N=%d: the MXFP8 mode needs a multiple of 128 output columns", N);
+    const char* mode = fp4 ? "NVFP4" : "MXFP8";
+    const int stage_elems = fp4 ? Fmt<true>::kStageElems : Fmt<false>::kStageElems;
+    DQ_CHECK_FMT(K % stage_elems == 0, "K=%d: the %s mode needs the reduction length to be a multiple of %d", K, mode, stage_elems);
+    DQ_CHECK_FMT(N % 128 == 0, "N=%d: the %s mode needs a multiple of 128 output columns", N, mode);
     DQ_CHECK(a != nullptr && w != nullptr && a_sf != nullptr && w_sf != nullptr && offsets != nullptr && mtile_prefix != nullptr);
     DQ_CHECK((out != nullptr || row_dst != nullptr) && (row_dst == nullptr || !gated));
     DQ_CHECK(is_aligned(a, 16) && is_aligned(w, 16) && is_aligned(out, 16) && is_aligned(row_dst, 8) && is_aligned(a_sf, 16) &&
              is_aligned(w_sf, 16));
     if (gated) DQ_CHECK(out_sf != nullptr && is_aligned(out_sf, 16));
+    if (fp4) DQ_CHECK(ga != nullptr && gw != nullptr && (!gated || gout != nullptr));
     Params p;
     p.n_rows = n;
     p.N = N;
@@ -445,8 +570,8 @@ int grouped_gemm_mx(const void* a, const uint8_t* a_sf, const void* w, const uin
     p.n_tiles = gated ? ceil_div(N, kBox) : ceil_div(N, kN);
     p.tile_w_rows = gated ? kBox : kN;
     p.box2_off = gated ? N : kBox;
-    p.kb_count = K / kBK;
-    DQ_CHECK_FMT(p.w_rows % 128 == 0, "N=%d: weight rows per expert must be a multiple of 128 in the MXFP8 mode", N);
+    p.kb_count = K / stage_elems;
+    DQ_CHECK_FMT(p.w_rows % 128 == 0, "N=%d: weight rows per expert must be a multiple of 128 in the %s mode", N, mode);
     p.w_blocks = int(int64_t(E) * p.w_rows / 128);
     p.offsets = offsets;
     p.mtile_prefix = mtile_prefix;
@@ -455,16 +580,21 @@ int grouped_gemm_mx(const void* a, const uint8_t* a_sf, const void* w, const uin
     p.out = out;
     p.out_sf = out_sf;
     p.bias = bias;
+    p.ga = ga;
+    p.gw = gw;
+    p.gout = gout;
     p.dest_to_src = dest_to_src;
     p.row_dst = static_cast<const unsigned long long*>(row_dst);
     p.status = device_status_word();
     if (p.status == nullptr) return DQMOE_ERR_CUDA;
+    const uint64_t row_bytes = fp4 ? uint64_t(K) / 2 : uint64_t(K);  // both formats as byte matrices
     CUtensorMap ma, mb;
-    int rc = gemm::make_map(&ma, a, 1, uint64_t(n), uint64_t(K), kBM);
+    int rc = gemm::make_map(&ma, a, 1, uint64_t(n), row_bytes, kBM);
     if (rc != DQMOE_OK) return rc;
-    rc = gemm::make_map(&mb, w, 1, uint64_t(E) * p.w_rows, uint64_t(K), kBox);
+    rc = gemm::make_map(&mb, w, 1, uint64_t(E) * p.w_rows, row_bytes, kBox);
     if (rc != DQMOE_OK) return rc;
-    return gated ? launch<true>(ma, mb, p, stream) : launch<false>(ma, mb, p, stream);
+    if (fp4) return gated ? launch<true, true>(ma, mb, p, stream) : launch<false, true>(ma, mb, p, stream);
+    return gated ? launch<true, false>(ma, mb, p, stream) : launch<false, false>(ma, mb, p, stream);
 }
 
 }  // namespace gemm_mx
@@ -475,12 +605,23 @@ extern "C" int dqmoe_grouped_gemm_mx(const void* a, const uint8_t* a_sf, const v
                                      int gated, void* out, uint8_t* out_sf, const int32_t* dest_to_src,
                                      dqmoe_stream_t stream) {
     return dq::gemm_mx::grouped_gemm_mx(a, a_sf, w, w_sf, offsets, mtile_prefix, n, N, K, E, gated, out, out_sf,
-                                        dest_to_src, nullptr, nullptr, static_cast<cudaStream_t>(stream));
+                                        dest_to_src, nullptr, nullptr, false, nullptr, nullptr, nullptr,
+                                        static_cast<cudaStream_t>(stream));
 }
 
 extern "C" int dqmoe_grouped_gemm_mx_rows(const void* a, const uint8_t* a_sf, const void* w, const uint8_t* w_sf,
                                           const int32_t* offsets, const int32_t* mtile_prefix, int n, int N, int K, int E,
                                           const void* row_dst, dqmoe_stream_t stream) {
     return dq::gemm_mx::grouped_gemm_mx(a, a_sf, w, w_sf, offsets, mtile_prefix, n, N, K, E, 0, nullptr, nullptr, nullptr,
-                                        row_dst, nullptr, static_cast<cudaStream_t>(stream));
+                                        row_dst, nullptr, false, nullptr, nullptr, nullptr, static_cast<cudaStream_t>(stream));
+}
+
+extern "C" int dqmoe_grouped_gemm_nvfp4(const void* a, const uint8_t* a_sf, const float* a_gscale, const void* w,
+                                        const uint8_t* w_sf, const float* w_gscale, const int32_t* offsets,
+                                        const int32_t* mtile_prefix, int n, int N, int K, int E, int gated, void* out,
+                                        uint8_t* out_sf, const float* out_gscale, const int32_t* dest_to_src,
+                                        dqmoe_stream_t stream) {
+    return dq::gemm_mx::grouped_gemm_mx(a, a_sf, w, w_sf, offsets, mtile_prefix, n, N, K, E, gated, out, out_sf,
+                                        dest_to_src, nullptr, nullptr, true, a_gscale, w_gscale, out_gscale,
+                                        static_cast<cudaStream_t>(stream));
 }

@@ -27,7 +27,8 @@ enum Elem : int { kElemBf16 = 0, kElemHalf = 1, kElemF32 = 2 };  // element type
 namespace gemm_mx {
 int grouped_gemm_mx(const void* a, const uint8_t* a_sf, const void* w, const uint8_t* w_sf, const int* offsets,
                     const int* mtile_prefix, int n, int N, int K, int E, int gated, void* out, uint8_t* out_sf,
-                    const int* dest_to_src, const void* row_dst, const float* bias, cudaStream_t stream);
+                    const int* dest_to_src, const void* row_dst, const float* bias, bool fp4, const float* ga,
+                    const float* gw, const float* gout, cudaStream_t stream);
 }  // namespace gemm_mx
 
 namespace decode {
@@ -54,6 +55,9 @@ static bool valid_mode(int q) {
            q == DQMOE_QUANT_FP8_BLOCK || q == DQMOE_QUANT_FP8_MX;
 }
 
+// modes the workspace can be laid out for: those of dqmoe_moe_forward plus NVFP4, which has its own entry point
+static bool valid_layout_mode(int q) { return valid_mode(q) || q == DQMOE_QUANT_NVFP4; }
+
 static Layout make_layout(int T, int H, int I, int E, int k, int quant_mode, int elem = gemm::kElemBf16) {
     Layout L{};
     const size_t n = size_t(T) * k;
@@ -70,14 +74,17 @@ static Layout make_layout(int T, int H, int I, int E, int k, int quant_mode, int
     L.sort_ws_bytes = route::sort_workspace_bytes(int(n), E);
     L.sort_ws = add(L.sort_ws_bytes);
     L.dest_to_src = add(n * sizeof(int));
-    L.perm_a = add(n * H * esz);
+    const bool fp4 = quant_mode == DQMOE_QUANT_NVFP4;  // two elements per byte; scales tiled like MXFP8's, per 64 K elements
+    L.perm_a = add(fp4 ? n * H / 2 : n * H * esz);
     L.perm_scale_cols = quant_mode == DQMOE_QUANT_FP8_BLOCK ? ceil_div(H, 128)
                         : quant_mode == DQMOE_QUANT_FP8_CHANNEL ? 1 : 0;
     // MX mode: UE8M0 scale bytes in the tiled layout, whole 512-byte blocks per 128-row tile of the expert sort
     const bool mx = quant_mode == DQMOE_QUANT_FP8_MX;
-    L.perm_a_scale = add(mx ? dqmoe_mx_tiled_scale_bytes(int64_t(n), E, align_up(H, 128)) : n * L.perm_scale_cols * sizeof(float));
-    L.act = add(n * I * esz);
-    const size_t act_scale_elems = mx ? dqmoe_mx_tiled_scale_bytes(int64_t(n), E, align_up(I, 128)) / sizeof(float)
+    L.perm_a_scale = add(fp4 ? dqmoe_mx_tiled_scale_bytes(int64_t(n), E, 2 * align_up(H, 64))
+                         : mx ? dqmoe_mx_tiled_scale_bytes(int64_t(n), E, align_up(H, 128)) : n * L.perm_scale_cols * sizeof(float));
+    L.act = add(fp4 ? n * I / 2 : n * I * esz);
+    const size_t act_scale_elems = fp4 ? dqmoe_mx_tiled_scale_bytes(int64_t(n), E, 2 * align_up(I, 64)) / sizeof(float)
+                                   : mx ? dqmoe_mx_tiled_scale_bytes(int64_t(n), E, align_up(I, 128)) / sizeof(float)
                                    : quant_mode == DQMOE_QUANT_FP8_BLOCK ? n * ceil_div(I, 128)
                                    : quant_mode == DQMOE_QUANT_FP8_CHANNEL ? n
                                    : quant_mode == DQMOE_QUANT_FP8_TENSOR ? 1 : 0;
@@ -98,12 +105,12 @@ using namespace dq;
 extern "C" {
 
 size_t dqmoe_moe_workspace_bytes(int T, int H, int I, int E, int k, int quant_mode) {
-    if (T < 0 || H <= 0 || I <= 0 || E <= 0 || k <= 0 || !layer::valid_mode(quant_mode)) return 0;
+    if (T < 0 || H <= 0 || I <= 0 || E <= 0 || k <= 0 || !layer::valid_layout_mode(quant_mode)) return 0;
     return layer::make_layout(T, H, I, E, k, quant_mode).total;
 }
 
 void* dqmoe_moe_workspace_ptr(void* workspace, int which, int T, int H, int I, int E, int k, int quant_mode) {
-    if (workspace == nullptr || T < 0 || H <= 0 || I <= 0 || E <= 0 || k <= 0 || !layer::valid_mode(quant_mode))
+    if (workspace == nullptr || T < 0 || H <= 0 || I <= 0 || E <= 0 || k <= 0 || !layer::valid_layout_mode(quant_mode))
         return nullptr;
     const layer::Layout L = layer::make_layout(T, H, I, E, k, quant_mode);
     char* ws = static_cast<char*>(workspace);
@@ -181,11 +188,12 @@ static int moe_forward_impl(const void* a, const float* a_scale, const void* b, 
         if (rc != DQMOE_OK) return rc;
         rc = gemm_mx::grouped_gemm_mx(perm_a, reinterpret_cast<const uint8_t*>(perm_a_scale), b,
                                       reinterpret_cast<const uint8_t*>(b_scale), offsets, mtile_prefix, n, I, H, E, 1, act,
-                                      reinterpret_cast<uint8_t*>(act_scale), nullptr, nullptr, bias1, stream);
+                                      reinterpret_cast<uint8_t*>(act_scale), nullptr, nullptr, bias1, false, nullptr, nullptr,
+                                      nullptr, stream);
         if (rc != DQMOE_OK) return rc;
         return gemm_mx::grouped_gemm_mx(act, reinterpret_cast<const uint8_t*>(act_scale), b1,
                                         reinterpret_cast<const uint8_t*>(b1_scale), offsets, mtile_prefix, n, H, I, E, 0, d,
-                                        nullptr, dest_to_src, nullptr, bias2, stream);
+                                        nullptr, dest_to_src, nullptr, bias2, false, nullptr, nullptr, nullptr, stream);
     }
     const float* sa1 = quant_mode == DQMOE_QUANT_FP8_TENSOR ? a_scale : perm_a_scale;
     const bool two_pass = quant_mode == DQMOE_QUANT_FP8_TENSOR || quant_mode == DQMOE_QUANT_FP8_CHANNEL;
@@ -221,6 +229,52 @@ int dqmoe_moe_forward_bias(const void* a, const float* a_scale, const void* b, c
                            int k, int quant_mode, dqmoe_stream_t stream) {
     return moe_forward_impl(a, a_scale, b, b_scale, b1, b1_scale, d, m_indices, workspace, workspace_bytes, T, H, I, E, k,
                             quant_mode, gemm::kElemBf16, bias1, bias2, static_cast<cudaStream_t>(stream));
+}
+
+// The layer in the NVFP4 mode: expert sort, gather of the packed rows, gather of their scale bytes into the tiled
+// layout of the sort, grouped fc1 (SwiGLU, re-quantisation to NVFP4 with act_gscale) and grouped fc2.
+int dqmoe_moe_forward_nvfp4(const void* a, const uint8_t* a_sf, const float* a_gscale, const void* b, const uint8_t* b_sf,
+                            const float* b_gscale, const void* b1, const uint8_t* b1_sf, const float* b1_gscale,
+                            const float* act_gscale, const float* bias1, const float* bias2, void* d,
+                            const int32_t* m_indices, void* workspace, size_t workspace_bytes, int T, int H, int I, int E,
+                            int k, dqmoe_stream_t stream_) {
+    cudaStream_t stream = static_cast<cudaStream_t>(stream_);
+    DQ_CHECK(T >= 0 && H > 0 && I > 0 && E > 0 && k > 0);
+    DQ_CHECK_FMT(H % 256 == 0 && I % 256 == 0, "hidden_size=%d and inter_size=%d must be multiples of 256 in the NVFP4 mode", H, I);
+    if (T == 0) return DQMOE_OK;
+    DQ_CHECK(a != nullptr && b != nullptr && b1 != nullptr && d != nullptr && m_indices != nullptr);
+    DQ_CHECK(a_sf != nullptr && b_sf != nullptr && b1_sf != nullptr && a_gscale != nullptr && b_gscale != nullptr &&
+             b1_gscale != nullptr && act_gscale != nullptr);
+    DQ_CHECK_FMT(workspace != nullptr && is_aligned(workspace, layer::kAlign), "workspace pointer %p is not aligned!",
+                 workspace);
+    DQ_CHECK(int64_t(T) * k < (int64_t(1) << 31));
+    const int n = T * k;
+    const layer::Layout L = layer::make_layout(T, H, I, E, k, DQMOE_QUANT_NVFP4);
+    if (workspace_bytes != 0 && workspace_bytes < L.total)
+        return fail(DQMOE_ERR_WORKSPACE, __FILE__, __LINE__, "workspace_bytes >= dqmoe_moe_workspace_bytes(...)",
+                    "workspace has %zu bytes, the layer needs %zu", workspace_bytes, L.total);
+    char* ws = static_cast<char*>(workspace);
+    int* offsets = reinterpret_cast<int*>(ws + L.offsets);
+    int* counts = reinterpret_cast<int*>(ws + L.counts);
+    int* mtile_prefix = reinterpret_cast<int*>(ws + L.mtile_prefix);
+    int* dest_to_src = reinterpret_cast<int*>(ws + L.dest_to_src);
+    void* perm_a = ws + L.perm_a;
+    uint8_t* perm_a_sf = reinterpret_cast<uint8_t*>(ws + L.perm_a_scale);
+    void* act = ws + L.act;
+    uint8_t* act_sf = reinterpret_cast<uint8_t*>(ws + L.act_scale);
+    int rc = route::route_sort(m_indices, n, E, counts, offsets, mtile_prefix, dest_to_src, nullptr, ws + L.sort_ws,
+                               L.sort_ws_bytes, stream);
+    if (rc != DQMOE_OK) return rc;
+    rc = dqmoe_permute_rows(a, size_t(H) / 2, k, dest_to_src, n, perm_a, nullptr, 0, nullptr, stream);
+    if (rc != DQMOE_OK) return rc;
+    // one scale byte per 16 elements: the tiling kernel sees them as the scales of a row twice as long
+    rc = dqmoe_mx_tile_scales(a_sf, n, 2 * H, dest_to_src, k, offsets, mtile_prefix, E, perm_a_sf, stream);
+    if (rc != DQMOE_OK) return rc;
+    rc = gemm_mx::grouped_gemm_mx(perm_a, perm_a_sf, b, b_sf, offsets, mtile_prefix, n, I, H, E, 1, act, act_sf, nullptr,
+                                  nullptr, bias1, true, a_gscale, b_gscale, act_gscale, stream);
+    if (rc != DQMOE_OK) return rc;
+    return gemm_mx::grouped_gemm_mx(act, act_sf, b1, b1_sf, offsets, mtile_prefix, n, H, I, E, 0, d, nullptr, dest_to_src,
+                                    nullptr, bias2, true, act_gscale, b1_gscale, nullptr, stream);
 }
 
 int dqmoe_moe_forward_f16(const void* a, const void* b, const void* b1, void* d, const int32_t* m_indices,
@@ -349,11 +403,12 @@ static int moe_block_impl(const void* x_bf16, const float* logits, const void* b
         if (rc != DQMOE_OK) return rc;
         rc = gemm_mx::grouped_gemm_mx(perm_a, reinterpret_cast<const uint8_t*>(perm_a_scale), b,
                                       reinterpret_cast<const uint8_t*>(b_scale), offsets, mtile_prefix, n, I, H, E, 1, act,
-                                      reinterpret_cast<uint8_t*>(act_scale), nullptr, nullptr, nullptr, stream);
+                                      reinterpret_cast<uint8_t*>(act_scale), nullptr, nullptr, nullptr, false, nullptr, nullptr,
+                                      nullptr, stream);
         if (rc != DQMOE_OK) return rc;
         rc = gemm_mx::grouped_gemm_mx(act, reinterpret_cast<const uint8_t*>(act_scale), b1,
                                       reinterpret_cast<const uint8_t*>(b1_scale), offsets, mtile_prefix, n, H, I, E, 0, d,
-                                      nullptr, dest_to_src, nullptr, nullptr, stream);
+                                      nullptr, dest_to_src, nullptr, nullptr, false, nullptr, nullptr, nullptr, stream);
         if (rc != DQMOE_OK) return rc;
         return dqmoe_finalize_weighted(d, weights, out_bf16, T, k, H, stream);
     }

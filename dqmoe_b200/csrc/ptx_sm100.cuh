@@ -249,6 +249,27 @@ __device__ __forceinline__ void umma_mx(uint32_t tmem_d, uint64_t desc_a, uint64
         : "memory");
 }
 
+// Instruction descriptor of tcgen05.mma.kind::mxf4nvf4.block_scale.scale_vec::4X: A and B e2m1 (two per byte,
+// K-major), UE4M3 scale factors, one per row and 16 K elements; an instruction covers K = 64 and reads four scale
+// bytes per row (a whole 32-bit TMEM scale column), so the sf_id fields stay 0.
+__host__ __device__ constexpr uint32_t make_idesc_nvf4(uint32_t m, uint32_t n) {
+    return (1u << 7) | (1u << 10)  // A and B format e2m1
+           | ((n >> 3) << 17)      // N / 8; bit 23 = 0: scale format UE4M3
+           | ((m >> 4) << 24);     // M / 16
+}
+// D[tmem] (+)= (A * sfa) (B * sfb)^T with e2m1 operands and one UE4M3 scale per row and 16 K elements, K = 64.
+__device__ __forceinline__ void umma_nvf4(uint32_t tmem_d, uint64_t desc_a, uint64_t desc_b, uint32_t idesc,
+                                          uint32_t tmem_sfa, uint32_t tmem_sfb, uint32_t accumulate) {
+    asm volatile(
+        "{\n\t"
+        ".reg .pred p;\n\t"
+        "setp.ne.b32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::1.kind::mxf4nvf4.block_scale.scale_vec::4X [%0], %1, %2, %3, [%5], [%6], p;\n\t"
+        "}" ::"r"(tmem_d),
+        "l"(desc_a), "l"(desc_b), "r"(idesc), "r"(accumulate), "r"(tmem_sfa), "r"(tmem_sfb)
+        : "memory");
+}
+
 // Shared-memory descriptor of one 512-byte scale-factor block for tcgen05.cp: 32 rows of 16 bytes, no swizzle,
 // 8-row groups 128 bytes apart. Row r0 holds the scale bytes of tile rows r0, r0+32, r0+64, r0+96 (4 each, one
 // per 32-wide K step).

@@ -153,6 +153,42 @@ static int grid_for(int64_t work_items, int per_block) {
     return int(want < 1 ? 1 : (want < cap ? want : cap));
 }
 
+
+// NVFP4: e2m1 values (two per byte, element 2i in the low nibble), one UE4M3 scale byte per 16 consecutive elements
+// of a row, and one fp32 global scale g per group of rows_per_g rows (a whole tensor for activations, one expert's
+// rows for weights): x ~ e2m1 * e4m3 * g. One thread per 16-element group:
+//   scale byte  = e4m3_rne((amax / 6) / g), saturating at 448
+//   nibbles     = e2m1_rne(x * (1 / (e4m3 * g))), saturating at 6; an all-zero group stores zeros
+// All divisions IEEE fp32. Scale bytes row-major [rows, cols / 16].
+__global__ void __launch_bounds__(kThreads) quant_nvfp4_kernel(const uint8_t* __restrict__ x, int64_t rows, int cols,
+                                                               const float* __restrict__ g, int64_t rows_per_g,
+                                                               uint8_t* __restrict__ q, uint8_t* __restrict__ sf) {
+    const int groups = cols / 16;
+    const int64_t total = rows * groups;
+    for (int64_t i = blockIdx.x * int64_t(kThreads) + threadIdx.x; i < total; i += int64_t(gridDim.x) * kThreads) {
+        const int64_t r = i / groups;
+        const Vec16 v0 = ld_nc16(x + i * 32), v1 = ld_nc16(x + i * 32 + 16);
+        const uint32_t w[8] = {v0.x, v0.y, v0.z, v0.w, v1.x, v1.y, v1.z, v1.w};
+        float f[16];
+        float amax = 0.0f;
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {
+            f[2 * j] = bf16_lo(w[j]);
+            f[2 * j + 1] = bf16_hi(w[j]);
+            amax = fmaxf(amax, fmaxf(fabsf(f[2 * j]), fabsf(f[2 * j + 1])));
+        }
+        float inv;
+        sf[i] = uint8_t(nvfp4_scale_byte(amax, g[r / rows_per_g], &inv));
+        float lo[8], hi[8];
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {
+            lo[j] = f[j] * inv;
+            hi[j] = f[8 + j] * inv;
+        }
+        *reinterpret_cast<uint2*>(q + i * 8) = make_uint2(f2e2m1x8(lo), f2e2m1x8(hi));
+    }
+}
+
 }  // namespace quant_mx
 }  // namespace dq
 
@@ -217,6 +253,20 @@ int dqmoe_mx_tile_scales(const uint8_t* scale_rows, int64_t rows, int cols, cons
                                    offsets != nullptr ? size_t(2 * (E + 1)) * sizeof(int) : 0,
                                    static_cast<cudaStream_t>(stream)>>>(
         reinterpret_cast<const uint32_t*>(scale_rows), rows, kblocks, dest_to_src, k, offsets, mtile_prefix, E, scale_tiled);
+    DQ_LAUNCH_CHECK();
+    return DQMOE_OK;
+}
+
+int dqmoe_quant_nvfp4(const void* x_bf16, int64_t rows, int cols, const float* gscale, int64_t rows_per_gscale, void* q,
+                      uint8_t* scale, dqmoe_stream_t stream) {
+    DQ_CHECK(rows >= 0 && cols > 0 && rows_per_gscale > 0);
+    if (rows == 0) return DQMOE_OK;
+    DQ_CHECK(x_bf16 != nullptr && gscale != nullptr && q != nullptr && scale != nullptr);
+    DQ_CHECK_FMT(cols % 16 == 0, "cols=%d: NVFP4 rows are made of 16-element groups", cols);
+    DQ_CHECK(is_aligned(x_bf16, 16) && is_aligned(q, 8));
+    quant_mx::quant_nvfp4_kernel<<<quant_mx::grid_for(rows * (cols / 16), quant_mx::kThreads), quant_mx::kThreads, 0,
+                                   static_cast<cudaStream_t>(stream)>>>(static_cast<const uint8_t*>(x_bf16), rows, cols, gscale,
+                                                                        rows_per_gscale, static_cast<uint8_t*>(q), scale);
     DQ_LAUNCH_CHECK();
     return DQMOE_OK;
 }

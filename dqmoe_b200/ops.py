@@ -406,6 +406,73 @@ def moe_permute_quant_mx(x: torch.Tensor, dest_to_src: torch.Tensor, k: int, off
     return q, s
 
 
+def nvfp4_global_scale(x: torch.Tensor) -> torch.Tensor:
+    """amax / (448 * 6) of x as a [1] fp32 tensor: the usual NVFP4 global scale (set-up arithmetic in torch)."""
+    # tensor / tensor: an IEEE division (a division by a Python scalar may run as a multiplication by 1 / 2688)
+    return (x.float().abs().amax().clamp(min=1e-4) / torch.full((), 2688.0, device=x.device)).reshape(1)
+
+
+def nvfp4_cast(x: torch.Tensor, gscale: torch.Tensor):
+    """NVFP4: (packed e2m1 bytes [..., n/2], UE4M3 scale bytes [..., n/16]) for bf16 x [..., n]; gscale holds one
+    global scale for all of x, or one per index of x's first dimension (weights [E, rows, n]); see
+    dqmoe_quant_nvfp4."""
+    _cuda(x, "x")
+    _cuda(gscale, "gscale")
+    assert x.dtype == torch.bfloat16 and x.shape[-1] % 16 == 0 and gscale.dtype == torch.float32
+    n = x.shape[-1]
+    rows = x.numel() // n
+    groups = gscale.numel()
+    assert groups == 1 or groups == x.shape[0]
+    q = torch.empty((*x.shape[:-1], n // 2), dtype=torch.uint8, device=x.device)
+    s = torch.empty((*x.shape[:-1], n // 16), dtype=torch.uint8, device=x.device)
+    with torch.cuda.device(x.device):
+        _lib.check(_lib.load().dqmoe_quant_nvfp4(_p(x), rows, n, _p(gscale), max(rows // groups, 1), _p(q), _p(s),
+                                                 _stream(x.device)))
+    return q, s
+
+
+def nvfp4_cast_weights(w: torch.Tensor):
+    """NVFP4 weights [E, rows, cols] (rows a multiple of 128, cols of 64): (packed bytes, scale bytes in the tiled
+    layout of the grouped GEMM, per-expert global scales [E])."""
+    g = (w.float().abs().amax(dim=(1, 2)).clamp(min=1e-4) / torch.full((), 2688.0, device=w.device)).contiguous()
+    q, s = nvfp4_cast(w, g)
+    return q, mx_tile_scales(s, 2 * w.shape[-1]), g
+
+
+def grouped_gemm_nvfp4(a, a_sf, a_g, w, w_sf, w_g, offsets, mtile_pref, N: int, gated: bool, out, out_sf=None, out_g=None,
+                       dest_to_src=None) -> None:
+    """The grouped GEMM in the NVFP4 mode; see dqmoe_grouped_gemm_nvfp4. a [n, K/2] packed."""
+    n, K = a.shape[0], a.shape[1] * 2
+    E = w.shape[0]
+    with torch.cuda.device(a.device):
+        _lib.check(_lib.load().dqmoe_grouped_gemm_nvfp4(_p(a), _p(a_sf), _p(a_g), _p(w), _p(w_sf), _p(w_g), _p(offsets),
+                                                        _p(mtile_pref), n, N, K, E, int(bool(gated)), _p(out), _p(out_sf),
+                                                        _p(out_g), _p(dest_to_src), _stream(a.device)))
+
+
+def moe_forward_nvfp4(a, a_sf, a_g, b, b_sf, b_g, b1, b1_sf, b1_g, act_g, d, m_indices, workspace, bias1=None,
+                      bias2=None) -> None:
+    """The layer in the NVFP4 mode; see dqmoe_moe_forward_nvfp4. a [T, H/2] packed with row-major scale bytes
+    [T, H/16]; weights packed with tiled scale bytes and per-expert global scales (nvfp4_cast_weights)."""
+    for name, t in (("a", a), ("b", b), ("b1", b1), ("d", d), ("m_indices", m_indices), ("workspace", workspace)):
+        _cuda(t, name)
+    T, H = a.shape[0], a.shape[1] * 2
+    E, I = b1.shape[0], b1.shape[2] * 2
+    k = m_indices.shape[1]
+    assert a.dtype == torch.uint8 and b.dtype == torch.uint8 and b1.dtype == torch.uint8 and d.dtype == torch.bfloat16
+    assert tuple(b.shape) == (E, 2 * I, H // 2) and tuple(b1.shape) == (E, H, I // 2) and tuple(d.shape) == (T, k, H)
+    assert a_sf.dtype == torch.uint8 and tuple(a_sf.shape) == (T, H // 16) and m_indices.dtype == torch.int32
+    for g, cnt in ((a_g, 1), (b_g, E), (b1_g, E), (act_g, 1)):
+        assert g.dtype == torch.float32 and g.numel() == cnt and g.is_cuda
+    _check_bias(bias1, E, 2 * I, "bias1")
+    _check_bias(bias2, E, H, "bias2")
+    with torch.cuda.device(a.device):
+        _lib.check(_lib.load().dqmoe_moe_forward_nvfp4(
+            _p(a), _p(a_sf), _p(a_g), _p(b), _p(b_sf), _p(b_g), _p(b1), _p(b1_sf), _p(b1_g), _p(act_g), _p(bias1), _p(bias2),
+            _p(d), _p(m_indices), _p(workspace), workspace.numel() * workspace.element_size(), T, H, I, E, k,
+            _stream(a.device)))
+
+
 # ---------------------------------------------------------------------- grouped GEMM
 
 def grouped_gemm_mx(a, a_sf, w, w_sf, offsets, mtile_pref, N: int, gated: bool, out, out_sf=None, dest_to_src=None) -> None:

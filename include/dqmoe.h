@@ -57,6 +57,12 @@ extern "C" {
  * alike; the bit between FP8_BLOCKWISE (1 << 10) and FP4 (1 << 12), which the reference leaves unused
  * (csrc/quantization.h:25-38). Needs H and I to be multiples of 128. */
 #define DQMOE_QUANT_FP8_MX 2048
+/* NVFP4: e2m1 values, two per byte, with one UE4M3 scale byte per row and 16 K elements and an fp32 global scale
+ * per tensor (per expert for the weights): the bit the reference names FP4 / nvfp4() and reserves without a
+ * kernel behind it (csrc/quantization.h:30-33, 81-84, 116-119). Served by dqmoe_moe_forward_nvfp4 (the global
+ * scales do not fit dqmoe_moe_forward's argument list); dqmoe_moe_workspace_bytes accepts the value. Needs H and
+ * I to be multiples of 256. */
+#define DQMOE_QUANT_NVFP4 4096
 
 /* router scoring functions */
 #define DQMOE_SCORE_SOFTMAX 0 /* softmax over experts, top-k, renormalised to sum 1 */
@@ -126,6 +132,19 @@ int dqmoe_moe_forward_bias(const void* a, const float* a_scale, const void* b, c
                            const void* b1, const float* b1_scale, const float* bias1, const float* bias2,
                            void* d, const int32_t* m_indices, void* workspace, size_t workspace_bytes, int T,
                            int H, int I, int E, int k, int quant_mode, dqmoe_stream_t stream);
+
+/*
+ * The layer in the NVFP4 mode: a [T, H/2] packed e2m1 with a_sf [T, H/16] UE4M3 bytes row-major and a_gscale
+ * (1 float); b [E, 2I, H/2] and b1 [E, H, I/2] with tiled scale bytes (dqmoe_mx_tile_scales over cols = 2H / 2I)
+ * and per-expert global scales [E]; act_gscale (1 float) the global scale the intermediate is re-quantised
+ * with (a calibrated constant, as NVFP4 inference stacks keep one per layer); bias1 / bias2 fp32 or NULL; d
+ * [T, k, H] bf16. Workspace: dqmoe_moe_workspace_bytes(..., DQMOE_QUANT_NVFP4). No counterpart in the reference.
+ */
+int dqmoe_moe_forward_nvfp4(const void* a, const uint8_t* a_sf, const float* a_gscale, const void* b, const uint8_t* b_sf,
+                            const float* b_gscale, const void* b1, const uint8_t* b1_sf, const float* b1_gscale,
+                            const float* act_gscale, const float* bias1, const float* bias2, void* d,
+                            const int32_t* m_indices, void* workspace, size_t workspace_bytes, int T, int H, int I, int E,
+                            int k, dqmoe_stream_t stream);
 int dqmoe_moe_forward_f16_bias(const void* a, const void* b, const void* b1, const float* bias1,
                                const float* bias2, void* d, const int32_t* m_indices, void* workspace,
                                size_t workspace_bytes, int T, int H, int I, int E, int k,
@@ -380,6 +399,19 @@ int dqmoe_permute_quant_mxfp8(const void* x_bf16, int H, int k, const int32_t* d
                               const int32_t* offsets, const int32_t* mtile_prefix, int E, void* q,
                               uint8_t* scale_tiled, dqmoe_stream_t stream);
 
+/*
+ * NVFP4 quantiser over bf16 input (see DQMOE_QUANT_NVFP4; no counterpart in the reference): q [rows, cols/2]
+ * bytes, element 2i of a row in the low nibble of byte i; scale [rows, cols/16] UE4M3 bytes row-major; gscale
+ * one fp32 global scale per rows_per_gscale rows (rows for a whole tensor, rows of one expert for weights), given
+ * by the caller - amax / (448 * 6) of the rows it covers is the usual choice. Per 16-element group:
+ * scale byte = e4m3_rne((amax / 6) / g) saturating at 448, nibbles = e2m1_rne(x * (1 / (e4m3 * g))) saturating
+ * at 6 (all divisions IEEE fp32; a group whose scale byte is zero stores zeros). cols a multiple of 16.
+ * dqmoe_mx_tile_scales called with cols = 2 * (row length) turns the scale bytes into the tiled layout the
+ * grouped GEMM reads: one 512-byte block per 128 rows and 64 elements.
+ */
+int dqmoe_quant_nvfp4(const void* x_bf16, int64_t rows, int cols, const float* gscale, int64_t rows_per_gscale, void* q,
+                      uint8_t* scale, dqmoe_stream_t stream);
+
 /* ------------------------------------------------------------------ grouped GEMM */
 
 /*
@@ -425,6 +457,20 @@ int dqmoe_grouped_gemm_mx(const void* a, const uint8_t* a_sf, const void* w, con
 int dqmoe_grouped_gemm_mx_rows(const void* a, const uint8_t* a_sf, const void* w, const uint8_t* w_sf,
                                const int32_t* offsets, const int32_t* mtile_prefix, int n, int N, int K, int E,
                                const void* row_dst, dqmoe_stream_t stream);
+
+/*
+ * The grouped GEMM in the NVFP4 mode (tcgen05.mma.kind::mxf4nvf4, 16-element UE4M3 scales in TMEM): a [n, K/2]
+ * and w [E, gated ? 2N : N, K/2] packed e2m1; a_sf / w_sf tiled with one 512-byte block per 128 rows and 64 K
+ * elements; a_gscale (1 float) and w_gscale [E] the global scales, whose product multiplies the accumulator.
+ * Stage 1 re-quantises silu(gate) * value to NVFP4 with out_gscale (1 float, the caller's global scale of the
+ * intermediate) and writes [n, N/2] bytes plus out_sf, tiled like a_sf; stage 2 writes bf16 rows through
+ * dest_to_src. K a multiple of 256, N of 128. No counterpart in the reference.
+ */
+int dqmoe_grouped_gemm_nvfp4(const void* a, const uint8_t* a_sf, const float* a_gscale, const void* w,
+                             const uint8_t* w_sf, const float* w_gscale, const int32_t* offsets,
+                             const int32_t* mtile_prefix, int n, int N, int K, int E, int gated, void* out,
+                             uint8_t* out_sf, const float* out_gscale, const int32_t* dest_to_src,
+                             dqmoe_stream_t stream);
 
 /* cumulative 128-row tile counts per expert from offsets[E+1] (device to device) */
 int dqmoe_mtile_prefix(const int32_t* offsets, int E, int32_t* mtile_prefix, dqmoe_stream_t stream);

@@ -35,6 +35,7 @@ GROUP = 128
 
 QUANT_NONE, QUANT_TENSOR, QUANT_CHANNEL, QUANT_BLOCK = 0, 256, 512, 1024
 QUANT_MX = 2048   # MXFP8: e4m3 with one UE8M0 scale per 32 elements (no counterpart in the reference)
+QUANT_NVFP4 = 4096  # e2m1 with one UE4M3 scale per 16 elements and an fp32 global scale (the reference's FP4 bit, no code)
 MX_GROUP = 32
 
 
@@ -119,6 +120,85 @@ def dequant_mx(q: torch.Tensor, sf: torch.Tensor) -> torch.Tensor:
     n = q.shape[-1]
     scale = (sf.to(torch.int32) << 23).view(torch.float32)        # 2^(byte - 127)
     return (q.float().reshape(*q.shape[:-1], n // MX_GROUP, MX_GROUP) * scale.unsqueeze(-1)).reshape(q.shape)
+
+
+
+# ---------------------------------------------------------------------- NVFP4 (parity unpinned)
+
+NVFP4_GROUP = 16
+E2M1_MAX = 6.0
+_E2M1_VALUES = torch.tensor([0.0, 0.5, 1.0, 1.5, 2.0, 3.0, 4.0, 6.0])
+# round-to-nearest-even thresholds between neighbouring codes; a tie goes to the even code
+_E2M1_MID = torch.tensor([0.25, 0.75, 1.25, 1.75, 2.5, 3.5, 5.0])
+_E2M1_TIE_UP = torch.tensor([False, True, False, True, False, True, False])  # tie at mid[i] goes to code i + 1?
+
+
+def e2m1_codes(v: torch.Tensor) -> torch.Tensor:
+    """fp32 -> e2m1 code 0..15 (sign in bit 3), round to nearest even, saturating at 6."""
+    mag = v.abs()
+    code = torch.zeros(v.shape, dtype=torch.int32)
+    for i in range(7):
+        up = (mag >= _E2M1_MID[i]) if bool(_E2M1_TIE_UP[i]) else (mag > _E2M1_MID[i])
+        code += up.to(torch.int32)
+    return code | (torch.signbit(v).to(torch.int32) << 3)
+
+
+def nvfp4_global_scale(x: torch.Tensor) -> torch.Tensor:
+    """The usual global scale of a tensor: amax / (448 * 6), so that the largest block scale is the largest e4m3."""
+    return (x.float().abs().amax().clamp(min=AMAX_FLOOR) / (FP8_MAX * E2M1_MAX)).reshape(1)
+
+
+def quant_nvfp4(x: torch.Tensor, g: torch.Tensor):
+    """NVFP4 quantiser, parity unpinned (the reference names the format, csrc/quantization.h:30-33, 81-84, and has
+    no code for it). x [..., n] with n a multiple of 16; g: fp32 global scale, one value or one per leading index
+    of x (per expert for weights). Per 16 consecutive elements: scale byte = e4m3((amax / 6) / g) saturating at
+    448; nibbles = e2m1(x * (1 / (e4m3 * g))), zeros where the scale byte is zero. Returns the packed bytes
+    [..., n/2] (element 2i in the low nibble) and the scale bytes [..., n/16] (e4m3 bit patterns, uint8)."""
+    n = x.shape[-1]
+    assert n % NVFP4_GROUP == 0
+    grp = x.float().reshape(*x.shape[:-1], n // NVFP4_GROUP, NVFP4_GROUP)
+    gg = g.float().reshape(-1, *([1] * (grp.dim() - 1))) if g.numel() > 1 else g.float().reshape(())
+    s = ((grp.abs().amax(dim=-1, keepdim=True) / E2M1_MAX) / gg).clamp(max=FP8_MAX)
+    s8 = s.to(FP8)
+    d = s8.float() * gg
+    inv = torch.where(d > 0, 1.0 / d, torch.zeros_like(d))
+    codes = e2m1_codes(grp * inv).reshape(*x.shape[:-1], n // 2, 2)
+    packed = (codes[..., 0] | (codes[..., 1] << 4)).to(torch.uint8)
+    return packed.contiguous(), s8.view(torch.uint8).reshape(*x.shape[:-1], n // NVFP4_GROUP).contiguous()
+
+
+def dequant_nvfp4(packed: torch.Tensor, sf: torch.Tensor, g: torch.Tensor) -> torch.Tensor:
+    p = packed.to(torch.int32)
+    codes = torch.stack([p & 15, p >> 4], dim=-1).reshape(*packed.shape[:-1], packed.shape[-1] * 2)
+    vals = _E2M1_VALUES[(codes & 7).long()] * torch.where((codes & 8) != 0, -1.0, 1.0)
+    n = vals.shape[-1]
+    scale = sf.view(FP8).float()
+    gg = g.float().reshape(-1, *([1] * (vals.dim() - 1))) if g.numel() > 1 else g.float().reshape(())
+    return (vals.reshape(*vals.shape[:-1], n // NVFP4_GROUP, NVFP4_GROUP) * scale.unsqueeze(-1)).reshape(vals.shape) * gg
+
+
+def moe_layer_nvfp4(a_q, a_sf, a_g, b_q, b_sf, b_g, b1_q, b1_sf, b1_g, act_g, m_indices, E: int, bias1=None, bias2=None):
+    """The layer in the NVFP4 mode (parity unpinned), same steps as the other quantised modes: dequantise, fp32
+    linear, round to bf16, SwiGLU in bf16, re-quantise the intermediate to NVFP4 with the given global scale
+    act_g, dequantise, fp32 linear, round to bf16."""
+    T, k = m_indices.shape
+    H = a_q.shape[1] * 2
+    d = torch.zeros((T, k, H), dtype=torch.bfloat16)
+    a_f = dequant_nvfp4(a_q, a_sf, a_g)
+    for e in range(E):
+        tok, slot = torch.where(m_indices == e)
+        if tok.numel() == 0:
+            continue
+        inter = F.linear(a_f[tok], dequant_nvfp4(b_q[e], b_sf[e], b_g[e:e + 1]))
+        if bias1 is not None:
+            inter = inter + bias1[e].float()
+        act = _swiglu_bf16(inter.to(torch.bfloat16))
+        q, s = quant_nvfp4(act, act_g)
+        out = F.linear(dequant_nvfp4(q, s, act_g), dequant_nvfp4(b1_q[e], b1_sf[e], b1_g[e:e + 1]))
+        if bias2 is not None:
+            out = out + bias2[e].float()
+        d[tok, slot] = out.to(torch.bfloat16)
+    return d
 
 
 # ---------------------------------------------------------------------- routing
