@@ -1012,7 +1012,7 @@ def run_nvfp4(args, ops, dev, name="c2"):
         raise SystemExit("device status non-zero: a kernel's bounded wait gave up; no number reported")
     flops = 6.0 * T * k * H * I
     pk = peaks()
-    peak = 4.0 * pk["bf16_tflops"]
+    peak = 4.0 * pk["bf16"]
     # fc1 alone on the step's own sorted rows (the workspace still holds them)
     lib = _lib.load()
     n = T * k

@@ -321,83 +321,89 @@ moe_GemmGrouped_GemmUniversal_tcgen05_mx(const __grid_constant__ CUtensorMap tma
                 }
             };
 
-            if constexpr (kGated && kFp4) {
-                // act columns nt*128 + h*64 + [0, 64): four scale groups of 16, packed two values per byte
-                const float alpha = p.ga[0] * p.gw[tl.e], gout = p.gout[0];
-                uint32_t sf_bytes = 0;
+            if constexpr (kFp4) {
+                // Both NVFP4 epilogues read this warp's 128 accumulator columns into registers first and hand the
+                // buffer back at once - the shared columns to the other buffer's next tile, the whole buffer to the
+                // tile after - so that all arithmetic and all stores overlap the tensor core's next tiles.
+                uint32_t r[4][32];
 #pragma unroll
-                for (int jj = 0; jj < 2; ++jj) {
-                    const int j = buf == 0u ? 1 - jj : jj;
-                    uint32_t g[32], v[32];
-                    const int c0 = h * 64 + j * 32;
-                    ptx::tmem_ld32(t_buf + c0, g);
-                    ptx::tmem_ld32(t_buf + kBox + c0, v);
-                    const int col0 = tl.nt * kBox + c0;
-                    ptx::tmem_wait_ld(g);
-                    ptx::tmem_wait_ld(v);
-                    overlap_drained(jj + 1);
-                    float act[32];
-                    float amax[2] = {0.0f, 0.0f};
+                for (int c = 0; c < 4; ++c)
+                    ptx::tmem_ld32(t_buf + (c >> 1) * kBox + h * 64 + (c & 1) * 32, r[c]);
 #pragma unroll
-                    for (int i = 0; i < 32; ++i) {
-                        const float bg = has_bias ? __ldg(bias_e + col0 + i) : 0.0f;
-                        const float bv = has_bias ? __ldg(bias_e + N + col0 + i) : 0.0f;
-                        const float gate = bf_round_cvt(__uint_as_float(g[i]) * alpha + bg);
-                        const float val = bf_round_cvt(__uint_as_float(v[i]) * alpha + bv);
-                        act[i] = bf_round_cvt(bf_round_cvt(__fdividef(gate, 1.0f + __expf(-gate))) * val);
-                        amax[i >> 4] = fmaxf(amax[i >> 4], fabsf(act[i]));
-                    }
-                    uint32_t w4[4];
-#pragma unroll
-                    for (int b = 0; b < 2; ++b) {
-                        float inv;
-                        sf_bytes |= nvfp4_scale_byte(amax[b], gout, &inv) << (16 * j + 8 * b);
-#pragma unroll
-                        for (int hf = 0; hf < 2; ++hf) {
-                            float x8[8];
-#pragma unroll
-                            for (int i = 0; i < 8; ++i) x8[i] = act[16 * b + 8 * hf + i] * inv;
-                            w4[2 * b + hf] = f2e2m1x8(x8);
-                        }
-                    }
-                    if (row_ok)
-                        st16(static_cast<uint8_t*>(p.out) + (size_t(grow) * N + col0) / 2, Vec16{w4[0], w4[1], w4[2], w4[3]});
+                for (int c = 0; c < 4; ++c) ptx::tmem_wait_ld(r[c]);
+                ptx::tc_fence_before();
+                __syncwarp();
+                if (lane == 0) {
+                    ptx::mbar_arrive(&st.overlap_free[buf]);
+                    ptx::mbar_arrive(&st.tmem_empty[buf]);
                 }
-                // scale bytes of this row's four groups into the tile's block of the next GEMM's 64-wide K block
-                *reinterpret_cast<uint32_t*>(p.out_sf + (size_t(tl.mtile) * (N / 64) + tl.nt * 2 + h) * kSfBlock +
-                                             (r_in_tile & 31) * 16 + (r_in_tile >> 5) * 4) = sf_bytes;
-            } else if constexpr (kFp4) {
                 const float alpha = p.ga[0] * p.gw[tl.e];
-                int orow_idx = grow;
-                if (row_ok && p.dest_to_src != nullptr) orow_idx = p.dest_to_src[grow];
-                uint8_t* orow = static_cast<uint8_t*>(p.out) + size_t(orow_idx) * N * 2;
-                if (p.row_dst != nullptr) {
-                    orow = row_ok ? reinterpret_cast<uint8_t*>(p.row_dst[grow]) : nullptr;
-                    orow_idx = orow != nullptr ? 0 : -1;
-                }
-#pragma unroll 1
-                for (int cc = 0; cc < 4; ++cc) {
-                    const int c = buf == 0u ? 3 - cc : cc;
-                    uint32_t r[32];
-                    const int tc = (c >> 1) * kBox + h * 64 + (c & 1) * 32;
-                    ptx::tmem_ld32(t_buf + tc, r);
-                    const int col0 = tl.nt * kN + tc;
-                    ptx::tmem_wait_ld(r);
-                    overlap_drained(cc + 1);
+                if constexpr (kGated) {
+                    // r[j] = gate, r[2 + j] = value of act columns nt*128 + h*64 + j*32 + [0, 32): four scale groups
+                    // of 16 per thread and row, packed two values per byte
+                    const float gout = p.gout[0];
+                    uint32_t sf_bytes = 0;
+#pragma unroll
+                    for (int j = 0; j < 2; ++j) {
+                        const int col0 = tl.nt * kBox + h * 64 + j * 32;
+                        float act[32];
+                        float amax[2] = {0.0f, 0.0f};
+#pragma unroll
+                        for (int i = 0; i < 32; ++i) {
+                            const float bg = has_bias ? __ldg(bias_e + col0 + i) : 0.0f;
+                            const float bv = has_bias ? __ldg(bias_e + N + col0 + i) : 0.0f;
+                            const float gate = bf_round_cvt(__uint_as_float(r[j][i]) * alpha + bg);
+                            const float val = bf_round_cvt(__uint_as_float(r[2 + j][i]) * alpha + bv);
+                            act[i] = bf_round_cvt(bf_round_cvt(__fdividef(gate, 1.0f + __expf(-gate))) * val);
+                            amax[i >> 4] = fmaxf(amax[i >> 4], fabsf(act[i]));
+                        }
+                        uint32_t w4[4];
+#pragma unroll
+                        for (int b = 0; b < 2; ++b) {
+                            float inv;
+                            sf_bytes |= nvfp4_scale_byte(amax[b], gout, &inv) << (16 * j + 8 * b);
+#pragma unroll
+                            for (int hf = 0; hf < 2; ++hf) {
+                                float x8[8];
+#pragma unroll
+                                for (int i = 0; i < 8; ++i) x8[i] = act[16 * b + 8 * hf + i] * inv;
+                                w4[2 * b + hf] = f2e2m1x8(x8);
+                            }
+                        }
+                        if (row_ok)
+                            st16(static_cast<uint8_t*>(p.out) + (size_t(grow) * N + col0) / 2, Vec16{w4[0], w4[1], w4[2], w4[3]});
+                    }
+                    // scale bytes of this row's four groups into the tile's block of the next GEMM's 64-wide K block
+                    *reinterpret_cast<uint32_t*>(p.out_sf + (size_t(tl.mtile) * (N / 64) + tl.nt * 2 + h) * kSfBlock +
+                                                 (r_in_tile & 31) * 16 + (r_in_tile >> 5) * 4) = sf_bytes;
+                } else {
+                    int orow_idx = grow;
+                    if (row_ok && p.dest_to_src != nullptr) orow_idx = p.dest_to_src[grow];
+                    uint8_t* orow = static_cast<uint8_t*>(p.out) + size_t(orow_idx) * N * 2;
+                    if (p.row_dst != nullptr) {
+                        orow = row_ok ? reinterpret_cast<uint8_t*>(p.row_dst[grow]) : nullptr;
+                        orow_idx = orow != nullptr ? 0 : -1;
+                    }
                     if (row_ok && orow_idx >= 0) {
 #pragma unroll
-                        for (int i = 0; i < 32; i += 8) {
-                            if (col0 + i < N) {
-                                float y[8];
+                        for (int c = 0; c < 4; ++c) {
+                            const int col0 = tl.nt * kN + (c >> 1) * kBox + h * 64 + (c & 1) * 32;
 #pragma unroll
-                                for (int u = 0; u < 8; ++u)
-                                    y[u] = __uint_as_float(r[i + u]) * alpha + (has_bias ? __ldg(bias_e + min(col0 + i + u, N - 1)) : 0.0f);
-                                st16(orow + size_t(col0 + i) * 2, Vec16{pack_bf16x2(y[0], y[1]), pack_bf16x2(y[2], y[3]),
-                                                                      pack_bf16x2(y[4], y[5]), pack_bf16x2(y[6], y[7])});
+                            for (int i = 0; i < 32; i += 8) {
+                                if (col0 + i < N) {
+                                    float y[8];
+#pragma unroll
+                                    for (int u = 0; u < 8; ++u)
+                                        y[u] = __uint_as_float(r[c][i + u]) * alpha +
+                                               (has_bias ? __ldg(bias_e + min(col0 + i + u, N - 1)) : 0.0f);
+                                    st16(orow + size_t(col0 + i) * 2, Vec16{pack_bf16x2(y[0], y[1]), pack_bf16x2(y[2], y[3]),
+                                                                          pack_bf16x2(y[4], y[5]), pack_bf16x2(y[6], y[7])});
+                                }
                             }
                         }
                     }
                 }
+                continue;  // the buffer has been handed back above
             } else if constexpr (kGated) {
                 // act columns nt*128 + h*64 + [0, 64): two scale groups of 32
                 uint32_t pk[2][8];   // e4m3 bytes of the two groups in the order they were drained
