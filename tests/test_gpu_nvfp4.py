@@ -190,3 +190,41 @@ def test_nvfp4_mode_rejects_shapes_it_cannot_tile(ops):
         ops.moe_forward_nvfp4(z(T, H // 2), z(T, H // 16), f(1), z(E, 2 * I, H // 2), z(4096), f(E), z(E, H, I // 2), z(4096), f(E),
                               f(1), torch.zeros(T, k, H, dtype=torch.bfloat16, device=DEV),
                               torch.zeros(T, k, dtype=torch.int32, device=DEV), ws)
+
+
+def test_mixtral_shape_nvfp4_full_size_sample(ops):
+    """T=4096, H=4096, I=14336, E=8, top-2 in the NVFP4 mode: a sample of tokens against the oracle at full H and I,
+    and the same sample as a small batch bit for bit."""
+    T, H, I, E, k = 4096, 4096, 14336, 8, 2
+    g = torch.Generator(device=DEV).manual_seed(78)
+    x = torch.randn(T, H, generator=g, device=DEV).to(torch.bfloat16)
+    idx, _ = ops.route_topk(torch.randn(T, E, generator=g, device=DEV), k, "softmax")
+    b = (torch.randn(E, 2 * I, H, generator=g, device=DEV) * 0.02).to(torch.bfloat16)
+    b_g = (b.float().abs().amax(dim=(1, 2)) / torch.full((), 2688.0, device=DEV)).contiguous()
+    bq, bs_rows = ops.nvfp4_cast(b, b_g)
+    bs = ops.mx_tile_scales(bs_rows, 2 * H)
+    del b
+    b1 = (torch.randn(E, H, I, generator=g, device=DEV) * 0.02).to(torch.bfloat16)
+    b1_g = (b1.float().abs().amax(dim=(1, 2)) / torch.full((), 2688.0, device=DEV)).contiguous()
+    b1q, b1s_rows = ops.nvfp4_cast(b1, b1_g)
+    b1s = ops.mx_tile_scales(b1s_rows, 2 * I)
+    del b1
+    a_g = ops.nvfp4_global_scale(x)
+    aq, a_sf = ops.nvfp4_cast(x, a_g)
+    act_g = torch.tensor([64.0 / 2688.0], dtype=torch.float32, device=DEV)
+    ws = torch.empty(ops.moe_workspace_bytes(T, H, I, E, k, orc.QUANT_NVFP4), dtype=torch.uint8, device=DEV)
+    d = torch.empty(T, k, H, dtype=torch.bfloat16, device=DEV)
+    ops.moe_forward_nvfp4(aq, a_sf, a_g, bq, bs, b_g, b1q, b1s, b1_g, act_g, d, idx, ws)
+    torch.cuda.synchronize()
+    assert ops.device_status() == 0
+    assert torch.isfinite(d.float()).all() and (d.float().abs().amax(dim=2) > 0).all()
+    rows = torch.arange(3, T, 17, device=DEV)[:200]
+    small = torch.empty(rows.numel(), k, H, dtype=torch.bfloat16, device=DEV)
+    ops.moe_forward_nvfp4(aq[rows].contiguous(), a_sf[rows].contiguous(), a_g, bq, bs, b_g, b1q, b1s, b1_g, act_g, small,
+                          idx[rows].contiguous(), ws)
+    assert torch.equal(small, d[rows])
+    srows = torch.arange(5, T, 127, device=DEV)[:16]
+    ref = orc.moe_layer_nvfp4(aq[srows].cpu(), a_sf[srows].cpu(), a_g.cpu(), bq.cpu(), bs_rows.cpu(), b_g.cpu(), b1q.cpu(),
+                              b1s_rows.cpu(), b1_g.cpu(), act_g.cpu(), idx[srows].cpu(), E)
+    got = d[srows].cpu()
+    assert orc.cosine(got, ref) >= COS_MIN and orc.max_rel_err(got, ref) <= REL_MAX
