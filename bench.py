@@ -649,9 +649,9 @@ def run_prefill(args, name, wl, ops, dev, rank, world, local_rank, dist=None, ep
     else:
         layer = EPModel(wl, T, dev, 0, ops, ep, dist, out_buffers=2 if headline else 1)
         sort_l = 1 if n <= 2048 else 3
-        # peer exchange per rank and step: sort + publish/plan, dispatch, wait, row_ptrs, fc1, [requant | scale tiling],
-        # fc2, signal/wait; collective exchange: sort, gather, segment ids, the layer on the received rows, scatter
-        per_step_launches = (sort_l + 7 + (1 if mode in (512, 2048) else 0)) * world if layer.impl == "peer" else \
+        # peer exchange per rank and step: sort + publish/plan, dispatch, wait + row addresses, fc1, [requant | scale
+        # tiling], fc2, signal/wait; collective exchange: sort, gather, segment ids, the layer on the received rows, scatter
+        per_step_launches = (sort_l + 6 + (1 if mode in (512, 2048) else 0)) * world if layer.impl == "peer" else \
             (sort_l + 2 + (3 + 3 + (1 if mode in (256, 512) else 0)) + 1) * world
 
         def step():

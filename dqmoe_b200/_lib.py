@@ -69,6 +69,7 @@ SIGNATURES = {
     "dqmoe_ep_wait": (_c_int, [_ptr, _c_int, _c_int, _c_int, _ptr]),
     "dqmoe_ep_signal": (_c_int, [_ptr, _c_int, _c_int, _c_int, _c_int, _ptr]),
     "dqmoe_ep_row_ptrs": (_c_int, [_ptr, _ptr, _c_int, _ptr, _c_int, _c_size, _c_int, _ptr, _ptr]),
+    "dqmoe_ep_wait_row_ptrs": (_c_int, [_ptr, _c_int, _ptr, _ptr, _c_int, _ptr, _c_int, _c_size, _c_int, _ptr, _ptr]),
     "dqmoe_mtile_prefix": (_c_int, [_ptr, _c_int, _ptr, _ptr]),
     "dqmoe_requant_from_amax": (_c_int, [_ptr, _c_i64, _c_int, _ptr, _c_int, _ptr, _ptr, _ptr]),
     "dqmoe_requant_from_amax_dev": (_c_int, [_ptr, _c_i64, _c_int, _ptr, _c_int, _ptr, _ptr, _ptr, _ptr]),

@@ -293,6 +293,29 @@ __global__ void __launch_bounds__(256) row_ptrs_kernel(const int* __restrict__ r
     }
 }
 
+// wait for every source's phase-1 flag (rows landed), then row_ptrs: one launch; every block polls the W flags itself
+__global__ void __launch_bounds__(256) wait_row_ptrs_kernel(const int* __restrict__ my_flags, int W, int epoch, int* status,
+                                                            long long limit, const int* __restrict__ rx_home,
+                                                            const int* __restrict__ rx_offsets, int El, Peers d_out,
+                                                            size_t out_row_bytes, int cap,
+                                                            unsigned long long* __restrict__ row_dst) {
+    if (threadIdx.x < W) {
+        wait_flag(my_flags + 1 * kMaxRanks + threadIdx.x, epoch, status, 211, limit);
+        __threadfence_system();  // acquire: the rows the flags announce are visible to this kernel and those that follow
+    }
+    __syncthreads();
+    const int n_recv = rx_offsets[El];
+    for (int r = blockIdx.x * blockDim.x + threadIdx.x; r < cap; r += gridDim.x * blockDim.x) {
+        unsigned long long ptr = 0;
+        if (r < n_recv) {
+            const int h = __ldcg(rx_home + r);  // written by peers: not through the read-only path
+            ptr = reinterpret_cast<unsigned long long>(static_cast<uint8_t*>(d_out.p[h >> 27]) +
+                                                       size_t(h & ((1 << 27) - 1)) * out_row_bytes);
+        }
+        row_dst[r] = ptr;
+    }
+}
+
 static int make_peers(Peers* out, const void* const* ptrs, int W) {
     DQ_CHECK(W >= 1 && W <= kMaxRanks && ptrs != nullptr);
     for (int i = 0; i < kMaxRanks; ++i) out->p[i] = i < W ? const_cast<void*>(ptrs[i]) : nullptr;
@@ -410,6 +433,22 @@ int dqmoe_ep_signal(const void* const* flag_ptrs, int phase, int me, int W, int 
     const int rc = ep::make_peers(&flags, flag_ptrs, W);
     if (rc != DQMOE_OK) return rc;
     ep::signal_kernel<<<1, 32, 0, static_cast<cudaStream_t>(stream)>>>(flags, phase, me, W, epoch);
+    DQ_LAUNCH_CHECK();
+    return DQMOE_OK;
+}
+
+int dqmoe_ep_wait_row_ptrs(const int32_t* my_flags, int epoch, const int32_t* rx_home, const int32_t* rx_offsets, int E_local,
+                           const void* const* d_out_ptrs, int W, size_t out_row_bytes, int cap, void* row_dst,
+                           dqmoe_stream_t stream) {
+    DQ_CHECK(my_flags != nullptr && rx_home != nullptr && rx_offsets != nullptr && row_dst != nullptr && E_local > 0 && cap >= 0);
+    ep::Peers d_out;
+    const int rc = ep::make_peers(&d_out, d_out_ptrs, W);
+    if (rc != DQMOE_OK) return rc;
+    const int want = (cap + 255) / 256;
+    const int lim = sm_count() * 4;
+    ep::wait_row_ptrs_kernel<<<want < 1 ? 1 : (want < lim ? want : lim), 256, 0, static_cast<cudaStream_t>(stream)>>>(
+        my_flags, W, epoch, device_status_word(), ep::wait_limit(), rx_home, rx_offsets, E_local, d_out, out_row_bytes, cap,
+        static_cast<unsigned long long*>(row_dst));
     DQ_LAUNCH_CHECK();
     return DQMOE_OK;
 }

@@ -321,11 +321,10 @@ class PeerExpertParallelLayer:
                                          E, me, W, P["rx_rows"], P["rx_scale"], P["rx_home"], P["flags"],
                                          vp(self.done.data_ptr()), ep_, stream))
         mark("dispatch")
-        self.check(lib.dqmoe_ep_wait(vp(self.local["flags"]), 1, W, ep_, stream))
-        mark("wait_rows")
-        self.check(lib.dqmoe_ep_row_ptrs(vp(self.local["rx_home"]), vp(self.rx_offsets.data_ptr()), El, P[out_name], W,
-                                         H * 2, self.cap, vp(self.row_dst.data_ptr()), stream))
-        mark("row_ptrs")
+        self.check(lib.dqmoe_ep_wait_row_ptrs(vp(self.local["flags"]), ep_, vp(self.local["rx_home"]),
+                                              vp(self.rx_offsets.data_ptr()), El, P[out_name], W, H * 2, self.cap,
+                                              vp(self.row_dst.data_ptr()), stream))
+        mark("wait_rows+row_ptrs")
         b, bs, b1, b1s = self.weights_q
         sp = lambda t: None if t is None else vp(t.data_ptr())
         rx_scale = vp(self.local["rx_scale"]) if self.scale_cols else None

@@ -539,6 +539,10 @@ int dqmoe_ep_signal(const void* const* flag_ptrs, int phase, int me, int W, int 
 int dqmoe_ep_row_ptrs(const int32_t* rx_home, const int32_t* rx_offsets, int E_local,
                       const void* const* d_out_ptrs, int W, size_t out_row_bytes, int cap, void* row_dst,
                       dqmoe_stream_t stream);
+/* dqmoe_ep_wait on phase 1 and dqmoe_ep_row_ptrs as one launch (every block waits for the W flags itself). */
+int dqmoe_ep_wait_row_ptrs(const int32_t* my_flags, int epoch, const int32_t* rx_home, const int32_t* rx_offsets, int E_local,
+                           const void* const* d_out_ptrs, int W, size_t out_row_bytes, int cap, void* row_dst,
+                           dqmoe_stream_t stream);
 
 #ifdef __cplusplus
 }
