@@ -305,16 +305,15 @@ moe_GemmGrouped_GemmUniversal_tcgen05_mx(const __grid_constant__ CUtensorMap tma
             }
             ptx::tc_fence_after();
             const uint32_t t_buf = t_lane + (buf ? kAccCol1 : 0);
-            // The columns shared with the other buffer are the last ones of buffer 0 and the first ones of buffer 1:
-            // the chunk order starts there, and a warp reports once the shared chunks it owns are drained.
-            //   MXFP8, 24 columns: one chunk of the warps with h = 1 (buffer 0) / h = 0 (buffer 1)
-            //   NVFP4, 96 columns: buffer 0: one chunk of h = 0, two of h = 1; buffer 1: two of h = 0, one of h = 1
-            const int at_shared_end = buf == 0u ? h : 1 - h;
-            const int overlap_chunks = kFp4 ? 1 + at_shared_end : at_shared_end;
+            // The columns shared with the other buffer are the last ones of buffer 0 and the first ones of buffer 1.
+            // MXFP8 (24 columns): the chunk order starts there, and the warps that own the chunk holding them (h = 1
+            // for buffer 0, h = 0 for buffer 1) report once it is drained. NVFP4 (96 columns, every warp owns some):
+            // see below.
+            const bool owns_overlap = h == (buf == 0u ? 1 : 0);
             const bool has_bias = p.bias != nullptr;
             const float* bias_e = has_bias ? p.bias + size_t(tl.e) * p.w_rows : nullptr;
             auto overlap_drained = [&](int chunks_done) {
-                if (chunks_done == overlap_chunks) {
+                if (owns_overlap && chunks_done == 1) {
                     ptx::tc_fence_before();
                     __syncwarp();
                     if (lane == 0) ptx::mbar_arrive(&st.overlap_free[buf]);

@@ -7,6 +7,8 @@
 // block, per-chunk scatter with warp-level match ranks) or a single launch when
 // the rows fit one chunk; no atomics decide the order, so the result is the
 // stable order torch.where produces (test/util.py:80).
+#include <mutex>
+
 #include "common.cuh"
 
 namespace dq {
@@ -80,26 +82,36 @@ __device__ void block_exclusive_scan(int* s_val, int len, int* s_warp_tot) {
 
 // ---------------------------------------------------------------- pass 2: scan
 // chunk_hist becomes, per chunk and bucket, the first destination row of that chunk's rows.
+// kStaged: the whole table fits shared memory and is scanned there (coalesced in, coalesced out; walking the table
+// bucket by bucket in global memory is a chain of strided round trips: 15.7 us at 64 chunks x 129 buckets).
+template <bool kStaged>
 __global__ void __launch_bounds__(1024) sort_scan_kernel(int* __restrict__ chunk_hist, int chunks, int E,
                                                          int* __restrict__ counts, int* __restrict__ offsets,
                                                          int* __restrict__ mtile_prefix) {
+    extern __shared__ int s_hist[];  // kStaged: [chunks][E + 1]
     __shared__ int s_tot[kMaxExperts + 2];
     __shared__ int s_tiles[kMaxExperts + 2];
     __shared__ int s_warp_tot[33];
+    const int total = chunks * (E + 1);
+    int* tab = kStaged ? s_hist : chunk_hist;
+    if constexpr (kStaged) {
+        for (int i = threadIdx.x; i < total; i += blockDim.x) s_hist[i] = chunk_hist[i];
+        __syncthreads();
+    }
     // one warp per bucket, lanes over chunks: the chunk counters of a bucket are scanned 32 at a time
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, nwarps = blockDim.x >> 5;
     for (int b = warp; b <= E; b += nwarps) {
         int run = 0;
         for (int c0 = 0; c0 < chunks; c0 += 32) {
             const int c = c0 + lane;
-            const int v = c < chunks ? chunk_hist[size_t(c) * (E + 1) + b] : 0;
+            const int v = c < chunks ? tab[size_t(c) * (E + 1) + b] : 0;
             int incl = v;
 #pragma unroll
             for (int o = 1; o < 32; o <<= 1) {
                 const int up = __shfl_up_sync(0xffffffffu, incl, o);
                 if (lane >= o) incl += up;
             }
-            if (c < chunks) chunk_hist[size_t(c) * (E + 1) + b] = run + incl - v;
+            if (c < chunks) tab[size_t(c) * (E + 1) + b] = run + incl - v;
             run += __shfl_sync(0xffffffffu, incl, 31);
         }
         if (lane == 0) {
@@ -115,7 +127,7 @@ __global__ void __launch_bounds__(1024) sort_scan_kernel(int* __restrict__ chunk
         offsets[b] = s_tot[b];  // offsets[E] = number of kept rows
         if (mtile_prefix != nullptr) mtile_prefix[b] = s_tiles[b];
     }
-    for (int i = threadIdx.x; i < chunks * (E + 1); i += blockDim.x) chunk_hist[i] += s_tot[i % (E + 1)];
+    for (int i = threadIdx.x; i < total; i += blockDim.x) chunk_hist[i] = tab[i] + s_tot[i % (E + 1)];
 }
 
 // ---------------------------------------------------------------- pass 3: scatter
@@ -248,13 +260,23 @@ int route_sort(const int* ids, int n, int E, int* counts, int* offsets, int* mti
     DQ_CHECK(ids != nullptr && dest_to_src != nullptr);
     const int chunks = ceil_div(n, kChunk);
     const size_t smem_scatter = (size_t(kSortWarps) * (E + 1) + 2 * (E + 2)) * sizeof(int);
-    if (chunks == 1) {
-        static bool attr_set = false;
-        if (!attr_set && smem_scatter > 48 * 1024) {
-            DQ_CUDA(cudaFuncSetAttribute(sort_scatter_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                         int(smem_scatter)));
-            attr_set = true;
+    // shared-memory opt-ins are per function and per device
+    constexpr int kScanSmemMax = 160 * 1024;
+    static std::mutex mu;
+    static bool configured[64] = {};
+    int dev = 0;
+    DQ_CUDA(cudaGetDevice(&dev));
+    DQ_CHECK(dev >= 0 && dev < 64);
+    {
+        std::lock_guard<std::mutex> lock(mu);
+        if (!configured[dev]) {
+            DQ_CUDA(cudaFuncSetAttribute(sort_scatter_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024));
+            DQ_CUDA(cudaFuncSetAttribute(sort_scatter_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024));
+            DQ_CUDA(cudaFuncSetAttribute(sort_scan_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, kScanSmemMax));
+            configured[dev] = true;
         }
+    }
+    if (chunks == 1) {
         sort_scatter_kernel<true><<<1, kSortThreads, smem_scatter, stream>>>(ids, n, E, nullptr, counts, offsets,
                                                                             mtile_prefix, dest_to_src, src_to_dest);
         DQ_LAUNCH_CHECK();
@@ -266,14 +288,12 @@ int route_sort(const int* ids, int n, int E, int* counts, int* offsets, int* mti
     int* chunk_hist = static_cast<int*>(ws);
     sort_hist_kernel<<<chunks, kSortThreads, (E + 1) * sizeof(int), stream>>>(ids, n, E, chunk_hist);
     DQ_LAUNCH_CHECK();
-    sort_scan_kernel<<<1, 1024, 0, stream>>>(chunk_hist, chunks, E, counts, offsets, mtile_prefix);
+    const size_t smem_scan = size_t(chunks) * (E + 1) * sizeof(int);
+    if (smem_scan <= size_t(kScanSmemMax))
+        sort_scan_kernel<true><<<1, 1024, smem_scan, stream>>>(chunk_hist, chunks, E, counts, offsets, mtile_prefix);
+    else
+        sort_scan_kernel<false><<<1, 1024, 0, stream>>>(chunk_hist, chunks, E, counts, offsets, mtile_prefix);
     DQ_LAUNCH_CHECK();
-    static bool attr_set2 = false;
-    if (!attr_set2 && smem_scatter > 48 * 1024) {
-        DQ_CUDA(cudaFuncSetAttribute(sort_scatter_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                     int(smem_scatter)));
-        attr_set2 = true;
-    }
     sort_scatter_kernel<false><<<chunks, kSortThreads, smem_scatter, stream>>>(ids, n, E, chunk_hist, counts, offsets,
                                                                               mtile_prefix, dest_to_src, src_to_dest);
     DQ_LAUNCH_CHECK();

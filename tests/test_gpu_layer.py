@@ -366,3 +366,19 @@ def test_layer_replays_from_a_cuda_graph(ops, workspace, mode):
     torch.cuda.synchronize()
     assert ops.device_status() == 0
     assert_close(d, ref2)
+
+
+@pytest.mark.parametrize("mode,E,T,H,I,k", [(0, 2, 3, 4104, 2056, 2), (0, 3, 4, 1048, 520, 2), (256, 2, 4, 4112, 8208, 2),
+                                            (256, 3, 1, 1040, 528, 3)])
+def test_decode_path_ragged_sizes(ops, workspace, mode, E, T, H, I, k):
+    """Up to 8 expanded rows take the weight-streaming path: rows longer than one 4 KB ring segment with a short last
+    segment, a last pass of fewer than 8 / 16 columns (bf16 sizes that are 8 mod 16), several slots on one expert, a
+    dropped slot."""
+    a, b, b1, _, m_indices = make_inputs(19, T, H, I, E, k, 1.0, 0.05)
+    if T > 1:
+        m_indices[1, 0] = -1
+    d, ref = run_layer(a, b, b1, m_indices, mode, workspace)
+    assert ops.device_status() == 0
+    assert_close(d, ref)
+    if T > 1:
+        assert torch.count_nonzero(d[1, 0]) == 0
