@@ -2,8 +2,9 @@
 
     python tests/reference_drivers/fetch.py [reference_root]
 
-Copies test/torch_test.py, test/bench.py and test/util.py of the reference checkout (default
-/root/reference) into baseline/_ref/test/ at the root of this repository. That folder is ignored by git,
+Copies test/torch_test.py, test/bench.py and test/util.py of the reference checkout (the directory given on the
+command line or in DQMOE_REFERENCE_ROOT; REFERENCE_ROOT below otherwise) into baseline/_ref/test/ at the root of this
+repository. That folder is ignored by git,
 so the scripts never enter this repository's history; tests/test_gpu_reference_drivers.py runs
 torch_test.py from there as a child process with dqmoe_b200/dropin on PYTHONPATH, so that its
 `import moe_test` resolves to the drop-in module, as the reference's develop.sh:12-15 arranges for its own
@@ -19,6 +20,7 @@ import sys
 FILES = ("torch_test.py", "bench.py", "util.py")
 ROOT = os.path.dirname(os.path.dirname(os.path.dirname(os.path.abspath(__file__))))
 DEST = os.path.join(ROOT, "baseline", "_ref", "test")
+REFERENCE_ROOT = os.environ.get("DQMOE_REFERENCE_ROOT", "/root/reference")
 
 
 def _digest(path: str) -> str:
@@ -26,7 +28,7 @@ def _digest(path: str) -> str:
         return hashlib.sha256(f.read()).hexdigest()
 
 
-def fetch(reference_root: str = "/root/reference") -> bool:
+def fetch(reference_root: str = REFERENCE_ROOT) -> bool:
     """True when the three scripts are in place (copied now or earlier); False without a reference checkout."""
     src_dir = os.path.join(reference_root, "test")
     if not all(os.path.exists(os.path.join(src_dir, f)) for f in FILES):
@@ -41,5 +43,5 @@ def fetch(reference_root: str = "/root/reference") -> bool:
 
 
 if __name__ == "__main__":
-    ok = fetch(sys.argv[1] if len(sys.argv) > 1 else "/root/reference")
+    ok = fetch(sys.argv[1] if len(sys.argv) > 1 else REFERENCE_ROOT)
     print(DEST if ok else "no reference checkout found")
